@@ -1,0 +1,47 @@
+/* Additive operator exports of the B200 build.  Same calling contract as
+ * tinyinfer_backend_v2.h (device pointers, caller-owned stream, device already current,
+ * host-side validation before anything is enqueued, ti_v2_last_error for the text).
+ * The reference has no such entry points: it runs these steps as separate kernels
+ * (ti_v2_gemm_ex_i8 -> ti_v2_gelu_new_f16 / add, gather_cache -> ti_v2_attention_f16,
+ * llm/src/runtime.cu:142-154); they exist so the fused forms the model runtime uses can be
+ * called, checked against that sequence and timed on their own.
+ */
+#ifndef TINYINFER_B200_EXT_H
+#define TINYINFER_B200_EXT_H
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* INT8-weight GEMM with the epilogue fused:
+ *   t = fp16(acc + bias);  if (gelu) t = fp16(gelu_tanh(t));  if (residual) t = fp16(residual + t)
+ * i.e. the rounding points of reference ti_v2_gemm_ex_i8 (backend/runtime_v2.cu:69-76) followed
+ * by ti_v2_gelu_new_f16 (:97-101) and the runtime's residual add (llm/src/runtime.cu:31-33).
+ * output_dtype 1 (fp32) allows neither gelu nor residual.  residual is fp16 [M,N], nullable. */
+int ti_b200_gemm_i8_fused(const uint16_t* a, const int8_t* b, const float* scales, const uint16_t* bias,
+                          const uint16_t* residual, void* y, int m, int n, int k, int output_dtype, int gelu,
+                          uintptr_t stream, int device);
+
+/* Decode attention (one query per request) reading k/v[B,H,K,64] in place:
+ * q[B,H,1,64] -> y[B,H,1,64], keys 0..kv_lengths[b]-1 visible.  Equals reference
+ * ti_v2_attention_f16 (backend/runtime_v2.cu:82-90) with q_len 1 and
+ * query_offsets = kv_lengths-1.  Each (request, head) history is cut into chunks of `chunk`
+ * keys (multiple of 32) processed by separate CTAs; their partial results live in `scratch`,
+ * device memory of at least ti_b200_attention_decode_scratch_floats(...) floats, 16-byte
+ * aligned, owned by the caller and private to this call until it completes. */
+int64_t ti_b200_attention_decode_scratch_floats(int batch, int heads, int kv_len, int chunk);
+int ti_b200_attention_decode_f16(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* y,
+                                 const int32_t* kv_lengths, int batch, int heads, int kv_len, int head_dim,
+                                 int chunk, float* scratch, int64_t scratch_floats, uintptr_t stream, int device);
+
+/* Exported by libtinyinfer_llm.so.  Verifies manifest.json + weights.bin exactly as
+ * ti_llm_create does before touching the GPU (reference llm/src/artifact.hpp:153-199; the
+ * reference only reaches these checks through ti_llm_create) and reports the model shape.
+ * Pure host code.  Returns a ti_llm_status; ti_llm_last_error() has the text.  Out-pointers
+ * are optional. */
+int ti_b200_artifact_check(const char* manifest_path, int32_t* layers, int32_t* heads, int32_t* hidden,
+                           int32_t* int8_weights);
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,283 @@
+// Ragged causal attention over per-request KV histories, fp16 in / fp32 math / fp16 out.
+//
+// Semantics are the reference's online_attention (kernels/src/cuda/tc/attention.cu:9-57):
+// key j is visible to query i of request b when j < min(kv_len, kv_lengths[b]) and
+// (!causal || j <= query_offsets[b] + i); the score is q.k * rsqrt(D); the softmax runs on an
+// online (max, sum, acc) state in fp32; query rows at or past q_lengths[b] and rows that see no
+// key are written as exact zeros.
+//
+// Two kernels, both HBM/L2-bound streaming kernels with no tensor-core use:
+//   attn_tile_kernel     any number of queries per request (prefill, operator ABI): 8 queries
+//                        per CTA share 32-key K/V tiles staged in shared memory.
+//   attn_decode_kernel   one query per request (decode): the history of one (request, head) is
+//                        cut into chunks, one CTA per chunk, K/V read in place with fully
+//                        coalesced 16-byte loads (4 keys x 128 B per warp instruction); chunk
+//                        results (max, sum, unnormalised acc) go to a scratch buffer and
+//                        attn_combine_kernel merges them.  With a single chunk the result is
+//                        written directly.
+//
+// K/V are reached through an accessor: packed [B,H,K,D] tensors (operator ABI) or the paged
+// pool of the model runtime (pages of 32 positions, [page][layer][head][32][D], located through
+// a per-slot page table), so the cache is read where it lives -- no gather copy.
+#pragma once
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace tib {
+
+constexpr int kPageTokens = 32;
+
+struct KvPacked {
+  const __half* k; const __half* v; int heads, kv_len, d;
+  __device__ __forceinline__ size_t offset(int b, int h, int key) const {
+    return ((size_t(b) * heads + h) * kv_len + key) * d;
+  }
+};
+struct KvPaged {
+  const __half* k; const __half* v;       // page pools
+  const int32_t* table;                   // [slots][table_pitch] page ids
+  const int32_t* slots;                   // [batch] slot of each request
+  int table_pitch, layers, layer, heads, d;
+  __device__ __forceinline__ size_t offset(int b, int h, int key) const {
+    const int page = table[size_t(slots[b]) * table_pitch + (key / kPageTokens)];
+    return (((size_t(page) * layers + layer) * heads + h) * kPageTokens + (key % kPageTokens)) * d;
+  }
+};
+
+struct AttnArgs {
+  const __half* q; long long q_sb, q_sh, q_si;      // element strides: request, head, query row
+  __half* out; long long o_sb, o_sh, o_si;
+  const int32_t* row_start;                        // optional: request b starts at row row_start[b] (replaces b*q_sb, b*o_sb)
+  const int32_t* q_lengths; const int32_t* kv_lengths; const int32_t* offsets;
+  int batch, heads, q_len, kv_len, causal;
+};
+
+// ------------------------------------------------------------------ tiled kernel (Q >= 1)
+constexpr int kAttnTileQ = 8, kAttnTileK = 32;
+
+template <int D, typename KV>
+__global__ void __launch_bounds__(256)
+attn_tile_kernel(const AttnArgs p, const KV kv) {
+  constexpr int PITCH = D + 8;                                  // halves; keeps 16-byte row reads conflict-free
+  __shared__ __align__(16) __half ks[kAttnTileK][PITCH];
+  __shared__ __align__(16) __half vs[kAttnTileK][D];
+  __shared__ __align__(16) __half qs[kAttnTileQ][D];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int h = blockIdx.y, b = blockIdx.z, qi = blockIdx.x * kAttnTileQ + warp;
+  pdl_wait();
+  const int q_valid = max(0, min(p.q_len, p.q_lengths[b]));
+  const int kv_valid = max(0, min(p.kv_len, p.kv_lengths[b]));
+  const long long off = p.offsets[b];
+  const long long q_base = p.row_start ? p.row_start[b] * p.q_si : b * p.q_sb;
+  const long long o_base = p.row_start ? p.row_start[b] * p.o_si : b * p.o_sb;
+  const bool active = qi < q_valid;
+  const int last_query = min(q_valid - 1, int(blockIdx.x) * kAttnTileQ + kAttnTileQ - 1);
+  long long bound = p.causal ? off + last_query + 1 : kv_valid;
+  const int end = last_query < 0 || bound < 0 ? 0 : int(bound < (long long)kv_valid ? bound : (long long)kv_valid);
+  const long long my_last = p.causal ? off + qi : (long long)kv_valid - 1;   // last visible key of this row
+
+  for (int i = lane; i < D / 8; i += 32) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (active) v = *reinterpret_cast<const uint4*>(p.q + q_base + h * p.q_sh + (long long)qi * p.q_si + i * 8);
+    *reinterpret_cast<uint4*>(&qs[warp][i * 8]) = v;
+  }
+  float m = -CUDART_INF_F, l = 0.f, acc[D / 32];
+#pragma unroll
+  for (int z = 0; z < D / 32; ++z) acc[z] = 0.f;
+
+  for (int k0 = 0; k0 < end; k0 += kAttnTileK) {
+    __syncthreads();
+    for (int i = tid; i < kAttnTileK * (D / 8); i += 256) {
+      const int r = i / (D / 8), c = i % (D / 8), key = k0 + r;
+      uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
+      if (key < end) {
+        const size_t o = kv.offset(b, h, key) + c * 8;
+        kk = *reinterpret_cast<const uint4*>(kv.k + o);
+        vv = *reinterpret_cast<const uint4*>(kv.v + o);
+      }
+      *reinterpret_cast<uint4*>(&ks[r][c * 8]) = kk;
+      *reinterpret_cast<uint4*>(&vs[r][c * 8]) = vv;
+    }
+    __syncthreads();
+    const int key = k0 + lane;
+    const bool visible = active && key < end && (long long)key <= my_last;
+    float score = 0.f;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+      const uint4 qq = *reinterpret_cast<const uint4*>(&qs[warp][c * 8]);
+      const uint4 kk = *reinterpret_cast<const uint4*>(&ks[lane][c * 8]);
+      const __half2* q2 = reinterpret_cast<const __half2*>(&qq);
+      const __half2* k2 = reinterpret_cast<const __half2*>(&kk);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        score = fma_f16(score, __low2half(q2[e]), __low2half(k2[e]));
+        score = fma_f16(score, __high2half(q2[e]), __high2half(k2[e]));
+      }
+    }
+    score = visible ? score * rsqrtf(float(D)) : -CUDART_INF_F;
+    const float tile_max = warp_max(score);
+    if (tile_max > -CUDART_INF_F) {                              // warp-uniform
+      const float next = fmaxf(m, tile_max);
+      const float alpha = expf(m - next);                        // exp(-inf) = 0 on the first tile
+      const float pr = visible ? expf(score - next) : 0.f;
+      l = l * alpha + warp_sum(pr);
+#pragma unroll
+      for (int z = 0; z < D / 32; ++z) acc[z] *= alpha;
+      for (int j = 0; j < kAttnTileK; ++j) {
+        const float pj = __shfl_sync(0xffffffffu, pr, j);
+#pragma unroll
+        for (int z = 0; z < D / 32; ++z) acc[z] = fmaf(pj, h2f(vs[j][lane + 32 * z]), acc[z]);
+      }
+      m = next;
+    }
+  }
+  pdl_launch_dependents();
+  if (qi < p.q_len) {
+    __half* o = p.out + o_base + h * p.o_sh + (long long)qi * p.o_si;
+#pragma unroll
+    for (int z = 0; z < D / 32; ++z) o[lane + 32 * z] = f2h(l > 0.f ? acc[z] / l : 0.f);
+  }
+}
+
+// ------------------------------------------------------------------ decode kernel (Q == 1)
+constexpr int kDecodeWarps = 4;
+
+struct DecodeArgs {
+  const __half* q; long long q_sb, q_sh;            // one query row per request
+  __half* out; long long o_sb, o_sh;
+  const int32_t* kv_lengths;                         // visible keys of each request (its new token included)
+  float* part_acc;                                   // scratch fp32 [batch][heads][chunks][D]
+  float* part_ml;                                    // scratch fp32 [batch][heads][chunks][2]  (max, sum)
+  int batch, heads, chunk, chunks;                   // keys per CTA; grid.x
+};
+
+// grid = (chunks, heads, batch), block = 128.
+template <int D, typename KV>
+__global__ void __launch_bounds__(kDecodeWarps * 32)
+attn_decode_kernel(const DecodeArgs p, const KV kv) {
+  static_assert(D == 64 || D == 128, "head_dim");
+  constexpr int DP = D / 8;                           // lanes that share one key (8 dims each)
+  constexpr int KPS = 32 / DP;                        // keys per warp instruction
+  constexpr int STEPS = 32 / KPS;                     // instructions per 32-key tile
+  __shared__ float s_acc[kDecodeWarps][D];
+  __shared__ float s_ml[kDecodeWarps][2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int dp = lane % DP, ksub = lane / DP;
+  const int h = blockIdx.y, b = blockIdx.z;
+  pdl_wait();
+  const int len = p.kv_lengths[b];
+  const int begin = blockIdx.x * p.chunk, end = min(len, begin + p.chunk);
+  if (begin >= end && !(blockIdx.x == 0)) return;     // nothing to do for this chunk (uniform per CTA)
+
+  const uint4 qraw = *reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + dp * 8);
+  const __half2* q2 = reinterpret_cast<const __half2*>(&qraw);
+  float m = -CUDART_INF_F, l = 0.f, acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+
+  for (int t0 = begin + warp * 32; t0 < end; t0 += kDecodeWarps * 32) {
+    uint4 kreg[STEPS], vreg[STEPS];
+#pragma unroll
+    for (int i = 0; i < STEPS; ++i) {
+      const int key = t0 + i * KPS + ksub;
+      kreg[i] = make_uint4(0, 0, 0, 0); vreg[i] = kreg[i];
+      if (key < end) {
+        const size_t o = kv.offset(b, h, key) + dp * 8;
+        kreg[i] = *reinterpret_cast<const uint4*>(kv.k + o);
+        vreg[i] = *reinterpret_cast<const uint4*>(kv.v + o);
+      }
+    }
+    float sc[STEPS], tile_max = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < STEPS; ++i) {
+      const __half2* k2 = reinterpret_cast<const __half2*>(&kreg[i]);
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        d = fma_f16(d, __low2half(q2[e]), __low2half(k2[e]));
+        d = fma_f16(d, __high2half(q2[e]), __high2half(k2[e]));
+      }
+#pragma unroll
+      for (int x = 1; x < DP; x <<= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+      const int key = t0 + i * KPS + ksub;
+      sc[i] = key < end ? d * rsqrtf(float(D)) : -CUDART_INF_F;
+      tile_max = fmaxf(tile_max, sc[i]);
+    }
+#pragma unroll
+    for (int x = DP; x < 32; x <<= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, x));
+    const float next = fmaxf(m, tile_max);              // the tile holds at least one key
+    const float alpha = expf(m - next);
+    l *= alpha;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] *= alpha;
+#pragma unroll
+    for (int i = 0; i < STEPS; ++i) {
+      const float pr = expf(sc[i] - next);               // exp(-inf) = 0 for keys past the end
+      l += pr;
+      const __half2* v2 = reinterpret_cast<const __half2*>(&vreg[i]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] = fmaf(pr, __low2float(v2[e]), acc[2 * e]);
+        acc[2 * e + 1] = fmaf(pr, __high2float(v2[e]), acc[2 * e + 1]);
+      }
+    }
+    m = next;
+  }
+  // key sub-groups of the warp share `m`; add their sums
+#pragma unroll
+  for (int x = DP; x < 32; x <<= 1) {
+    l += __shfl_xor_sync(0xffffffffu, l, x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], x);
+  }
+  if (lane < DP) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_acc[warp][dp * 8 + e] = acc[e];
+    if (lane == 0) { s_ml[warp][0] = m; s_ml[warp][1] = l; }
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+  if (tid < D) {
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) mm = fmaxf(mm, s_ml[w][0]);
+    float ll = 0.f, aa = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDecodeWarps; ++w) {
+      const float f = s_ml[w][0] > -CUDART_INF_F ? expf(s_ml[w][0] - mm) : 0.f;
+      ll += s_ml[w][1] * f; aa += s_acc[w][tid] * f;
+    }
+    if (p.chunks == 1) {
+      p.out[b * p.o_sb + h * p.o_sh + tid] = f2h(ll > 0.f ? aa / ll : 0.f);
+    } else {
+      const size_t slot = (size_t(b) * p.heads + h) * p.chunks + blockIdx.x;
+      p.part_acc[slot * D + tid] = aa;
+      if (tid == 0) { p.part_ml[slot * 2] = mm; p.part_ml[slot * 2 + 1] = ll; }
+    }
+  }
+}
+
+// grid = (heads, batch), block = D.  Merges the chunk partials of one (request, head).
+template <int D>
+__global__ void __launch_bounds__(D)
+attn_combine_kernel(const DecodeArgs p) {
+  const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
+  pdl_wait();
+  const int len = p.kv_lengths[b];
+  const int used = max(1, min(p.chunks, (len + p.chunk - 1) / p.chunk));
+  const size_t base = (size_t(b) * p.heads + h) * p.chunks;
+  float mm = -CUDART_INF_F;
+  for (int c = 0; c < used; ++c) mm = fmaxf(mm, p.part_ml[(base + c) * 2]);
+  float ll = 0.f, aa = 0.f;
+  for (int c = 0; c < used; ++c) {
+    const float mc = p.part_ml[(base + c) * 2];
+    const float f = mc > -CUDART_INF_F ? expf(mc - mm) : 0.f;
+    ll += p.part_ml[(base + c) * 2 + 1] * f;
+    aa += p.part_acc[(base + c) * D + tid] * f;
+  }
+  pdl_launch_dependents();
+  p.out[b * p.o_sb + h * p.o_sh + tid] = f2h(ll > 0.f ? aa / ll : 0.f);
+}
+
+}  // namespace tib

@@ -1,0 +1,125 @@
+// Device-side building blocks shared by every kernel of the INT8-weight decode path:
+// binary16 helpers, the int8 -> fp16 weight dequantisation with the reference's rounding,
+// mbarrier / TMA (cp.async.bulk.tensor) wrappers for sm_100a, and bounded waits.
+//
+// Every wait on an mbarrier is bounded: after kSpinLimit polls the waiter records a code in
+// the library's device status word and returns false, and the caller falls through to the
+// kernel's exit path instead of spinning.  The status word is read by the host runtime after
+// it synchronises (tib::read_device_status).
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace tib {
+
+constexpr uint32_t kSpinLimit = 1u << 22;   // polls of ~20-40 ns each: far above any healthy TMA latency
+
+enum DeviceStatus : unsigned int {
+  kStatusOk = 0,
+  kStatusTmaTimeout = 1,       // a weight tile never arrived
+  kStatusMmaTimeout = 2,       // a tcgen05.commit never arrived
+  kStatusPipeTimeout = 3,      // a consumer never released a stage
+};
+
+// One status word per device for the library (defined in kernels.cu, the only device translation unit).
+#ifndef TIB_STATUS_DEFINED
+extern __device__ unsigned int g_device_status;
+#endif
+
+__device__ __forceinline__ void report(unsigned int code) { atomicCAS(&g_device_status, 0u, code); }
+
+// ------------------------------------------------------------------ binary16 helpers
+__device__ __forceinline__ float h2f(__half h) { return __half2float(h); }
+__device__ __forceinline__ __half f2h(float f) { return __float2half_rn(f); }
+
+// Weight used in every product: fp16_rn(float(q) * scale)  (reference load_stage,
+// kernels/src/cuda/tc/gemm.cu:21-24 with dequantize_scalar).  Two at a time: the pair of fp32
+// products is narrowed by one cvt.rn.f16x2.f32.
+__device__ __forceinline__ __half2 dequant2(int q_lo, int q_hi, float s_lo, float s_hi) {
+  return __floats2half2_rn(float(q_lo) * s_lo, float(q_hi) * s_hi);
+}
+
+// acc += float(a) * float(b), one rounding (the product of two binary16 values is exact in
+// binary32).  Mixed-precision FMA of the sm_100 family.
+__device__ __forceinline__ float fma_f16(float acc, __half a, __half b) {
+  asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(acc) : "h"(__half_as_ushort(a)), "h"(__half_as_ushort(b)));
+  return acc;
+}
+
+// tanh-GELU exactly as the reference writes it (kernels/src/cuda/tc/elementwise.cu:30-31).
+__device__ __forceinline__ float gelu_tanh(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// ------------------------------------------------------------------ shared-memory addresses
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ------------------------------------------------------------------ mbarrier
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
+// Bounded wait; false (and a recorded status) if the phase never completes.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int code) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    if (mbar_try(bar, parity)) return true;
+  report(code);
+  return false;
+}
+
+// ------------------------------------------------------------------ TMA (tensor tile loads, no multicast)
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
+// 2-D tile load: x is the fast (contiguous) coordinate and x * element_size must be a multiple
+// of 16 bytes; out-of-range parts of the box are filled with zeros.
+__device__ __forceinline__ void tma_load_2d(void* dst, const void* tmap, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+// Generic-proxy writes to shared memory made visible to the async proxy (TMA / tcgen05).
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// wait: block until the kernels this launch depends on have completed and flushed.
+// launch_dependents: allow the next kernel in the stream to start its prologue.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ------------------------------------------------------------------ warp reductions
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, d));
+  return v;
+}
+
+}  // namespace tib

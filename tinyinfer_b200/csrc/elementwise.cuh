@@ -1,0 +1,101 @@
+// Row-wise LayerNorm / softmax and element-wise tanh-GELU on fp16 rows (fp32 math).
+//
+// The reference sums a row with 256 threads (thread t takes columns t, t+256, ... in order)
+// followed by a halving tree over the 256 partials (block_sum, kernels/src/cuda/tc/
+// elementwise.cu:7-14).  Here ONE warp owns a row and replays that exact order: lane L holds
+// the partials of the virtual threads L, L+32, ..., L+224; tree levels 128/64/32 fold
+// registers inside a lane, levels 16..1 are shuffles.  The fp32 sums -- and therefore mean,
+// variance and every output -- carry the same bits as the reference while a 768-wide row costs
+// one warp instead of a 256-thread block with eight barriers.
+#pragma once
+#include <math_constants.h>
+
+#include "common.cuh"
+
+namespace tib {
+
+// Sum of v[j] (virtual thread lane + 32*j) over all 256 virtual threads, reference order.
+__device__ __forceinline__ float tree256(float (&v)[8]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] += v[j + 4];
+  v[0] += v[2]; v[1] += v[3];
+  float x = v[0] + v[1];
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) x += __shfl_down_sync(0xffffffffu, x, d);
+  return __shfl_sync(0xffffffffu, x, 0);
+}
+
+// Mean and 1/sqrt(var+eps) of one row, by one warp (reference norm, elementwise.cu:15-24).
+__device__ __forceinline__ void row_stats(const __half* x, int cols, float eps, float& mean, float& inv) {
+  const int lane = threadIdx.x & 31;
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float s = 0.f;
+    for (int c = lane + 32 * j; c < cols; c += 256) s += h2f(x[c]);
+    v[j] = s;
+  }
+  mean = tree256(v) / cols;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float s = 0.f;
+    for (int c = lane + 32 * j; c < cols; c += 256) { const float z = h2f(x[c]) - mean; s += z * z; }
+    v[j] = s;
+  }
+  inv = rsqrtf(tree256(v) / cols + eps);
+}
+
+// grid = ceil(rows / 4), block = 128: one warp per row.
+__global__ void __launch_bounds__(128)
+layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, const __half* b, __half* y,
+                 int rows, int cols, float eps) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  pdl_wait();
+  if (row >= rows) return;
+  const __half* xr = x + size_t(row_index ? row_index[row] : row) * cols;   // optional gather of input rows
+  __half* yr = y + size_t(row) * cols;
+  float mean, inv;
+  row_stats(xr, cols, eps, mean, inv);
+  pdl_launch_dependents();
+  for (int c = lane; c < cols; c += 32)
+    yr[c] = f2h((h2f(xr[c]) - mean) * inv * h2f(g[c]) + h2f(b[c]));
+}
+
+// Row softmax (reference normalized_exp, elementwise.cu:34-46), one warp per row.
+__global__ void __launch_bounds__(128)
+softmax_kernel(const __half* x, __half* y, int rows, int cols) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __half* xr = x + size_t(row) * cols;
+  __half* yr = y + size_t(row) * cols;
+  float top = -CUDART_INF_F;
+  for (int c = lane; c < cols; c += 32) top = fmaxf(top, h2f(xr[c]));
+  top = warp_max(top);
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float s = 0.f;
+    for (int c = lane + 32 * j; c < cols; c += 256) s += expf(h2f(xr[c]) - top);
+    v[j] = s;
+  }
+  const float denom = tree256(v);
+  for (int c = lane; c < cols; c += 32) yr[c] = f2h(expf(h2f(xr[c]) - top) / denom);
+}
+
+// tanh-GELU (reference gelu, elementwise.cu:28-33); grid-stride, 8 values per thread when the
+// buffers are 16-byte aligned.
+__global__ void __launch_bounds__(256)
+gelu_kernel(const __half* x, __half* y, long long count, int vector_ok) {
+  const long long stride = (long long)gridDim.x * blockDim.x, t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long vec = vector_ok ? count / 8 : 0;
+  for (long long i = t; i < vec; i += stride) {
+    uint4 raw = reinterpret_cast<const uint4*>(x)[i];
+    __half* hv = reinterpret_cast<__half*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) hv[e] = f2h(gelu_tanh(h2f(hv[e])));
+    reinterpret_cast<uint4*>(y)[i] = raw;
+  }
+  for (long long i = vec * 8 + t; i < count; i += stride) y[i] = f2h(gelu_tanh(h2f(x[i])));
+}
+
+}  // namespace tib

@@ -1,0 +1,248 @@
+// Skinny weight-streaming GEMM ("GEMV" at decode batch sizes) for sm_100a.
+//
+//   out[M,N] = A[M,K] (fp16) . W[K,N] + bias[N],  W = int8 with per-column fp32 scales
+//   (dequantised as fp16_rn(float(q)*scale), the reference's rounding, gemm.cu:21-24) or fp16.
+//
+// HBM-bound: every weight byte is read once per M-tile.  A CTA owns a 128-byte-wide column
+// slab of W and a contiguous K range; a thread-block cluster of up to 8 CTAs splits K for one
+// slab and reduces its partial sums through distributed shared memory in rank order, so the
+// result does not depend on timing.  Weight tiles (64 rows x 128 bytes) are staged by TMA
+// (cp.async.bulk.tensor.2d, zero fill out of range) into a ring of shared-memory stages guarded
+// by full/empty mbarriers; a thread reads 16 bytes of one row (ld.shared.v4), dequantises
+// them once and issues mixed-precision FMAs (fp16 x fp16 + fp32) against up to 4 rows of A
+// held in shared memory.  Rows are reduced with warp shuffles (4 row-lanes per warp) and a
+// fixed-order pass over the 8 warps.
+//
+// Epilogue (fused): + bias -> fp16 round -> optional tanh-GELU (+ fp16 round) -> optional
+// residual add (+ fp16 round), or fp32 store for the vocabulary projection.  These are the
+// rounding points of the reference's separate kernels (gemm.cu:76-78, elementwise.cu:30-31,
+// llm/src/runtime.cu:31-33).
+//
+// When W cannot be described by a tensor map (row pitch or base not a multiple of 16 bytes,
+// e.g. N = 50257) the same compute runs on tiles filled by guarded byte loads.
+#pragma once
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace tib {
+namespace cg = cooperative_groups;
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvRowBytes = 128;        // bytes of one weight row per CTA slab
+constexpr int kGemvStageRows = 64;
+constexpr int kGemvStages = 4;
+constexpr int kGemvMaxMT = 4;             // rows of A per pass
+constexpr int kGemvAChunk = 4096;         // K values of A resident in shared memory at a time
+
+struct GemvArgs {
+  const __half* a;            // [M,K], row pitch lda
+  const void* w;              // int8 or fp16 [K,N], row pitch ldw elements
+  const float* scales;        // fp32[N] for int8 weights
+  const __half* bias;         // fp16[N] or null
+  void* out;                  // fp16 or fp32 [M,N], row pitch ldo
+  const __half* residual;     // fp16 [M,N] (pitch ldo) or null; fp16 output only
+  int lda, ldo;
+  long long ldw;
+  int m, n, k;
+  int k_chunk;                // K rows per CTA, multiple of kGemvStageRows
+  int out_fp32, gelu;
+};
+
+template <typename WT> struct WeightTraits;
+template <> struct WeightTraits<int8_t> { static constexpr int kCols = 16; };   // columns per 16-byte read
+template <> struct WeightTraits<__half> { static constexpr int kCols = 8; };
+
+struct GemvSmem {
+  static constexpr int kStageBytes = kGemvStageRows * kGemvRowBytes;
+  static constexpr int kStagesOff = 0;
+  static constexpr int kAOff = kStagesOff + kGemvStages * kStageBytes;                       // fp16 [MT][kGemvAChunk]
+  static constexpr int kRedOff = kAOff + kGemvMaxMT * kGemvAChunk * 2;                       // fp32 [8 warps][MT][128]
+  static constexpr int kPartOff = kRedOff + 8 * kGemvMaxMT * 128 * 4;                        // fp32 [MT][128]
+  static constexpr int kBarOff = kPartOff + kGemvMaxMT * 128 * 4;
+  static constexpr int kBytes = kBarOff + 2 * kGemvStages * 8 + 64;
+};
+
+template <typename WT, int MT>
+__device__ __forceinline__ void gemv_consume_stage(const uint8_t* stage, const __half* a_smem, int a_pitch, int kk0,
+                                                   const float* s, float (&acc)[MT][WeightTraits<WT>::kCols]) {
+  constexpr int C = WeightTraits<WT>::kCols;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int it = 0; it < kGemvStageRows / 32; ++it) {
+    const int r = it * 32 + warp * 4 + (lane >> 3);
+    const uint4 raw = *reinterpret_cast<const uint4*>(stage + r * kGemvRowBytes + (lane & 7) * 16);
+    __half2 w2[C / 2];
+    if constexpr (sizeof(WT) == 1) {
+      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int q0 = int(int8_t(words[j] & 0xffu)), q1 = int(int8_t((words[j] >> 8) & 0xffu));
+        const int q2 = int(int8_t((words[j] >> 16) & 0xffu)), q3 = int(int8_t(words[j] >> 24));
+        w2[2 * j] = dequant2(q0, q1, s[4 * j], s[4 * j + 1]);
+        w2[2 * j + 1] = dequant2(q2, q3, s[4 * j + 2], s[4 * j + 3]);
+      }
+    } else {
+      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w2[j] = *reinterpret_cast<const __half2*>(&words[j]);
+    }
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const __half av = a_smem[m * a_pitch + kk0 + r];
+#pragma unroll
+      for (int j = 0; j < C / 2; ++j) {
+        acc[m][2 * j] = fma_f16(acc[m][2 * j], av, __low2half(w2[j]));
+        acc[m][2 * j + 1] = fma_f16(acc[m][2 * j + 1], av, __high2half(w2[j]));
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void gemv_store(const GemvArgs& p, int row, int col, float acc) {
+  const float v = acc + (p.bias ? h2f(p.bias[col]) : 0.f);
+  if (p.out_fp32) { static_cast<float*>(p.out)[size_t(row) * p.ldo + col] = v; return; }
+  __half h = f2h(v);
+  if (p.gelu) h = f2h(gelu_tanh(h2f(h)));
+  if (p.residual) h = f2h(h2f(p.residual[size_t(row) * p.ldo + col]) + h2f(h));
+  static_cast<__half*>(p.out)[size_t(row) * p.ldo + col] = h;
+}
+
+// grid = (column slabs, k splits [cluster dimension], M tiles); block = 256.
+template <typename WT, int MT, bool TMA>
+__global__ void __launch_bounds__(kGemvThreads, 2)
+gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
+  constexpr int C = WeightTraits<WT>::kCols;
+  constexpr int BN = 8 * C;                                   // columns per slab: 128 (int8) or 64 (fp16)
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* stages = smem + GemvSmem::kStagesOff;
+  __half* a_smem = reinterpret_cast<__half*>(smem + GemvSmem::kAOff);
+  float* red = reinterpret_cast<float*>(smem + GemvSmem::kRedOff);
+  float* part = reinterpret_cast<float*>(smem + GemvSmem::kPartOff);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + GemvSmem::kBarOff);
+  uint64_t* empty = full + kGemvStages;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int splits = int(gridDim.y), rank = int(blockIdx.y);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.z * MT;
+  const int k_begin = rank * p.k_chunk, k_end = min(p.k, k_begin + p.k_chunk);
+  const int n_stages_total = k_end > k_begin ? (k_end - k_begin + kGemvStageRows - 1) / kGemvStageRows : 0;
+
+  if (TMA && tid == 0) {
+    tma_prefetch_desc(&w_map);
+    for (int s = 0; s < kGemvStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kGemvThreads / 32); }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  // Weights do not depend on the producer of A: start streaming before anything else.
+  int issued = 0;
+  if (TMA && tid == 0) {
+    for (; issued < min(kGemvStages, n_stages_total); ++issued) {
+      mbar_expect_tx(&full[issued], GemvSmem::kStageBytes);
+      tma_load_2d(stages + issued * GemvSmem::kStageBytes, &w_map, n0, k_begin + issued * kGemvStageRows, &full[issued]);
+    }
+  }
+
+  float s[C];
+#pragma unroll
+  for (int j = 0; j < C; ++j) {
+    const int col = n0 + (lane & 7) * C + j;
+    s[j] = (sizeof(WT) == 1 && col < p.n) ? p.scales[col] : 1.f;
+  }
+  float acc[MT][C];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int j = 0; j < C; ++j) acc[m][j] = 0.f;
+
+  pdl_wait();   // A (and the residual) come from the previous kernel in the stream
+
+  bool healthy = true;
+  int stage_index = 0;   // global stage counter of this CTA
+  for (int kc0 = k_begin; kc0 < k_end; kc0 += kGemvAChunk) {
+    const int kc1 = min(k_end, kc0 + kGemvAChunk);
+    const int padded = ((kc1 - kc0 + kGemvStageRows - 1) / kGemvStageRows) * kGemvStageRows;
+    __syncthreads();                                          // previous chunk of A fully consumed
+    for (int i = tid; i < MT * padded; i += kGemvThreads) {
+      const int m = i / padded, kk = i - m * padded;
+      const int row = m0 + m, kidx = kc0 + kk;
+      a_smem[m * kGemvAChunk + kk] = (row < p.m && kidx < kc1) ? p.a[size_t(row) * p.lda + kidx] : __float2half(0.f);
+    }
+    __syncthreads();
+    for (int kk0 = 0; kk0 < padded; kk0 += kGemvStageRows, ++stage_index) {
+      const int slot = stage_index % kGemvStages;
+      uint8_t* stage = stages + slot * GemvSmem::kStageBytes;
+      if constexpr (TMA) {
+        const uint32_t phase = uint32_t(stage_index / kGemvStages) & 1u;
+        if (healthy) healthy = mbar_wait(&full[slot], phase, kStatusTmaTimeout);
+        if (healthy) gemv_consume_stage<WT, MT>(stage, a_smem, kGemvAChunk, kk0, s, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[slot]);
+        if (tid == 0 && issued < n_stages_total && healthy) {
+          // refill this slot with the tile kGemvStages ahead once every warp has released it
+          healthy = mbar_wait(&empty[slot], phase, kStatusPipeTimeout);
+          if (healthy) {
+            mbar_expect_tx(&full[slot], GemvSmem::kStageBytes);
+            tma_load_2d(stage, &w_map, n0, k_begin + issued * kGemvStageRows, &full[slot]);
+            ++issued;
+          }
+        }
+      } else {
+        // Tiles filled by guarded loads (any alignment, any pitch); zero outside the matrix.
+        __syncthreads();
+        const WT* w = static_cast<const WT*>(p.w);
+        for (int i = tid; i < kGemvStageRows * BN; i += kGemvThreads) {
+          const int r = i / BN, c = i - r * BN;
+          const int kidx = kc0 + kk0 + r, col = n0 + c;
+          WT v = WT(0);
+          if (kidx < kc1 && col < p.n) v = w[size_t(kidx) * p.ldw + col];
+          reinterpret_cast<WT*>(stages)[r * BN + c] = v;
+        }
+        __syncthreads();
+        gemv_consume_stage<WT, MT>(stages, a_smem, kGemvAChunk, kk0, s, acc);
+      }
+    }
+  }
+  pdl_launch_dependents();
+
+  // 4 row-lanes of a warp -> lanes 0..7, then the 8 warps in fixed order.
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int j = 0; j < C; ++j) {
+      float v = acc[m][j];
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 16);
+      acc[m][j] = v;
+    }
+  if (lane < 8) {
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+      for (int j = 0; j < C; ++j) red[(warp * MT + m) * 128 + lane * C + j] = acc[m][j];
+  }
+  __syncthreads();
+  for (int i = tid; i < MT * BN; i += kGemvThreads) {
+    const int m = i / BN, c = i - m * BN;
+    float v = 0.f;
+#pragma unroll
+    for (int w8 = 0; w8 < 8; ++w8) v += red[(w8 * MT + m) * 128 + c];
+    part[m * 128 + c] = v;
+  }
+  if (splits > 1) cluster.sync(); else __syncthreads();
+  const int cols_per_rank = BN / splits;                       // splits is 1, 2, 4 or 8
+  for (int i = tid; i < MT * cols_per_rank; i += kGemvThreads) {
+    const int m = i / cols_per_rank, c = rank * cols_per_rank + (i - m * cols_per_rank);
+    float v = 0.f;
+    if (splits > 1) {
+      for (int r = 0; r < splits; ++r) v += cluster.map_shared_rank(part, r)[m * 128 + c];
+    } else v = part[m * 128 + c];
+    const int row = m0 + m, col = n0 + c;
+    if (row < p.m && col < p.n && healthy) gemv_store(p, row, col, v);
+  }
+  if (splits > 1) cluster.sync();                              // peers may still be reading `part`
+}
+
+}  // namespace tib

@@ -1,0 +1,254 @@
+// The single device translation unit of libtinyinfer_backend.so: every sm_100a kernel of the
+// INT8-weight decode path plus the host functions that configure and enqueue them
+// (declared in launch.hpp).
+#include <cuda.h>
+
+#include <algorithm>
+#include <cstring>
+#include <mutex>
+
+#include "launch.hpp"
+
+namespace tib { __device__ unsigned int g_device_status = 0; }
+#define TIB_STATUS_DEFINED
+#include "attention.cuh"
+#include "common.cuh"
+#include "elementwise.cuh"
+#include "gemm_simt.cuh"
+#include "model_glue.cuh"
+
+namespace tib {
+namespace {
+
+// ---------------------------------------------------------------- generic launch helper
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, const LaunchOpts& o,
+                   int cluster_y, Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = o.stream;
+  cudaLaunchAttribute attrs[2]; unsigned n = 0;
+  if (cluster_y > 1) {
+    attrs[n].id = cudaLaunchAttributeClusterDimension;
+    attrs[n].val.clusterDim.x = 1; attrs[n].val.clusterDim.y = unsigned(cluster_y); attrs[n].val.clusterDim.z = 1; ++n;
+  }
+  if (o.pdl) {
+    attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[n].val.programmaticStreamSerializationAllowed = 1; ++n;
+  }
+  cfg.attrs = attrs; cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+
+// ---------------------------------------------------------------- tensor maps
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr; cudaDriverEntryPointQueryResult q{};
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D map over a row-major [rows, cols] matrix with `pitch` elements per row; box = (box_cols, box_rows).
+bool make_map_2d(CUtensorMap* map, const void* base, bool int8, uint64_t rows, uint64_t cols, uint64_t pitch,
+                 uint32_t box_cols, uint32_t box_rows) {
+  const uint64_t esize = int8 ? 1 : 2;
+  if (!encode_tiled() || reinterpret_cast<uintptr_t>(base) % 16 || (pitch * esize) % 16 || pitch * esize >= (1ull << 40) ||
+      rows == 0 || cols == 0 || rows > 0xffffffffull || cols > 0xffffffffull)
+    return false;
+  const cuuint64_t dims[2] = {cols, rows}, strides[1] = {pitch * esize};
+  const cuuint32_t box[2] = {box_cols, box_rows}, estr[2] = {1, 1};
+  return encode_tiled()(map, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename K>
+cudaError_t allow_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+}
+
+int sm_count() {
+  static int n = [] { int dev = 0, v = 148; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); return v; }();
+  return n;
+}
+
+template <typename WT, int MT, bool TMA>
+cudaError_t launch_gemv(const CUtensorMap& map, const GemvArgs& args, dim3 grid, const LaunchOpts& o) {
+  static cudaError_t once = allow_smem(gemv_kernel<WT, MT, TMA>, GemvSmem::kBytes);
+  if (once != cudaSuccess) return once;
+  return launch(gemv_kernel<WT, MT, TMA>, grid, dim3(kGemvThreads), GemvSmem::kBytes, o, int(grid.y), map, args);
+}
+template <typename WT, bool TMA>
+cudaError_t launch_gemv_mt(int mt, const CUtensorMap& map, const GemvArgs& args, dim3 grid, const LaunchOpts& o) {
+  switch (mt) {
+    case 1: return launch_gemv<WT, 1, TMA>(map, args, grid, o);
+    case 2: return launch_gemv<WT, 2, TMA>(map, args, grid, o);
+    default: return launch_gemv<WT, 4, TMA>(map, args, grid, o);
+  }
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- GEMM
+cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
+  GemvArgs a{};
+  a.a = static_cast<const __half*>(c.a); a.w = c.w; a.scales = c.scales; a.bias = static_cast<const __half*>(c.bias);
+  a.out = c.out; a.residual = static_cast<const __half*>(c.residual);
+  a.lda = c.lda; a.ldo = c.ldo; a.ldw = c.ldw; a.m = c.m; a.n = c.n; a.k = c.k;
+  a.out_fp32 = c.out_fp32; a.gelu = c.gelu;
+  const int bn = c.w_int8 ? 128 : 64;
+  const int mt = c.m >= 3 ? 4 : c.m;
+  const int slabs = (c.n + bn - 1) / bn, m_tiles = (c.m + mt - 1) / mt;
+  // Split K over a cluster until the grid covers the SMs (or a CTA would own less than one stage).
+  int splits = 1;
+  while (splits < 8 && slabs * m_tiles * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= kGemvStageRows) splits *= 2;
+  int chunk = (c.k + splits - 1) / splits;
+  chunk = (chunk + kGemvStageRows - 1) / kGemvStageRows * kGemvStageRows;
+  a.k_chunk = chunk;
+  CUtensorMap map; std::memset(&map, 0, sizeof map);
+  const bool tma = make_map_2d(&map, c.w, c.w_int8, uint64_t(c.k), uint64_t(c.n), uint64_t(c.ldw),
+                               uint32_t(bn), uint32_t(kGemvStageRows));
+  const dim3 grid(slabs, splits, m_tiles);
+  if (c.w_int8) return tma ? launch_gemv_mt<int8_t, true>(mt, map, a, grid, o) : launch_gemv_mt<int8_t, false>(mt, map, a, grid, o);
+  return tma ? launch_gemv_mt<__half, true>(mt, map, a, grid, o) : launch_gemv_mt<__half, false>(mt, map, a, grid, o);
+}
+
+cudaError_t sgemm(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
+  sgemm_kernel<<<dim3((n + 15) / 16, (m + 15) / 16), 256, 0, stream>>>(a, b, c, m, n, k);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- attention
+cudaError_t attention_packed(const void* q, const void* k, const void* v, void* y, const int32_t* ql, const int32_t* kl,
+                             const int32_t* off, int batch, int heads, int q_len, int kv_len, int d, bool causal,
+                             const LaunchOpts& o) {
+  AttnArgs p{};
+  p.q = static_cast<const __half*>(q); p.out = static_cast<__half*>(y);
+  p.q_sb = (long long)heads * q_len * d; p.q_sh = (long long)q_len * d; p.q_si = d;
+  p.o_sb = p.q_sb; p.o_sh = p.q_sh; p.o_si = d;
+  p.row_start = nullptr;
+  p.q_lengths = ql; p.kv_lengths = kl; p.offsets = off;
+  p.batch = batch; p.heads = heads; p.q_len = q_len; p.kv_len = kv_len; p.causal = causal;
+  KvPacked kv{static_cast<const __half*>(k), static_cast<const __half*>(v), heads, kv_len, d};
+  const dim3 grid((q_len + kAttnTileQ - 1) / kAttnTileQ, heads, batch);
+  if (d == 64) return launch(attn_tile_kernel<64, KvPacked>, grid, dim3(256), 0, o, 1, p, kv);
+  if (d == 128) return launch(attn_tile_kernel<128, KvPacked>, grid, dim3(256), 0, o, 1, p, kv);
+  return cudaErrorInvalidValue;
+}
+
+static KvPaged paged(const PagedKv& kv) {
+  return KvPaged{static_cast<const __half*>(kv.k_pool), static_cast<const __half*>(kv.v_pool), kv.table, kv.slots,
+                 kv.table_pitch, kv.layers, kv.layer, kv.heads, kv.head_dim};
+}
+
+cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start, const int32_t* ql, const int32_t* kl,
+                            const int32_t* off, int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& o) {
+  if (kv.head_dim != 64) return cudaErrorInvalidValue;
+  const int hidden = kv.heads * kv.head_dim;
+  AttnArgs p{};
+  p.q = static_cast<const __half*>(qkv); p.out = static_cast<__half*>(out);
+  p.q_sb = 0; p.q_sh = kv.head_dim; p.q_si = 3LL * hidden;
+  p.o_sb = 0; p.o_sh = kv.head_dim; p.o_si = hidden;
+  p.row_start = row_start;
+  p.q_lengths = ql; p.kv_lengths = kl; p.offsets = off;
+  p.batch = batch; p.heads = kv.heads; p.q_len = max_q; p.kv_len = max_kv; p.causal = 1;
+  const dim3 grid((max_q + kAttnTileQ - 1) / kAttnTileQ, kv.heads, batch);
+  return launch(attn_tile_kernel<64, KvPaged>, grid, dim3(256), 0, o, 1, p, paged(kv));
+}
+
+int decode_chunks(int max_kv, int chunk) { return std::max(1, (max_kv + chunk - 1) / chunk); }
+
+cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kl, int batch, int max_kv, int chunk,
+                                   float* scratch_acc, float* scratch_ml, const PagedKv& kv, const LaunchOpts& o) {
+  if (kv.head_dim != 64) return cudaErrorInvalidValue;
+  const int hidden = kv.heads * kv.head_dim;
+  DecodeArgs p{};
+  p.q = static_cast<const __half*>(qkv); p.q_sb = 3LL * hidden; p.q_sh = kv.head_dim;
+  p.out = static_cast<__half*>(out); p.o_sb = hidden; p.o_sh = kv.head_dim;
+  p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml;
+  p.batch = batch; p.heads = kv.heads; p.chunk = chunk; p.chunks = decode_chunks(max_kv, chunk);
+  cudaError_t st = launch(attn_decode_kernel<64, KvPaged>, dim3(p.chunks, kv.heads, batch), dim3(kDecodeWarps * 32), 0, o, 1, p, paged(kv));
+  if (st != cudaSuccess || p.chunks == 1) return st;
+  return launch(attn_combine_kernel<64>, dim3(kv.heads, batch), dim3(64), 0, o, 1, p);
+}
+
+cudaError_t attention_packed_decode(const void* q, const void* k, const void* v, void* y, const int32_t* kl, int batch,
+                                    int heads, int kv_len, int chunk, float* scratch_acc, float* scratch_ml,
+                                    const LaunchOpts& o) {
+  DecodeArgs p{};
+  p.q = static_cast<const __half*>(q); p.q_sb = 64LL * heads; p.q_sh = 64;
+  p.out = static_cast<__half*>(y); p.o_sb = 64LL * heads; p.o_sh = 64;
+  p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml;
+  p.batch = batch; p.heads = heads; p.chunk = chunk; p.chunks = decode_chunks(kv_len, chunk);
+  KvPacked kv{static_cast<const __half*>(k), static_cast<const __half*>(v), heads, kv_len, 64};
+  cudaError_t st = launch(attn_decode_kernel<64, KvPacked>, dim3(p.chunks, heads, batch), dim3(kDecodeWarps * 32), 0, o, 1, p, kv);
+  if (st != cudaSuccess || p.chunks == 1) return st;
+  return launch(attn_combine_kernel<64>, dim3(heads, batch), dim3(64), 0, o, 1, p);
+}
+
+// ---------------------------------------------------------------- elementwise / glue
+cudaError_t layernorm(const void* x, const int32_t* row_index, const void* g, const void* b, void* y, int rows, int cols,
+                      float eps, const LaunchOpts& o) {
+  return launch(layernorm_kernel, dim3((rows + 3) / 4), dim3(128), 0, o, 1, static_cast<const __half*>(x), row_index,
+                static_cast<const __half*>(g), static_cast<const __half*>(b), static_cast<__half*>(y), rows, cols, eps);
+}
+cudaError_t gelu(const void* x, void* y, long long count, cudaStream_t stream) {
+  const int vec = (reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) ? 1 : 0;
+  const long long work = vec ? (count + 7) / 8 : count;
+  const int blocks = int(std::min<long long>((work + 255) / 256, 148LL * 16));
+  gelu_kernel<<<std::max(blocks, 1), 256, 0, stream>>>(static_cast<const __half*>(x), static_cast<__half*>(y), count, vec);
+  return cudaGetLastError();
+}
+cudaError_t softmax(const void* x, void* y, int rows, int cols, cudaStream_t stream) {
+  softmax_kernel<<<(rows + 3) / 4, 128, 0, stream>>>(static_cast<const __half*>(x), static_cast<__half*>(y), rows, cols);
+  return cudaGetLastError();
+}
+cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const void* wte, const void* wpe, void* x, int rows,
+                  int hidden, const LaunchOpts& o) {
+  const long long work = (long long)rows * (hidden / 8);
+  const int blocks = int(std::min<long long>((work + 255) / 256, 148LL * 8));
+  return launch(embed_kernel, dim3(std::max(blocks, 1)), dim3(256), 0, o, 1, ids, row_pos, static_cast<const __half*>(wte),
+                static_cast<const __half*>(wpe), static_cast<__half*>(x), rows, hidden);
+}
+cudaError_t kv_scatter(const void* qkv, const int32_t* row_req, const int32_t* row_pos, int rows, int hidden,
+                       const PagedKv& kv, const LaunchOpts& o) {
+  const long long work = (long long)rows * (hidden / 8);
+  const int blocks = int(std::min<long long>((work + 255) / 256, 148LL * 8));
+  return launch(kv_scatter_kernel, dim3(std::max(blocks, 1)), dim3(256), 0, o, 1, static_cast<const __half*>(qkv), row_req,
+                row_pos, paged(kv), static_cast<__half*>(kv.k_pool), static_cast<__half*>(kv.v_pool), rows, hidden);
+}
+cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out, int32_t* feedback,
+                   const LaunchOpts& o) {
+  return launch(argmax_kernel, dim3(rows), dim3(256), 0, o, 1, logits, pitch, cols, out, feedback);
+}
+
+cudaError_t nll_rows(const float* logits, long long pitch, int rows, int cols, const int32_t* tokens, const uint8_t* mask,
+                     double* loss, int first_position, cudaStream_t stream) {
+  nll_kernel<<<rows, 256, 0, stream>>>(logits, pitch, cols, tokens, mask, loss, first_position);
+  return cudaGetLastError();
+}
+cudaError_t sum_f64(const double* values, double* out, int length, cudaStream_t stream) {
+  sum_f64_kernel<<<1, 256, 0, stream>>>(values, out, length);
+  return cudaGetLastError();
+}
+
+cudaError_t device_status_address(unsigned int** address) {
+  return cudaGetSymbolAddress(reinterpret_cast<void**>(address), g_device_status);
+}
+
+cudaError_t read_device_status(cudaStream_t stream, unsigned int* status) {
+  cudaError_t st = cudaStreamSynchronize(stream);
+  if (st != cudaSuccess) return st;
+  st = cudaMemcpyFromSymbol(status, g_device_status, sizeof(unsigned int));
+  if (st != cudaSuccess || *status == 0) return st;
+  const unsigned int zero = 0;
+  return cudaMemcpyToSymbol(g_device_status, &zero, sizeof zero);
+}
+
+}  // namespace tib

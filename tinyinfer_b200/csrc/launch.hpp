@@ -1,0 +1,89 @@
+// Host-side launch interface of the kernel translation unit (kernels.cu).  Plain C++: no device
+// code, usable from the C-ABI front ends (backend_api.cpp, llm_runtime.cpp).  Every function
+// only enqueues work on `stream` and returns the launch status.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#if defined(__GNUC__)
+#define TIB_EXPORT __attribute__((visibility("default")))
+#else
+#define TIB_EXPORT
+#endif
+
+namespace tib {
+
+struct LaunchOpts {
+  cudaStream_t stream = nullptr;
+  bool pdl = false;              // programmatic dependent launch: prologue may overlap the previous kernel
+};
+
+// out[M,N] = a[M,K] . W[K,N] + bias, fused epilogue; W int8 (+scales) or fp16.
+struct GemmCall {
+  const void* a = nullptr; int lda = 0;                 // fp16 [M,K]
+  const void* w = nullptr; long long ldw = 0;           // [K,N], pitch in elements
+  bool w_int8 = true;
+  const float* scales = nullptr;
+  const void* bias = nullptr;                           // fp16 [N] or null
+  void* out = nullptr; int ldo = 0; bool out_fp32 = false;
+  const void* residual = nullptr;                       // fp16 [M,N] pitch ldo, or null
+  bool gelu = false;
+  int m = 0, n = 0, k = 0;
+};
+TIB_EXPORT cudaError_t gemm(const GemmCall& call, const LaunchOpts& opts);
+
+TIB_EXPORT cudaError_t sgemm(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream);
+
+// Packed-tensor attention of the operator ABI: q[B,H,Q,D], k/v[B,H,K,D].
+TIB_EXPORT cudaError_t attention_packed(const void* q, const void* k, const void* v, void* y,
+                                        const int32_t* q_lengths, const int32_t* kv_lengths, const int32_t* offsets,
+                                        int batch, int heads, int q_len, int kv_len, int head_dim, bool causal,
+                                        const LaunchOpts& opts);
+
+// Paged KV pool of the model runtime; see attention.cuh for the page layout.
+struct PagedKv {
+  void* k_pool = nullptr; void* v_pool = nullptr;
+  const int32_t* table = nullptr;     // [slots][table_pitch]
+  const int32_t* slots = nullptr;     // [batch]
+  int table_pitch = 0, layers = 0, layer = 0, heads = 0, head_dim = 0;
+};
+// Prefill / mixed lengths: request b owns rows row_start[b] .. row_start[b]+q_lengths[b]-1 of
+// qkv[rows, 3*hidden]; attention output goes to out[rows, hidden] (heads merged).
+TIB_EXPORT cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start,
+                                       const int32_t* q_lengths, const int32_t* kv_lengths, const int32_t* offsets,
+                                       int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& opts);
+// Decode: one row per request.  scratch_acc: fp32 [batch*heads*chunks*D], scratch_ml: fp32
+// [batch*heads*chunks*2]; chunks = ceil(max_kv / chunk).
+TIB_EXPORT cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kv_lengths,
+                                              int batch, int max_kv, int chunk, float* scratch_acc, float* scratch_ml,
+                                              const PagedKv& kv, const LaunchOpts& opts);
+TIB_EXPORT int decode_chunks(int max_kv, int chunk);
+// Same decode attention over packed k/v[B,H,K,D] with q[B,H,1,D] (additive operator export).
+TIB_EXPORT cudaError_t attention_packed_decode(const void* q, const void* k, const void* v, void* y,
+                                               const int32_t* kv_lengths, int batch, int heads, int kv_len, int chunk,
+                                               float* scratch_acc, float* scratch_ml, const LaunchOpts& opts);
+
+// y[r,:] = LayerNorm(x[row_index ? row_index[r] : r, :]).
+TIB_EXPORT cudaError_t layernorm(const void* x, const int32_t* row_index, const void* gamma, const void* beta, void* y,
+                                 int rows, int cols, float eps, const LaunchOpts& opts);
+TIB_EXPORT cudaError_t gelu(const void* x, void* y, long long count, cudaStream_t stream);
+TIB_EXPORT cudaError_t softmax(const void* x, void* y, int rows, int cols, cudaStream_t stream);
+
+TIB_EXPORT cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const void* wte, const void* wpe,
+                             void* x, int rows, int hidden, const LaunchOpts& opts);
+TIB_EXPORT cudaError_t kv_scatter(const void* qkv, const int32_t* row_req, const int32_t* row_pos,
+                                  int rows, int hidden, const PagedKv& kv, const LaunchOpts& opts);
+TIB_EXPORT cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out,
+                              int32_t* feedback, const LaunchOpts& opts);
+
+TIB_EXPORT cudaError_t nll_rows(const float* logits, long long pitch, int rows, int cols, const int32_t* tokens,
+                                const uint8_t* mask, double* loss, int first_position, cudaStream_t stream);
+TIB_EXPORT cudaError_t sum_f64(const double* values, double* out, int length, cudaStream_t stream);
+
+// Reads and clears the device status word set by a kernel whose bounded wait ran out
+// (0 = healthy).  Synchronises `stream` first.
+TIB_EXPORT cudaError_t read_device_status(cudaStream_t stream, unsigned int* status);
+// Device address of that status word on the current device (for an asynchronous copy).
+TIB_EXPORT cudaError_t device_status_address(unsigned int** address);
+
+}  // namespace tib

@@ -1,0 +1,484 @@
+// Model C ABI v1 (include/tinyinfer_llm.h): GPT-2 forward / greedy / scoring on one GPU.
+//
+// Same observable behaviour as the reference runtime (llm/src/runtime.cu:97-211) -- argument
+// validation before anything is enqueued, transactional slot lengths, poison on execution
+// failure, exactly-N greedy tokens with the last one not appended, logical-operation trace
+// counters -- on a different execution plan:
+//   * rows are packed (a ragged prefill carries no padding rows);
+//   * the KV history lives in a paged pool (32 positions per page) addressed through a per-slot
+//     page table and is read in place by the attention kernels (the reference copies every
+//     request's whole history into a packed buffer for every layer of every step);
+//   * bias, GELU and the residual adds are epilogues of the weight-streaming GEMM, K/V are
+//     written to their pages by one small kernel, heads are merged by the attention store;
+//   * all per-call metadata reaches the GPU in one pinned-memory copy.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "artifact.hpp"
+#include "launch.hpp"
+#include "tinyinfer_b200_ext.h"
+#include "tinyinfer_backend_v2.h"
+#include "tinyinfer_llm.h"
+
+namespace {
+
+using tib::InvalidInput;
+struct GpuFailure : std::runtime_error { using std::runtime_error::runtime_error; };
+
+thread_local std::string g_error;
+
+void ck(cudaError_t st) { if (st != cudaSuccess) throw GpuFailure(cudaGetErrorString(st)); }
+
+struct DeviceGuard {
+  int before = -1; bool switched = false;
+  explicit DeviceGuard(int device) {
+    ck(cudaGetDevice(&before));
+    if (before != device) { ck(cudaSetDevice(device)); switched = true; }
+  }
+  ~DeviceGuard() { if (switched) cudaSetDevice(before); }
+};
+
+using Clock = std::chrono::steady_clock;
+double elapsed_ms(Clock::time_point from) { return std::chrono::duration<double, std::milli>(Clock::now() - from).count(); }
+
+constexpr int kScoreRows = 16;       // vocabulary rows scored per lm_head pass (reference SCORE_ROWS)
+constexpr int kDecodeChunk = 128;    // keys per decode-attention CTA
+
+struct Linear {
+  const void* w = nullptr; const float* scales = nullptr; const void* bias = nullptr;
+  int k = 0, n = 0; long long ldw = 0;
+};
+struct Block { const void *ln1_g, *ln1_b, *ln2_g, *ln2_b; Linear qkv, proj, fc, proj2; };
+
+}  // namespace
+
+struct ti_llm_model {
+  ti_llm_options opt{};
+  tib::ModelShape shape;
+  bool int8 = false, poisoned = false;
+  cudaStream_t stream = nullptr;
+  ti_llm_trace trace{};
+  std::vector<void*> owned;                      // cudaMalloc'ed
+  std::vector<void*> pinned;                     // cudaMallocHost'ed
+  // weights
+  const void *wte = nullptr, *wpe = nullptr, *lnf_g = nullptr, *lnf_b = nullptr;
+  std::vector<Block> blocks;
+  Linear head; int vpitch = 0;
+  // activations
+  void *x = nullptr, *res = nullptr, *norm = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr, *last = nullptr;
+  float* logits = nullptr;
+  float *att_acc = nullptr, *att_ml = nullptr;
+  // KV pool
+  void *k_pool = nullptr, *v_pool = nullptr;
+  int pages_per_slot = 0;
+  std::vector<int32_t> table, page_count, free_pages, lengths;
+  int32_t* d_table = nullptr; bool table_dirty = true;
+  // metadata staging: [ids | row_req | row_pos] (rows each) then 6 per-request arrays
+  int32_t *h_meta = nullptr, *d_meta = nullptr; size_t max_rows = 0;
+  int32_t *d_next = nullptr, *h_next = nullptr;
+  unsigned int *h_status = nullptr, *d_status_addr = nullptr;
+  // scoring
+  int32_t* d_score_tokens = nullptr; uint8_t* d_score_mask = nullptr; double *d_loss = nullptr, *d_loss_sum = nullptr;
+
+  template <class T> T* dev(size_t count) { void* p = nullptr; ck(cudaMalloc(&p, std::max<size_t>(count, 1) * sizeof(T))); owned.push_back(p); return static_cast<T*>(p); }
+  template <class T> T* host(size_t count) { void* p = nullptr; ck(cudaMallocHost(&p, std::max<size_t>(count, 1) * sizeof(T))); pinned.push_back(p); return static_cast<T*>(p); }
+
+  ~ti_llm_model() {
+    int before = -1;
+    cudaGetDevice(&before);
+    cudaSetDevice(opt.device);
+    if (stream) cudaStreamSynchronize(stream);
+    for (void* p : owned) cudaFree(p);
+    for (void* p : pinned) cudaFreeHost(p);
+    if (stream) cudaStreamDestroy(stream);
+    if (before >= 0) cudaSetDevice(before);
+  }
+
+  void ensure_usable() const { if (poisoned) throw GpuFailure("model poisoned by earlier execution failure; destroy/recreate required"); }
+
+  // ------------------------------------------------------------ load
+  void load(const tib::Artifact& art) {
+    shape = art.shape; int8 = art.precision == "int8";
+    const int H = shape.hidden, V = shape.vocab;
+    const char* linear_dtype = int8 ? "int8" : "float16";
+    uint8_t* blob = dev<uint8_t>(art.blob.size());
+    ck(cudaMemcpyAsync(blob, art.blob.data(), art.blob.size(), cudaMemcpyHostToDevice, stream));
+    size_t seen = 0;
+    auto at = [&](const std::string& name, std::vector<int> dims, const char* dtype) -> const void* {
+      ++seen; return blob + art.need(name, dims, dtype).offset;
+    };
+    auto linear = [&](const std::string& name, int k, int n, bool bias) {
+      Linear l; l.k = k; l.n = n; l.ldw = n;
+      l.w = at(name + ".weight", {k, n}, linear_dtype);
+      if (bias) l.bias = at(name + ".bias", {n}, "float16");
+      if (int8) l.scales = static_cast<const float*>(at(name + ".weight.scales", {n}, "float32"));
+      return l;
+    };
+    wte = at("transformer.wte.weight", {V, H}, "float16");
+    wpe = at("transformer.wpe.weight", {shape.positions, H}, "float16");
+    lnf_g = at("transformer.ln_f.weight", {H}, "float16");
+    lnf_b = at("transformer.ln_f.bias", {H}, "float16");
+    blocks.resize(size_t(shape.layers));
+    for (int l = 0; l < shape.layers; ++l) {
+      const std::string p = "transformer.h." + std::to_string(l) + ".";
+      Block& b = blocks[size_t(l)];
+      b.ln1_g = at(p + "ln_1.weight", {H}, "float16"); b.ln1_b = at(p + "ln_1.bias", {H}, "float16");
+      b.ln2_g = at(p + "ln_2.weight", {H}, "float16"); b.ln2_b = at(p + "ln_2.bias", {H}, "float16");
+      b.qkv = linear(p + "attn.c_attn", H, 3 * H, true);
+      b.proj = linear(p + "attn.c_proj", H, H, true);
+      b.fc = linear(p + "mlp.c_fc", H, 4 * H, true);
+      b.proj2 = linear(p + "mlp.c_proj", 4 * H, H, true);
+    }
+    head = linear("lm_head", H, V, false);
+    if (seen != art.tensors.size()) throw InvalidInput("unexpected tensor(s) in artifact");
+    // The vocabulary projection is re-pitched so its rows start on 128-byte boundaries and can be
+    // streamed by TMA; the pad columns are zero weights that are never stored.
+    vpitch = (V + 127) / 128 * 128;
+    const size_t esize = int8 ? 1 : 2;
+    uint8_t* padded = dev<uint8_t>(size_t(H) * vpitch * esize);
+    ck(cudaMemsetAsync(padded, 0, size_t(H) * vpitch * esize, stream));
+    ck(cudaMemcpy2DAsync(padded, size_t(vpitch) * esize, head.w, size_t(V) * esize, size_t(V) * esize, size_t(H),
+                         cudaMemcpyDeviceToDevice, stream));
+    head.w = padded; head.ldw = vpitch;
+
+    max_rows = size_t(opt.max_batch) * opt.capacity;
+    const size_t r = max_rows;
+    x = dev<uint16_t>(r * H); res = dev<uint16_t>(r * H); norm = dev<uint16_t>(r * H); attn = dev<uint16_t>(r * H);
+    qkv = dev<uint16_t>(r * 3 * H); act = dev<uint16_t>(r * 4 * H);
+    last = dev<uint16_t>(size_t(std::max(opt.max_batch, kScoreRows)) * H);
+    logits = dev<float>(size_t(std::max(opt.max_batch, kScoreRows)) * vpitch);
+    const int chunks = tib::decode_chunks(opt.capacity, kDecodeChunk);
+    att_acc = dev<float>(size_t(opt.max_batch) * shape.heads * chunks * 64);
+    att_ml = dev<float>(size_t(opt.max_batch) * shape.heads * chunks * 2);
+
+    pages_per_slot = (opt.capacity + tib_page_tokens() - 1) / tib_page_tokens();
+    const int slots = opt.cache_slots + 1;                       // +1: private slot of score_window
+    const size_t pages = size_t(slots) * pages_per_slot;
+    const size_t page_halfs = size_t(shape.layers) * shape.heads * tib_page_tokens() * 64;
+    k_pool = dev<uint16_t>(pages * page_halfs); v_pool = dev<uint16_t>(pages * page_halfs);
+    table.assign(size_t(slots) * pages_per_slot, 0); page_count.assign(size_t(slots), 0); lengths.assign(size_t(slots), 0);
+    free_pages.resize(pages);
+    for (size_t i = 0; i < pages; ++i) free_pages[i] = int32_t(pages - 1 - i);
+    d_table = dev<int32_t>(table.size());
+
+    const size_t meta = 3 * r + 6 * size_t(opt.max_batch);
+    h_meta = host<int32_t>(meta); d_meta = dev<int32_t>(meta);
+    d_next = dev<int32_t>(size_t(opt.max_batch)); h_next = host<int32_t>(size_t(opt.max_batch));
+    h_status = host<unsigned int>(1); *h_status = 0;
+    d_score_tokens = dev<int32_t>(size_t(opt.capacity)); d_score_mask = dev<uint8_t>(size_t(opt.capacity));
+    d_loss = dev<double>(size_t(opt.capacity)); d_loss_sum = dev<double>(1);
+    ck(cudaStreamSynchronize(stream));
+  }
+  static int tib_page_tokens() { return 32; }
+
+  // ------------------------------------------------------------ paging
+  void reserve(int slot, int new_length) {
+    const int need = (new_length + tib_page_tokens() - 1) / tib_page_tokens();
+    while (page_count[size_t(slot)] < need) {
+      if (free_pages.empty()) throw std::runtime_error("KV page pool exhausted");
+      table[size_t(slot) * pages_per_slot + page_count[size_t(slot)]++] = free_pages.back();
+      free_pages.pop_back();
+      table_dirty = true;
+    }
+  }
+  void release(int slot) {
+    for (int i = page_count[size_t(slot)] - 1; i >= 0; --i) free_pages.push_back(table[size_t(slot) * pages_per_slot + i]);
+    page_count[size_t(slot)] = 0; lengths[size_t(slot)] = 0;
+  }
+
+  // ------------------------------------------------------------ one pass over the layers
+  void gemm(const void* a, const Linear& l, void* out, int rows, bool fp32, const void* residual, bool gelu) {
+    tib::GemmCall c;
+    c.a = a; c.lda = l.k; c.w = l.w; c.ldw = l.ldw; c.w_int8 = int8; c.scales = l.scales; c.bias = l.bias;
+    c.out = out; c.ldo = fp32 ? vpitch : l.n; c.out_fp32 = fp32; c.residual = residual; c.gelu = gelu;
+    c.m = rows; c.n = l.n; c.k = l.k;
+    tib::LaunchOpts o; o.stream = stream;
+    ++(int8 ? trace.gemm_int8 : trace.gemm_fp16);
+    ck(tib::gemm(c, o));
+  }
+
+  // slots/lens describe `batch` requests; tokens are packed request after request.
+  // Leaves LayerNorm_f of each request's last row in `last` (and of every row in `norm` when
+  // all_rows is set, for scoring).
+  void transform(const std::vector<int32_t>& ss, const std::vector<int32_t>& packed, const std::vector<int32_t>& lens, bool all_rows) {
+    const int batch = int(ss.size()), H = shape.hidden;
+    int rows = 0, max_q = 0, max_kv = 0;
+    for (int b = 0; b < batch; ++b) { rows += lens[size_t(b)]; max_q = std::max(max_q, lens[size_t(b)]); }
+    int32_t* ids = h_meta; int32_t* row_req = ids + rows; int32_t* row_pos = row_req + rows; int32_t* per = row_pos + rows;
+    int32_t *row_start = per, *qlens = per + batch, *offsets = per + 2 * batch, *kvlens = per + 3 * batch,
+            *slot_of = per + 4 * batch, *last_row = per + 5 * batch;
+    int r = 0;
+    for (int b = 0; b < batch; ++b) {
+      const int s = ss[size_t(b)], n = lens[size_t(b)], start = lengths[size_t(s)];
+      reserve(s, start + n);
+      row_start[b] = r; qlens[b] = n; offsets[b] = start; kvlens[b] = start + n; slot_of[b] = s; last_row[b] = r + n - 1;
+      max_kv = std::max(max_kv, start + n);
+      for (int t = 0; t < n; ++t, ++r) { ids[r] = packed[size_t(r)]; row_req[r] = b; row_pos[r] = start + t; }
+    }
+    if (table_dirty) { ck(cudaMemcpyAsync(d_table, table.data(), table.size() * sizeof(int32_t), cudaMemcpyHostToDevice, stream)); table_dirty = false; }
+    const size_t meta_count = size_t(3 * rows + 6 * batch);
+    ck(cudaMemcpyAsync(d_meta, h_meta, meta_count * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    const int32_t *d_ids = d_meta, *d_row_req = d_meta + rows, *d_row_pos = d_meta + 2 * rows, *d_per = d_meta + 3 * rows;
+    const int32_t *d_row_start = d_per, *d_qlens = d_per + batch, *d_offsets = d_per + 2 * batch, *d_kvlens = d_per + 3 * batch,
+                  *d_slots = d_per + 4 * batch, *d_last_row = d_per + 5 * batch;
+
+    tib::LaunchOpts o; o.stream = stream;
+    ++trace.forward_calls; ++trace.embedding;
+    ck(tib::embed(d_ids, d_row_pos, wte, wpe, x, rows, H, o));
+    tib::PagedKv kv; kv.k_pool = k_pool; kv.v_pool = v_pool; kv.table = d_table; kv.slots = d_slots;
+    kv.table_pitch = pages_per_slot; kv.layers = shape.layers; kv.heads = shape.heads; kv.head_dim = 64;
+    const bool decode = max_q == 1;
+    for (int l = 0; l < shape.layers; ++l) {
+      const Block& b = blocks[size_t(l)];
+      kv.layer = l;
+      ++trace.layernorm; ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, rows, H, 1e-5f, o));
+      gemm(norm, b.qkv, qkv, rows, false, nullptr, false);
+      ++trace.kv_scatter_gather; ck(tib::kv_scatter(qkv, d_row_req, d_row_pos, rows, H, kv, o));
+      ++trace.attention;
+      if (decode) ck(tib::attention_paged_decode(qkv, attn, d_kvlens, batch, max_kv, kDecodeChunk, att_acc, att_ml, kv, o));
+      else ck(tib::attention_paged(qkv, attn, d_row_start, d_qlens, d_kvlens, d_offsets, batch, max_q, max_kv, kv, o));
+      ++trace.residual; gemm(attn, b.proj, res, rows, false, x, false);            // res = x + proj(attn)
+      ++trace.layernorm; ck(tib::layernorm(res, nullptr, b.ln2_g, b.ln2_b, norm, rows, H, 1e-5f, o));
+      ++trace.gelu; gemm(norm, b.fc, act, rows, false, nullptr, true);              // act = gelu(fc(norm))
+      ++trace.residual; gemm(act, b.proj2, x, rows, false, res, false);             // x = res + proj2(act)
+    }
+    ++trace.layernorm;
+    if (all_rows) ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, norm, rows, H, 1e-5f, o));
+    else ck(tib::layernorm(x, d_last_row, lnf_g, lnf_b, last, batch, H, 1e-5f, o));
+  }
+
+  void finish() {
+    ck(cudaMemcpyAsync(h_status, d_status_addr, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
+    ck(cudaStreamSynchronize(stream));
+    if (*h_status) {
+      const unsigned int code = *h_status; *h_status = 0;
+      unsigned int ignored = 0; tib::read_device_status(stream, &ignored);
+      throw GpuFailure("device wait timed out (status " + std::to_string(code) + ")");
+    }
+  }
+
+  void forward(const int32_t* s, const int32_t* tokens, const int32_t* lens, int batch, int stride, float* out, int32_t* greedy,
+               bool internal = false) {
+    ensure_usable();
+    if (!s || !tokens || !lens || batch < 1 || batch > opt.max_batch || stride < 1 || stride > opt.capacity)
+      throw InvalidInput("invalid batch/host pointers/stride");
+    std::vector<int32_t> ss(s, s + batch), ll(lens, lens + batch), packed;
+    std::vector<char> used(size_t(opt.cache_slots) + 1, 0);
+    for (int b = 0; b < batch; ++b) {
+      const int slot = s[b], n = lens[b];
+      if (slot < 0 || slot >= opt.cache_slots + (internal ? 1 : 0) || used[size_t(slot)] || n < 1 || n > stride ||
+          lengths[size_t(slot)] + n > opt.capacity)
+        throw InvalidInput("duplicate/invalid slot, length or capacity");
+      used[size_t(slot)] = 1;
+      for (int t = 0; t < n; ++t) {
+        const int32_t id = tokens[size_t(b) * stride + t];
+        if (id < 0 || id >= shape.vocab) throw InvalidInput("token ID outside GPT-2 vocabulary");
+        packed.push_back(id);
+      }
+    }
+    transform(ss, packed, ll, false);
+    tib::LaunchOpts o; o.stream = stream;
+    if (out || greedy) {
+      ++trace.lm_head; gemm(last, head, logits, batch, true, nullptr, false);
+      if (out) ck(cudaMemcpy2DAsync(out, size_t(shape.vocab) * 4, logits, size_t(vpitch) * 4, size_t(shape.vocab) * 4, size_t(batch),
+                                    cudaMemcpyDeviceToHost, stream));
+      if (greedy) {
+        ++trace.argmax; ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_next, nullptr, o));
+        ck(cudaMemcpyAsync(h_next, d_next, size_t(batch) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+      }
+    }
+    finish();
+    if (greedy) std::memcpy(greedy, h_next, size_t(batch) * sizeof(int32_t));
+    for (int b = 0; b < batch; ++b) lengths[size_t(s[b])] += lens[b];
+  }
+};
+
+namespace {
+
+template <class F>
+int guarded(ti_llm_model* model, F&& body) {
+  g_error.clear();
+  try {
+    if (!model) throw InvalidInput("null model");
+    DeviceGuard device(model->opt.device);
+    model->ensure_usable();
+    body();
+    return TI_LLM_OK;
+  } catch (const InvalidInput& e) { g_error = e.what(); return TI_LLM_INVALID;
+  } catch (const tib::IoFailure& e) { g_error = e.what(); return TI_LLM_IO;
+  } catch (const GpuFailure& e) { if (model) model->poisoned = true; g_error = e.what(); return TI_LLM_CUDA;
+  } catch (const std::exception& e) { if (model) model->poisoned = true; g_error = e.what(); return TI_LLM_INTERNAL;
+  } catch (...) { if (model) model->poisoned = true; g_error = "unknown native failure"; return TI_LLM_INTERNAL; }
+}
+
+}  // namespace
+
+extern "C" {
+
+int ti_llm_abi_version(void) { return 1; }
+const char* ti_llm_last_error(void) { return g_error.c_str(); }
+
+int ti_llm_create(const char* path, const ti_llm_options* o, ti_llm_model** out) {
+  g_error.clear();
+  if (out) *out = nullptr;
+  try {
+    if (!path || !o || !out || o->struct_size != sizeof(ti_llm_options) || o->device < 0 || o->max_batch < 1 || o->max_batch > 64 ||
+        o->cache_slots < o->max_batch || o->cache_slots > 1024 || o->capacity < 2 || o->capacity > 1024 || o->gemm_config < 0 ||
+        o->gemm_config > 11 || o->attention_config < 0 || o->attention_config > 1)
+      throw InvalidInput("invalid options/ABI size");
+    if (ti_v2_abi_version() != 2) throw InvalidInput("v2 kernel ABI required");
+    tib::Artifact art(path);
+    if (o->capacity > art.shape.positions) throw InvalidInput("capacity exceeds the model's learned positions");
+    DeviceGuard device(o->device);
+    std::unique_ptr<ti_llm_model> model(new ti_llm_model);
+    model->opt = *o;
+    ck(cudaStreamCreateWithFlags(&model->stream, cudaStreamNonBlocking));
+    unsigned int cleared = 0;
+    ck(tib::read_device_status(model->stream, &cleared));
+    ck(tib::device_status_address(&model->d_status_addr));
+    model->load(art);
+    *out = model.release();
+    return TI_LLM_OK;
+  } catch (const InvalidInput& e) { g_error = e.what(); return TI_LLM_INVALID;
+  } catch (const tib::IoFailure& e) { g_error = e.what(); return TI_LLM_IO;
+  } catch (const GpuFailure& e) { g_error = e.what(); return TI_LLM_CUDA;
+  } catch (const std::exception& e) { g_error = e.what(); return TI_LLM_INTERNAL;
+  } catch (...) { g_error = "unknown create failure"; return TI_LLM_INTERNAL; }
+}
+
+// Host-only verification of an artifact (no CUDA call): same checks ti_llm_create performs
+// before it touches the GPU.  Declared in include/tinyinfer_b200_ext.h.
+int ti_b200_artifact_check(const char* path, int32_t* layers, int32_t* heads, int32_t* hidden, int32_t* int8_weights) {
+  g_error.clear();
+  try {
+    if (!path) throw InvalidInput("null manifest path");
+    tib::Artifact art(path);
+    if (layers) *layers = art.shape.layers;
+    if (heads) *heads = art.shape.heads;
+    if (hidden) *hidden = art.shape.hidden;
+    if (int8_weights) *int8_weights = art.precision == "int8";
+    return TI_LLM_OK;
+  } catch (const InvalidInput& e) { g_error = e.what(); return TI_LLM_INVALID;
+  } catch (const tib::IoFailure& e) { g_error = e.what(); return TI_LLM_IO;
+  } catch (const std::exception& e) { g_error = e.what(); return TI_LLM_INTERNAL; }
+}
+
+int ti_llm_destroy(ti_llm_model* model) {
+  g_error.clear();
+  if (!model) { g_error = "null model"; return TI_LLM_INVALID; }
+  delete model;
+  return TI_LLM_OK;
+}
+
+int ti_llm_reset(ti_llm_model* m, int32_t slot) {
+  return guarded(m, [&] {
+    if (slot < 0 || slot >= m->opt.cache_slots) throw InvalidInput("invalid public slot");
+    m->release(slot);
+  });
+}
+int ti_llm_lengths(ti_llm_model* m, int32_t* out, int32_t count) {
+  return guarded(m, [&] {
+    if (!out || count != m->opt.cache_slots) throw InvalidInput("wrong lengths output extent");
+    std::copy(m->lengths.begin(), m->lengths.begin() + count, out);
+  });
+}
+int ti_llm_get_trace(ti_llm_model* m, ti_llm_trace* out) {
+  return guarded(m, [&] { if (!out) throw InvalidInput("null trace output"); *out = m->trace; });
+}
+
+int ti_llm_forward_batch(ti_llm_model* m, const int32_t* slots, const int32_t* tokens, const int32_t* lengths, int32_t batch,
+                         int32_t stride, float* logits, int32_t* next) {
+  return guarded(m, [&] { m->forward(slots, tokens, lengths, batch, stride, logits, next); });
+}
+
+int ti_llm_greedy_batch(ti_llm_model* m, const int32_t* slots, const int32_t* prompts, const int32_t* prompt_lengths,
+                        const int32_t* requested, int32_t batch, int32_t stride, int32_t* output, int32_t out_stride,
+                        int32_t* output_lengths, double* ttft, double* total) {
+  return guarded(m, [&] {
+    if (!slots || !prompts || !prompt_lengths || !requested || !output || batch < 1 || batch > m->opt.max_batch || stride < 1 ||
+        stride > m->opt.capacity || out_stride < 1 || out_stride > m->opt.capacity)
+      throw InvalidInput("invalid greedy arguments");
+    std::vector<char> used(size_t(m->opt.cache_slots), 0);
+    for (int i = 0; i < batch; ++i) {
+      const int s = slots[i];
+      if (s < 0 || s >= m->opt.cache_slots || used[size_t(s)] || m->lengths[size_t(s)] || prompt_lengths[i] < 1 ||
+          prompt_lengths[i] > stride || requested[i] < 1 || requested[i] > out_stride ||
+          requested[i] + prompt_lengths[i] > m->opt.capacity)
+        throw InvalidInput("greedy needs empty distinct slots and bounded positive lengths");
+      used[size_t(s)] = 1;
+      for (int t = 0; t < prompt_lengths[i]; ++t) {
+        const int32_t id = prompts[size_t(i) * stride + t];
+        if (id < 0 || id >= m->shape.vocab) throw InvalidInput("invalid prompt token");
+      }
+    }
+    std::fill(output, output + size_t(batch) * out_stride, -1);
+    if (output_lengths) std::fill(output_lengths, output_lengths + batch, 0);
+    const auto start = Clock::now();
+    std::vector<int32_t> next(static_cast<size_t>(batch), 0), produced(static_cast<size_t>(batch), 1);
+    m->forward(slots, prompts, prompt_lengths, batch, stride, nullptr, next.data());
+    const double first = elapsed_ms(start);
+    for (int i = 0; i < batch; ++i) {
+      output[size_t(i) * out_stride] = next[size_t(i)];
+      if (ttft) ttft[i] = first;
+      if (total && requested[i] == 1) total[i] = first;
+    }
+    std::vector<int32_t> live_slots, live_ids, ones, owner, fresh;
+    for (;;) {
+      live_slots.clear(); live_ids.clear(); owner.clear();
+      for (int i = 0; i < batch; ++i)
+        if (produced[size_t(i)] < requested[i]) { live_slots.push_back(slots[i]); live_ids.push_back(next[size_t(i)]); owner.push_back(i); }
+      if (owner.empty()) break;
+      ones.assign(owner.size(), 1); fresh.resize(owner.size());
+      m->forward(live_slots.data(), live_ids.data(), ones.data(), int(owner.size()), 1, nullptr, fresh.data());
+      const double now = elapsed_ms(start);
+      for (size_t j = 0; j < owner.size(); ++j) {
+        const int i = owner[j];
+        next[size_t(i)] = fresh[j];
+        output[size_t(i) * out_stride + produced[size_t(i)]++] = fresh[j];
+        if (total && produced[size_t(i)] == requested[i]) total[i] = now;
+      }
+    }
+    if (output_lengths) for (int i = 0; i < batch; ++i) output_lengths[i] = produced[size_t(i)];
+  });
+}
+
+int ti_llm_score_window(ti_llm_model* m, const int32_t* tokens, const uint8_t* mask, int32_t length, double* nll, uint64_t* count,
+                        double* positions) {
+  return guarded(m, [&] {
+    if (!tokens || !mask || !nll || !count || length < 2 || length > m->opt.capacity || mask[0]) throw InvalidInput("invalid score window");
+    uint64_t targets = 0;
+    for (int i = 0; i < length; ++i) {
+      if (tokens[i] < 0 || tokens[i] >= m->shape.vocab || mask[i] > 1) throw InvalidInput("invalid score token/mask");
+      targets += mask[i];
+    }
+    if (!targets) throw InvalidInput("no shifted targets selected");
+    const int slot = m->opt.cache_slots, rows = length - 1, H = m->shape.hidden;
+    m->release(slot);
+    m->transform({slot}, std::vector<int32_t>(tokens, tokens + rows), {rows}, true);
+    ck(cudaMemcpyAsync(m->d_score_tokens, tokens, size_t(length) * sizeof(int32_t), cudaMemcpyHostToDevice, m->stream));
+    ck(cudaMemcpyAsync(m->d_score_mask, mask, size_t(length), cudaMemcpyHostToDevice, m->stream));
+    ck(cudaMemsetAsync(m->d_loss, 0, size_t(length) * sizeof(double), m->stream));
+    for (int row = 0; row < rows; row += kScoreRows) {
+      const int n = std::min(kScoreRows, rows - row);
+      ++m->trace.lm_head;
+      m->gemm(static_cast<const uint16_t*>(m->norm) + size_t(row) * H, m->head, m->logits, n, true, nullptr, false);
+      ++m->trace.nll;
+      ck(tib::nll_rows(m->logits, m->vpitch, n, m->shape.vocab, m->d_score_tokens, m->d_score_mask, m->d_loss, row + 1, m->stream));
+    }
+    ck(tib::sum_f64(m->d_loss, m->d_loss_sum, length, m->stream));
+    ck(cudaMemcpyAsync(nll, m->d_loss_sum, sizeof(double), cudaMemcpyDeviceToHost, m->stream));
+    if (positions) ck(cudaMemcpyAsync(positions, m->d_loss, size_t(length) * sizeof(double), cudaMemcpyDeviceToHost, m->stream));
+    m->finish();
+    m->release(slot);
+    if (!std::isfinite(*nll) || *nll < 0) throw GpuFailure("nonfinite/negative NLL");
+    *count = targets;
+  });
+}
+
+}  // extern "C"

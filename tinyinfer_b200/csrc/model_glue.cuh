@@ -1,0 +1,144 @@
+// Small kernels that tie the GPT-2 layers together in the model runtime: token+position
+// embedding, K/V placement into the paged pool, and the greedy argmax.  Rows are packed
+// (no padding rows): row r belongs to request row_req[r] and sits at absolute position
+// row_pos[r] of that request.
+#pragma once
+#include "attention.cuh"
+#include "common.cuh"
+
+namespace tib {
+
+// x[r,:] = fp16(float(wte[id]) + float(wpe[pos]))  (reference embed, llm/src/runtime.cu:25-30).
+__global__ void __launch_bounds__(256)
+embed_kernel(const int32_t* ids, const int32_t* row_pos, const __half* wte, const __half* wpe,
+             __half* x, int rows, int hidden) {
+  pdl_wait();
+  const int chunks = hidden / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * chunks;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / chunks), c = int(i % chunks) * 8;
+    uint4 a = *reinterpret_cast<const uint4*>(wte + size_t(ids[r]) * hidden + c);
+    const uint4 b = *reinterpret_cast<const uint4*>(wpe + size_t(row_pos[r]) * hidden + c);
+    __half* ah = reinterpret_cast<__half*>(&a);
+    const __half* bh = reinterpret_cast<const __half*>(&b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ah[e] = f2h(h2f(ah[e]) + h2f(bh[e]));
+    *reinterpret_cast<uint4*>(x + size_t(r) * hidden + c) = a;
+  }
+  pdl_launch_dependents();
+}
+
+// Copies the K and V thirds of qkv[r, 3*hidden] into the paged pool at (slot, layer, head, pos)
+// (reference split_scatter, llm/src/runtime.cu:34-42; the Q third is read in place later).
+__global__ void __launch_bounds__(256)
+kv_scatter_kernel(const __half* qkv, const int32_t* row_req, const int32_t* row_pos, KvPaged kv,
+                  __half* kpool, __half* vpool, int rows, int hidden) {
+  pdl_wait();
+  const int chunks = hidden / 8, d = kv.d;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * chunks;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int r = int(i / chunks), c = int(i % chunks) * 8;
+    const int h = c / d, e = c % d;
+    const size_t dst = kv.offset(row_req[r], h, row_pos[r]) + e;
+    const __half* src = qkv + size_t(r) * 3 * hidden + c;
+    *reinterpret_cast<uint4*>(kpool + dst) = *reinterpret_cast<const uint4*>(src + hidden);
+    *reinterpret_cast<uint4*>(vpool + dst) = *reinterpret_cast<const uint4*>(src + 2 * hidden);
+  }
+  pdl_launch_dependents();
+}
+
+// Greedy argmax of fp32 logits, lowest id on ties (reference argmax, llm/src/runtime.cu:59-66).
+// grid = rows, block = 256.  Also stores the winner as the next step's input id when
+// `feedback` is non-null.
+__global__ void __launch_bounds__(256)
+argmax_kernel(const float* logits, long long pitch, int cols, int32_t* out, int32_t* feedback) {
+  __shared__ float best_v[8];
+  __shared__ int best_i[8];
+  pdl_wait();
+  const float* row = logits + (long long)blockIdx.x * pitch;
+  float bv = -CUDART_INF_F; int bi = 0x7fffffff;
+  for (int c = threadIdx.x; c < cols; c += 256) {
+    const float v = row[c];
+    if (v > bv || (v == bv && c < bi)) { bv = v; bi = c; }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
+    if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { best_v[threadIdx.x >> 5] = bv; best_i[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w)
+      if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
+    out[blockIdx.x] = bi;
+    if (feedback) feedback[blockIdx.x] = bi;
+  }
+}
+
+// Teacher-forced NLL of `rows` logit rows in FP64 (reference nll_rows, llm/src/runtime.cu:67-76):
+// loss[first_position + r] = mask ? max + log(sum exp(logit - max)) - logit[target] : 0.
+// grid = rows, block = 256.
+__global__ void __launch_bounds__(256)
+nll_kernel(const float* logits, long long pitch, int cols, const int32_t* tokens, const uint8_t* mask,
+           double* loss, int first_position) {
+  __shared__ float s_max[8];
+  __shared__ double s_sum[8];
+  const int pos = first_position + blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* row = logits + (long long)blockIdx.x * pitch;
+  float m = -CUDART_INF_F;
+  for (int c = threadIdx.x; c < cols; c += 256) m = fmaxf(m, row[c]);
+  m = warp_max(m);
+  if (lane == 0) s_max[warp] = m;
+  __syncthreads();
+  m = s_max[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) m = fmaxf(m, s_max[w]);
+  double s = 0.0;
+  for (int c = threadIdx.x; c < cols; c += 256) s += exp(double(row[c]) - double(m));
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+  if (lane == 0) s_sum[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double total = 0.0;
+    for (int w = 0; w < 8; ++w) total += s_sum[w];
+    loss[pos] = mask[pos] ? double(m) + log(total) - double(row[tokens[pos]]) : 0.0;
+  }
+}
+
+// out[0] = sum of loss[0..length) (reference sum_losses, llm/src/runtime.cu:77-80); one block.
+__global__ void __launch_bounds__(256)
+sum_f64_kernel(const double* loss, double* out, int length) {
+  __shared__ double part[8];
+  double v = 0.0;
+  for (int i = threadIdx.x; i < length; i += 256) v += loss[i];
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) { double t = 0.0; for (int w = 0; w < 8; ++w) t += part[w]; *out = t; }
+}
+
+// fp32 C = A.B kept only so the ABI symbol ti_v2_legacy_gemm_f32 resolves (reference legacy_f32,
+// kernels/src/cuda/tc/gemm.cu:85-117 serves the FP32 compiler backend, not this path).
+__global__ void __launch_bounds__(256)
+sgemm_kernel(const float* a, const float* b, float* c, int m, int n, int k) {
+  __shared__ float as[16][17], bs[16][17];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int row = blockIdx.y * 16 + ty, col = blockIdx.x * 16 + tx;
+  float acc = 0.f;
+  for (int k0 = 0; k0 < k; k0 += 16) {
+    as[ty][tx] = (row < m && k0 + tx < k) ? a[size_t(row) * k + k0 + tx] : 0.f;
+    bs[ty][tx] = (k0 + ty < k && col < n) ? b[size_t(k0 + ty) * n + col] : 0.f;
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) acc = fmaf(as[ty][kk], bs[kk][tx], acc);
+    __syncthreads();
+  }
+  if (row < m && col < n) c[size_t(row) * n + col] = acc;
+}
+
+}  // namespace tib
