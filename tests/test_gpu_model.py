@@ -1,0 +1,196 @@
+"""GPU parity of the model ABI: our runtime against the reference's runtime (compiled for
+sm_100a, oracle/_ref) and the CPU oracle, on the same seeded artifact and token ids, plus the
+reference's own model gate (llm/gpu_correctness.py:4-91) replayed on our runtime."""
+import numpy as np
+import pytest
+
+from tests.gpu_common import LOGIT_ATOL, LOGIT_RTOL, REF_DIR
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+CACHED_ATOL, CACHED_RTOL = 0.03, 0.005      # reference llm/configs/evaluation.json:13-14
+
+
+@pytest.fixture(scope="module")
+def manifest(tmp_path_factory):
+    from tinyinfer_b200 import artifact
+    return artifact.write_synthetic(tmp_path_factory.mktemp("gpt2_small_seed0"), seed=0)
+
+
+@pytest.fixture(scope="module")
+def model(manifest):
+    from tinyinfer_b200.runtime import NativeModel
+    with NativeModel(None, manifest, max_batch=32, cache_slots=32, capacity=1024) as m:
+        yield m
+
+
+@pytest.fixture(scope="module")
+def ref_model(manifest):
+    path = REF_DIR / "libtinyinfer_llm.so"
+    if not path.exists():
+        pytest.skip("reference build oracle/_ref is absent")
+    from tinyinfer_b200.runtime import NativeModel
+    with NativeModel(path, manifest, max_batch=32, cache_slots=32, capacity=1024) as m:
+        yield m
+
+
+def logits_of(result):
+    value = torch.frombuffer(result["logits"], dtype=torch.float32).reshape(result["shape"]).clone()
+    assert torch.isfinite(value).all()
+    assert result["next_tokens"] == value.argmax(-1).tolist()
+    return value
+
+
+def tokens(seed, count):
+    return np.random.default_rng(seed).integers(0, 50257, count).tolist()
+
+
+def test_config0_logits_and_greedy_tokens_match_reference_runtime(model, ref_model):
+    """Batch 1, 32-token prompt, 64 greedy tokens, seed 0."""
+    prompt = tokens(0, 32)
+    model.reset_all(); ref_model.reset_all()
+    ours, theirs = logits_of(model.forward([0], [prompt])), logits_of(ref_model.forward([0], [prompt]))
+    torch.testing.assert_close(ours, theirs, atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+    model.reset_all(); ref_model.reset_all()
+    got = model.greedy([prompt], 64)["tokens"][0]
+    want = ref_model.greedy([prompt], 64)["tokens"][0]
+    assert len(got) == 64 and got[:32] == want[:32]
+    agree = next((i for i, (x, y) in enumerate(zip(got, want)) if x != y), 64)
+    print(f"greedy agreement with the reference runtime: first {agree} of 64 tokens")
+
+
+def test_decode_logits_track_reference_step_by_step(model, ref_model):
+    prompt = tokens(7, 40)
+    model.reset_all(); ref_model.reset_all()
+    a, b = model.forward([3], [prompt]), ref_model.forward([3], [prompt])
+    for step in range(24):
+        la, lb = logits_of(a), logits_of(b)
+        torch.testing.assert_close(la, lb, atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+        nxt = b["next_tokens"][0]                   # teacher-force the reference's token so histories stay equal
+        a, b = model.forward([3], [[nxt]]), ref_model.forward([3], [[nxt]])
+
+
+def test_logits_match_cpu_oracle(model, manifest):
+    from oracle import ti_oracle as orc
+    from tinyinfer_b200 import artifact
+    meta, tensors = artifact.load(manifest)
+    oracle = orc.Gpt2Oracle(tensors, meta["architecture"])
+    prompt = tokens(1, 12)
+    model.reset_all()
+    ours = logits_of(model.forward([0], [prompt]))[0]
+    want = torch.from_numpy(oracle.forward(0, prompt))
+    torch.testing.assert_close(ours, want, atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+    step = logits_of(model.forward([0], [[int(want.argmax())]]))[0]
+    torch.testing.assert_close(step, torch.from_numpy(oracle.forward(0, [int(want.argmax())])), atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+
+
+def test_reference_model_gate_on_our_runtime(model):
+    """llm/gpu_correctness.py:13-72 without the HF branch."""
+    ids = tokens(42, 64)
+    prompts = [ids[0:33], ids[41:58]]
+    model.reset_all()
+    independent = []
+    for prompt in prompts:
+        model.reset(0)
+        independent.append(logits_of(model.forward([0], [prompt]))[0])
+    full = torch.stack(independent)
+    model.reset_all()
+    batched = logits_of(model.forward([0, 1], prompts))
+    torch.testing.assert_close(batched, full, atol=CACHED_ATOL, rtol=CACHED_RTOL)
+    model.reset_all()
+    model.forward([0, 1], [p[:3] for p in prompts], return_logits=False, return_next=False)
+    cached = logits_of(model.forward([0, 1], [p[3:] for p in prompts]))
+    torch.testing.assert_close(cached, full, atol=CACHED_ATOL, rtol=CACHED_RTOL)
+    model.reset(0)
+    survivor = logits_of(model.forward([1], [[ids[59]]]))
+    model.reset(2)
+    expected = logits_of(model.forward([2], [prompts[1] + [ids[59]]]))
+    torch.testing.assert_close(survivor, expected, atol=CACHED_ATOL, rtol=CACHED_RTOL)
+    before = model.lengths()
+    for slots, rows in (([1, 1], [[3], [4]]), ([1], [[3] * model.options.capacity])):
+        with pytest.raises(RuntimeError):
+            model.forward(slots, rows, return_logits=False, return_next=False)
+        assert model.lengths() == before
+    score = model.score(ids[:33], [0] + [1] * 32, positions=True)
+    assert model.lengths() == before and score["target_count"] == 32
+    assert abs(sum(score["position_nll"]) - score["sum_nll"]) <= 1e-7 * max(1., score["sum_nll"])
+    subset_mask = [0] + [int(i % 3 != 0) for i in range(1, 33)]
+    subset = model.score(ids[:33], subset_mask, positions=True)
+    want = sum(v for v, use in zip(score["position_nll"], subset_mask) if use)
+    assert subset["target_count"] == sum(subset_mask) and abs(subset["sum_nll"] - want) <= 1e-7 * max(1., want)
+    assert all(v == 0 for v, use in zip(subset["position_nll"], subset_mask) if not use)
+    model.reset_all()
+    gen_prompts, requested = [prompts[0][:7], prompts[1][:5]], [3, 1]
+    mixed = model.greedy(gen_prompts, requested, slots=[0, 1])
+    assert mixed["output_lengths"] == requested and model.lengths()[:2] == [9, 5]
+    for row, count, generated in zip(gen_prompts, requested, mixed["tokens"]):
+        model.reset(2)
+        assert model.greedy([row], count, slots=[2])["tokens"][0] == generated
+    trace = model.trace()
+    for key in ("embedding", "gemm_int8", "layernorm", "gelu", "attention", "residual", "kv_scatter_gather", "lm_head", "argmax", "nll"):
+        assert trace[key] > 0, key
+    model.reset_all()
+
+
+def test_score_matches_reference_runtime(model, ref_model):
+    ids = tokens(9, 48)
+    mask = [0] + [1] * 47
+    a, b = model.score(ids, mask, positions=True), ref_model.score(ids, mask, positions=True)
+    assert a["target_count"] == b["target_count"] == 47
+    assert abs(a["sum_nll"] - b["sum_nll"]) <= 2e-3 * b["sum_nll"]
+    np.testing.assert_allclose(a["position_nll"], b["position_nll"], atol=3e-2, rtol=1e-2)
+
+
+def test_config2_ragged_batch32_decode_matches_reference(model, ref_model):
+    """Batch 32, prompt lengths uniform in [16,512], greedy continuation, seed 2 (shortened to 16 tokens)."""
+    rng = np.random.default_rng(2)
+    lengths = rng.integers(16, 513, 32)
+    prompts = [rng.integers(0, 50257, int(n)).tolist() for n in lengths]
+    model.reset_all(); ref_model.reset_all()
+    ours = logits_of(model.forward(list(range(32)), prompts))
+    theirs = logits_of(ref_model.forward(list(range(32)), prompts))
+    torch.testing.assert_close(ours, theirs, atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+    nxt = theirs.argmax(-1).tolist()
+    for _ in range(4):
+        a = logits_of(model.forward(list(range(32)), [[t] for t in nxt]))
+        b = logits_of(ref_model.forward(list(range(32)), [[t] for t in nxt]))
+        torch.testing.assert_close(a, b, atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+        nxt = b.argmax(-1).tolist()
+    assert model.lengths() == ref_model.lengths()
+    model.reset_all(); ref_model.reset_all()
+    got = model.greedy(prompts, 16)["tokens"]
+    want = ref_model.greedy(prompts, 16)["tokens"]
+    same = sum(g == w for g, w in zip(got, want))
+    print(f"batch-32 ragged greedy: {same}/32 requests identical over 16 tokens")
+    assert same >= 28
+
+
+def test_slot_reuse_and_page_recycling(model):
+    prompt = tokens(5, 70)
+    model.reset_all()
+    first = logits_of(model.forward([5], [prompt]))
+    for slot in (6, 7, 8):
+        model.forward([slot], [tokens(slot, 100)], return_logits=False, return_next=False)
+    model.reset(5); model.reset(7)
+    again = logits_of(model.forward([7], [prompt]))
+    assert torch.equal(first, again)               # same kernels, same order: bit-identical whatever pages are used
+    model.reset_all()
+    assert model.lengths() == [0] * 32
+
+
+def test_validation_errors_and_struct_size(model, manifest):
+    import ctypes as C
+    from tinyinfer_b200.runtime import NativeModel, Options
+    with pytest.raises(RuntimeError):
+        model.greedy([[1, 2, 3]], 1022)            # prompt + new tokens exceeds capacity
+    model.forward([0], [[1, 2]], return_logits=False, return_next=False)
+    with pytest.raises(RuntimeError):
+        model.greedy([[1]], 1, slots=[0])          # greedy needs an empty slot
+    model.reset_all()
+    lib = model.lib
+    bad = Options(24, 0, 1, 1, 16, 0, 0)
+    handle = C.c_void_p()
+    assert lib.ti_llm_create(str(manifest).encode(), C.byref(bad), C.byref(handle)) == 1 and not handle
+    with pytest.raises(ValueError):
+        NativeModel(None, manifest, max_batch=65, cache_slots=65)
