@@ -1,0 +1,344 @@
+#!/usr/bin/env python
+"""Benchmark of the INT8-weight GPT-2 decode path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the metric's batched decode configuration): GPT-2 small, INT8 weights, random-init
+artifact (seed 0), batch 32 per GPU, prompt lengths uniform in [16, 512], 128 new tokens per
+request, token ids uniform, seed 2.  One "step" is one decode step of the whole batch (32 tokens);
+the default K + W covers the 127 decode steps of the 128-token generation.  With N > 1 every rank
+holds a full replica on its own GPU and runs the same per-GPU workload (weak scaling, no
+collective on the data path); the timed region is bracketed by barrier + synchronize and the
+slowest rank's device time is used.
+
+Printed JSON (one line, rank 0):
+  value      tokens/s with tokens, positions and KV cache resident on the GPU between steps
+             (ti_b200_llm_decode_steps; CUDA events on the model's stream)
+  e2e        tokens/s through the per-step reference-facing call ti_llm_forward_batch: every step
+             copies the step's ids + metadata from pinned host memory to the GPU and reads the
+             step's next-token ids back to the host
+  roofline   achieved HBM GB/s of the dominant kernel (timed alone, same shapes, CUDA events) and of
+             the whole step against the measured copy bandwidth of this pool's B200s
+  cpu_baseline  the decode sequence composed from the reference's own CPU kernels, timed on the
+             host cores for a bounded sample of the same workload
+
+--impl reference prints the CPU arm alone in the same format.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+BATCH, NEW_TOKENS, PROMPT_LO, PROMPT_HI, WORKLOAD_SEED, WEIGHT_SEED = 32, 128, 16, 512, 2, 0
+WORKLOAD = ("GPT-2 small INT8-weight batched decode: batch 32 per GPU, prompt lengths uniform in [16,512], "
+            "128 new tokens per request, seed 2")
+FALLBACK_HBM_GBS = 6650.0
+
+
+def workload_prompts():
+    rng = np.random.default_rng(WORKLOAD_SEED)
+    lengths = rng.integers(PROMPT_LO, PROMPT_HI + 1, BATCH)
+    return [rng.integers(0, 50257, int(n)).tolist() for n in lengths]
+
+
+def artifact_path():
+    """Seeded random GPT-2 small artifact, written once per machine."""
+    from tinyinfer_b200 import artifact
+    base = Path(os.environ.get("TINYINFER_B200_CACHE", Path(tempfile.gettempdir()) / "tinyinfer_b200_bench"))
+    return artifact.write_synthetic(base / f"gpt2_small_int8_seed{WEIGHT_SEED}", seed=WEIGHT_SEED)
+
+
+def peak_hbm():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+def step_bytes(weight_bytes, cached, hidden=768, kv_per_position=36864):
+    """Algorithmic bytes of one decode step: every weight byte once, plus per request one wte and
+    one wpe row and its KV history read (cached positions) and extended (one position)."""
+    return weight_bytes + sum(2 * hidden * 2 + kv_per_position * (t + 1) for t in cached)
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons while the timed region runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device, self.rows, self.proc = device, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *_):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+
+    def summary(self):
+        good = [r for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        if not good:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in good for n, v in zip(names, r[5:9]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(float(r[1]) for r in good), "sm_max_mhz": float(good[0][2]), "reasons": reasons,
+                "samples": len(good), "power_w_max": max(float(r[3]) for r in good if r[3].replace(".", "").isdigit())}
+
+
+# ---------------------------------------------------------------------------- CPU arm
+def cpu_arm(steps, warmup, threads=None):
+    from oracle import cpu_decode
+    from tinyinfer_b200 import artifact
+    meta, tensors = artifact.load(artifact_path())
+    lengths = [len(p) + NEW_TOKENS // 2 for p in workload_prompts()]        # cache sizes mid-way through the generation
+    result = cpu_decode.time_decode(tensors, meta["architecture"], lengths, steps, warmup, seed=WORKLOAD_SEED, threads=threads)
+    sample = (f"{steps} decode steps (+{warmup} warm-up) of the batch-32 workload at its mid-generation cache lengths; KV histories "
+              "filled with random values instead of running the prefill; harness composed from the reference's ti_cpu_gemm/"
+              "ti_cpu_layernorm/ti_cpu_softmax + host codec" if result["kind"] == "reference" else
+              f"{steps} decode steps of the batch-32 workload on the numpy port (oracle/_ref absent)")
+    return result, sample
+
+
+def reference_main(args, rank):
+    if rank != 0:
+        return
+    result, sample = cpu_arm(max(1, args.steps), max(0, args.warmup))
+    line = {"impl": "reference", "metric": "int8_gpt2_decode_tokens_per_s", "value": result["tokens_per_s"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": result["seconds_per_step"] * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "runs_on": "host CPU cores"},
+            "cpu_baseline": {"value": result["tokens_per_s"], "unit": "tokens/s", "cores": result["cores"], "kind": result["kind"], "sample": sample},
+            "e2e": {"value": result["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------- GPU arm
+def time_kernel(fn, iters=30, warm=5):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / iters * 1e-3
+
+
+def kernel_rooflines(cached, peak):
+    """The two kernel families that carry most of a step's bytes, timed alone on the step's shapes
+    (operator ABI, torch current stream, inputs far larger than L2 are cycled to defeat caching)."""
+    import torch
+    from tinyinfer_b200.native_ops import NativeOps
+    ops = NativeOps()
+    out = {}
+    g = torch.Generator().manual_seed(1)
+    # decode attention over the ragged histories of one layer, distinct K/V per call (12 "layers")
+    kmax = max(cached) + 1
+    q = torch.randn((BATCH, 12, 1, 64), generator=g).half().cuda()
+    ks = [torch.randn((BATCH, 12, kmax, 64), device="cuda", dtype=torch.float16) for _ in range(12)]
+    vs = [torch.randn((BATCH, 12, kmax, 64), device="cuda", dtype=torch.float16) for _ in range(12)]
+    lengths = [t + 1 for t in cached]
+    state = {"i": 0}
+    def attn():
+        i = state["i"] = (state["i"] + 1) % 12
+        ops.attention_decode(q, ks[i], vs[i], lengths, chunk=128)
+    seconds = time_kernel(attn)
+    nbytes = sum(lengths) * 12 * 64 * 2 * 2 + BATCH * 12 * 64 * 2 * 2
+    out["attention_decode (1 layer, 32 ragged requests)"] = {"seconds": seconds, "bytes": nbytes, "launches_per_step": 12}
+    del ks, vs
+    # lm_head GEMV, M = 32 (weights 38.6 MB, re-pitched to 50304 columns as the runtime does)
+    a = torch.randn((BATCH, 768), generator=g).half().cuda()
+    ws = [torch.randint(-127, 128, (768, 50304), dtype=torch.int8, device="cuda") for _ in range(6)]
+    s = (torch.rand(50304, generator=g) * 0.019 + 0.001).cuda()
+    def head():
+        i = state["i"] = (state["i"] + 1) % 6
+        ops.gemm_int8(a, ws[i], s, output_dtype=torch.float32)
+    seconds = time_kernel(head)
+    out["gemv_int8 lm_head (M=32, 768x50304)"] = {"seconds": seconds, "bytes": 768 * 50304 + 4 * 50304 + 2 * BATCH * 768 + 4 * BATCH * 50304,
+                                               "launches_per_step": 1}
+    del ws
+    # the four per-layer GEMVs, M = 32, one layer's worth of distinct weights per call
+    shapes = [(768, 2304), (768, 768), (768, 3072), (3072, 768)]
+    layers = [[(torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda"), (torch.rand(n, device="cuda") * 0.019 + 0.001),
+                torch.randn((BATCH, k), device="cuda").half()) for k, n in shapes] for _ in range(12)]
+    def block():
+        i = state["i"] = (state["i"] + 1) % 12
+        for w, sc, act in layers[i]:
+            ops.gemm_int8(act, w, sc)
+    seconds = time_kernel(block)
+    nbytes = sum(k * n + 4 * n + 2 * BATCH * k + 2 * BATCH * n for k, n in shapes)
+    out["gemv_int8 x4 of one layer (M=32)"] = {"seconds": seconds, "bytes": nbytes, "launches_per_step": 12}
+    for v in out.values():
+        v["gbs"] = v["bytes"] / v["seconds"] / 1e9
+        v["frac"] = v["gbs"] / peak
+    return out
+
+
+def gpu_main(args, rank, world):
+    import torch
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(value):
+        if not dist:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    from tinyinfer_b200 import artifact
+    from tinyinfer_b200.runtime import NativeModel
+    if rank == 0:
+        manifest_path = artifact_path()
+    barrier()
+    manifest_path = artifact_path()
+    manifest = json.loads(Path(manifest_path).read_text())
+    weights = artifact.weight_bytes(manifest)
+    prompts = workload_prompts()
+    slots = list(range(BATCH))
+    K, W = max(1, args.steps), max(0, args.warmup)
+    peak, peak_source = peak_hbm()
+
+    with NativeModel(None, manifest_path, device=local, max_batch=BATCH, cache_slots=BATCH, capacity=1024) as model:
+        room = 1024 - max(len(p) for p in prompts) - 1
+
+        def prefill():
+            model.reset_all()
+            t0 = time.perf_counter()
+            first = model.forward(slots, prompts, return_logits=False)["next_tokens"]
+            return first, (time.perf_counter() - t0) * 1e3
+
+        # ---- value: device-resident decode steps ------------------------------------------------
+        first, ttft_ms = prefill()
+        ids = first
+        if W:
+            ids = model.decode_steps(slots, ids, W)["tokens"][-1]
+        cached_at_start = model.lengths()[:BATCH]
+        barrier()
+        device_ms, done, total_bytes = 0.0, 0, 0
+        with ClockSampler(local) as clocks:
+            while done < K:
+                lengths_now = model.lengths()[:BATCH]
+                n = min(K - done, 1024 - max(lengths_now))
+                if n <= 0:                                  # generation exhausted the context: start over (untimed prefill)
+                    ids, _ = prefill()
+                    continue
+                out = model.decode_steps(slots, ids, n)
+                device_ms += out["device_ms"]
+                ids = out["tokens"][-1]
+                total_bytes += sum(step_bytes(weights, [t + i for t in lengths_now]) for i in range(n))
+                done += n
+        barrier()
+        device_ms = max_over_ranks(device_ms)
+        value = world * BATCH * K / (device_ms * 1e-3)
+        chunks = 1
+        while chunks * 128 < max(cached_at_start) + K:
+            chunks *= 2
+        launches_per_step = 1 + 12 * (8 + (1 if chunks > 1 else 0)) + 4
+        step_gbs = total_bytes / (device_ms * 1e-3) / 1e9
+
+        # ---- e2e: per-step reference-facing call, host ids in, host ids out ----------------------
+        first, _ = prefill()
+        ids = first
+        for _ in range(max(W, 3)):
+            ids = model.forward(slots, [[t] for t in ids], return_logits=False)["next_tokens"]
+        e2e_steps = min(K, 1024 - max(model.lengths()[:BATCH]) - 1)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            ids = model.forward(slots, [[t] for t in ids], return_logits=False)["next_tokens"]
+        e2e_s = max_over_ranks(time.perf_counter() - t0)
+        barrier()
+        e2e = {"value": world * BATCH * e2e_steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 5 * BATCH * 4,
+               "d2h_bytes_per_step": BATCH * 4 + 4, "steps": e2e_steps, "api": "ti_llm_forward_batch per step",
+               "note": "includes the ctypes marshalling of llm/runtime.py-style Python lists"}
+        # the generation call a user makes (prompts in, all tokens out), reference's decode-rate definition
+        model.reset_all()
+        gen = model.greedy(prompts, NEW_TOKENS)
+        decode_s = (max(gen["total_ms"]) - gen["ttft_ms"][0]) * 1e-3
+        e2e["greedy_batch_tokens_per_s"] = world * BATCH * (NEW_TOKENS - 1) / decode_s
+        e2e["greedy_batch_ttft_ms"] = gen["ttft_ms"][0]
+
+    line = {"metric": "int8_gpt2_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": device_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations x int8 weights, f32 accumulate",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "replicas": world, "l2": "inputs larger than L2 (about 0.5 GB of weights + KV per step)",
+                                            "weights": f"random N(0,0.02), seed {WEIGHT_SEED}", "prefill_ttft_ms": ttft_ms},
+            "e2e": e2e, "gpu_launches": launches_per_step * K, "clocks": clocks.summary()}
+    if rank == 0:
+        kernels = kernel_rooflines(cached_at_start, peak)
+        top = max(kernels.items(), key=lambda kv: kv[1]["seconds"] * kv[1]["launches_per_step"])
+        line["roofline"] = {"kernel": top[0], "bound": "hbm", "achieved": top[1]["gbs"], "peak": peak, "unit": "GB/s", "frac": top[1]["frac"],
+                            "traffic": None, "peak_source": peak_source,
+                            "share_of_step": top[1]["seconds"] * top[1]["launches_per_step"] / (device_ms * 1e-3 / K)}
+        line["step_roofline"] = {"bound": "hbm", "achieved": step_gbs / world if world > 1 else step_gbs, "peak": peak, "unit": "GB/s",
+                                 "frac": (step_gbs / world if world > 1 else step_gbs) / peak,
+                                 "bytes_per_step": total_bytes / K, "note": "algorithmic weight+KV bytes per step / step time, per GPU"}
+        line["kernels"] = {k: {"us": v["seconds"] * 1e6, "GBps": v["gbs"], "frac": v["frac"], "launches_per_step": v["launches_per_step"]}
+                           for k, v in kernels.items()}
+        if world == 1 and not args.no_cpu:
+            result, sample = cpu_arm(steps=int(os.environ.get("TINYINFER_B200_CPU_STEPS", 6)), warmup=1)
+            line["cpu_baseline"] = {"value": result["tokens_per_s"], "unit": "tokens/s", "cores": result["cores"], "kind": result["kind"], "sample": sample}
+        print(json.dumps(line))
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=120)
+    parser.add_argument("--warmup", type=int, default=7)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    args = parser.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        reference_main(args, rank)
+    else:
+        gpu_main(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -41,6 +41,19 @@ int ti_b200_attention_decode_f16(const uint16_t* q, const uint16_t* k, const uin
  * are optional. */
 int ti_b200_artifact_check(const char* manifest_path, int32_t* layers, int32_t* heads, int32_t* hidden,
                            int32_t* int8_weights);
+
+/* Exported by libtinyinfer_llm.so.  Runs `steps` greedy decode steps for `batch` requests whose
+ * slots already hold a prefix (ti_llm_forward_batch), starting from the input ids first_tokens[B]
+ * (normally the argmax the prefill returned).  Tokens, positions and the KV cache stay on the GPU
+ * between steps -- the host is involved once, at the end.  out_tokens (host, nullable) receives
+ * [steps][batch] ids; device_ms (nullable) the time between the first and the last kernel of the
+ * steps measured with CUDA events on the model's stream.  Each slot advances by `steps`.
+ * The reference has no counterpart: its ti_llm_greedy_batch returns to the host after every
+ * token (llm/src/runtime.cu:196-200).  ti_llm_greedy_batch of this build runs on the same
+ * mechanism; this entry point exposes it for measurement.  Returns a ti_llm_status. */
+struct ti_llm_model;
+int ti_b200_llm_decode_steps(struct ti_llm_model* model, const int32_t* slots, const int32_t* first_tokens,
+                             int32_t batch, int32_t steps, int32_t* out_tokens, double* device_ms);
 #ifdef __cplusplus
 }
 #endif

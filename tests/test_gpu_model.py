@@ -42,6 +42,15 @@ def logits_of(result):
     return value
 
 
+def assert_logits_close(ours, theirs, what):
+    """The model gate: |ours - theirs| <= 2e-2 + 1e-2 * |theirs| for every logit; prints the margin used."""
+    diff = (ours - theirs).abs()
+    bound = LOGIT_ATOL + LOGIT_RTOL * theirs.abs()
+    print(f"{what}: max |diff| {diff.max().item():.3e}, worst diff/bound {(diff / bound).max().item():.3f}, "
+          f"argmax equal {(ours.argmax(-1) == theirs.argmax(-1)).float().mean().item():.3f}")
+    assert (diff <= bound).all(), f"{what}: max |diff| {diff.max().item()}"
+
+
 def tokens(seed, count):
     return np.random.default_rng(seed).integers(0, 50257, count).tolist()
 
@@ -51,7 +60,7 @@ def test_config0_logits_and_greedy_tokens_match_reference_runtime(model, ref_mod
     prompt = tokens(0, 32)
     model.reset_all(); ref_model.reset_all()
     ours, theirs = logits_of(model.forward([0], [prompt])), logits_of(ref_model.forward([0], [prompt]))
-    torch.testing.assert_close(ours, theirs, atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+    assert_logits_close(ours, theirs, "config0 prompt logits")
     model.reset_all(); ref_model.reset_all()
     got = model.greedy([prompt], 64)["tokens"][0]
     want = ref_model.greedy([prompt], 64)["tokens"][0]
@@ -66,7 +75,7 @@ def test_decode_logits_track_reference_step_by_step(model, ref_model):
     a, b = model.forward([3], [prompt]), ref_model.forward([3], [prompt])
     for step in range(24):
         la, lb = logits_of(a), logits_of(b)
-        torch.testing.assert_close(la, lb, atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+        assert_logits_close(la, lb, f"decode step {step}")
         nxt = b["next_tokens"][0]                   # teacher-force the reference's token so histories stay equal
         a, b = model.forward([3], [[nxt]]), ref_model.forward([3], [[nxt]])
 
@@ -150,12 +159,12 @@ def test_config2_ragged_batch32_decode_matches_reference(model, ref_model):
     model.reset_all(); ref_model.reset_all()
     ours = logits_of(model.forward(list(range(32)), prompts))
     theirs = logits_of(ref_model.forward(list(range(32)), prompts))
-    torch.testing.assert_close(ours, theirs, atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+    assert_logits_close(ours, theirs, "config2 ragged prefill logits")
     nxt = theirs.argmax(-1).tolist()
     for _ in range(4):
         a = logits_of(model.forward(list(range(32)), [[t] for t in nxt]))
         b = logits_of(ref_model.forward(list(range(32)), [[t] for t in nxt]))
-        torch.testing.assert_close(a, b, atol=LOGIT_ATOL, rtol=LOGIT_RTOL)
+        assert_logits_close(a, b, "config2 decode step")
         nxt = b.argmax(-1).tolist()
     assert model.lengths() == ref_model.lengths()
     model.reset_all(); ref_model.reset_all()

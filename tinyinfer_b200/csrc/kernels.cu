@@ -224,8 +224,11 @@ cudaError_t kv_scatter(const void* qkv, const int32_t* row_req, const int32_t* r
                 row_pos, paged(kv), static_cast<__half*>(kv.k_pool), static_cast<__half*>(kv.v_pool), rows, hidden);
 }
 cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out, int32_t* feedback,
-                   const LaunchOpts& o) {
-  return launch(argmax_kernel, dim3(rows), dim3(256), 0, o, 1, logits, pitch, cols, out, feedback);
+                   const int32_t* step, const LaunchOpts& o) {
+  return launch(argmax_kernel, dim3(rows), dim3(256), 0, o, 1, logits, pitch, cols, out, feedback, step);
+}
+cudaError_t advance(int32_t* row_pos, int32_t* kv_lengths, int32_t* step, int batch, const LaunchOpts& o) {
+  return launch(advance_kernel, dim3((batch + 63) / 64), dim3(64), 0, o, 1, row_pos, kv_lengths, step, batch);
 }
 
 cudaError_t nll_rows(const float* logits, long long pitch, int rows, int cols, const int32_t* tokens, const uint8_t* mask,

@@ -73,8 +73,11 @@ TIB_EXPORT cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const v
                              void* x, int rows, int hidden, const LaunchOpts& opts);
 TIB_EXPORT cudaError_t kv_scatter(const void* qkv, const int32_t* row_req, const int32_t* row_pos,
                                   int rows, int hidden, const PagedKv& kv, const LaunchOpts& opts);
+// out[(*step) * rows + r] = argmax of row r (step may be null = 0); feedback[r] too when non-null.
 TIB_EXPORT cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out,
-                              int32_t* feedback, const LaunchOpts& opts);
+                              int32_t* feedback, const int32_t* step, const LaunchOpts& opts);
+// row_pos[b]++, kv_lengths[b]++ for b < batch, and (*step)++.
+TIB_EXPORT cudaError_t advance(int32_t* row_pos, int32_t* kv_lengths, int32_t* step, int batch, const LaunchOpts& opts);
 
 TIB_EXPORT cudaError_t nll_rows(const float* logits, long long pitch, int rows, int cols, const int32_t* tokens,
                                 const uint8_t* mask, double* loss, int first_position, cudaStream_t stream);

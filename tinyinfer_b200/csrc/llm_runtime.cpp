@@ -15,6 +15,7 @@
 
 #include <algorithm>
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -94,6 +95,7 @@ struct ti_llm_model {
     cudaGetDevice(&before);
     cudaSetDevice(opt.device);
     if (stream) cudaStreamSynchronize(stream);
+    for (const StepGraph& g : graphs) cudaGraphExecDestroy(g.exec);
     for (void* p : owned) cudaFree(p);
     for (void* p : pinned) cudaFreeHost(p);
     if (stream) cudaStreamDestroy(stream);
@@ -153,7 +155,8 @@ struct ti_llm_model {
     qkv = dev<uint16_t>(r * 3 * H); act = dev<uint16_t>(r * 4 * H);
     last = dev<uint16_t>(size_t(std::max(opt.max_batch, kScoreRows)) * H);
     logits = dev<float>(size_t(std::max(opt.max_batch, kScoreRows)) * vpitch);
-    const int chunks = tib::decode_chunks(opt.capacity, kDecodeChunk);
+    int chunks = 1;                                              // decode segments round the chunk count up to a power of two
+    while (chunks * kDecodeChunk < opt.capacity) chunks *= 2;
     att_acc = dev<float>(size_t(opt.max_batch) * shape.heads * chunks * 64);
     att_ml = dev<float>(size_t(opt.max_batch) * shape.heads * chunks * 2);
 
@@ -170,6 +173,11 @@ struct ti_llm_model {
     const size_t meta = 3 * r + 6 * size_t(opt.max_batch);
     h_meta = host<int32_t>(meta); d_meta = dev<int32_t>(meta);
     d_next = dev<int32_t>(size_t(opt.max_batch)); h_next = host<int32_t>(size_t(opt.max_batch));
+    d_seg = dev<int32_t>(size_t(5) * opt.max_batch); h_seg = host<int32_t>(size_t(5) * opt.max_batch);
+    d_step = dev<int32_t>(1);
+    d_log = dev<int32_t>(size_t(opt.capacity) * opt.max_batch); h_log = host<int32_t>(size_t(opt.capacity) * opt.max_batch);
+    if (const char* v = std::getenv("TINYINFER_B200_GRAPH")) use_graph = std::atoi(v) != 0;   // debugging aids: 0 = plain launches
+    if (const char* v = std::getenv("TINYINFER_B200_PDL")) use_pdl = std::atoi(v) != 0;
     h_status = host<unsigned int>(1); *h_status = 0;
     d_score_tokens = dev<int32_t>(size_t(opt.capacity)); d_score_mask = dev<uint8_t>(size_t(opt.capacity));
     d_loss = dev<double>(size_t(opt.capacity)); d_loss_sum = dev<double>(1);
@@ -198,18 +206,62 @@ struct ti_llm_model {
     c.a = a; c.lda = l.k; c.w = l.w; c.ldw = l.ldw; c.w_int8 = int8; c.scales = l.scales; c.bias = l.bias;
     c.out = out; c.ldo = fp32 ? vpitch : l.n; c.out_fp32 = fp32; c.residual = residual; c.gelu = gelu;
     c.m = rows; c.n = l.n; c.k = l.k;
-    tib::LaunchOpts o; o.stream = stream;
-    ++(int8 ? trace.gemm_int8 : trace.gemm_fp16);
+    tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
     ck(tib::gemm(c, o));
   }
 
-  // slots/lens describe `batch` requests; tokens are packed request after request.
-  // Leaves LayerNorm_f of each request's last row in `last` (and of every row in `norm` when
-  // all_rows is set, for scoring).
+  // Device-resident description of the rows of one pass.
+  struct Meta {
+    const int32_t *ids, *row_req, *row_pos;                       // per row
+    const int32_t *row_start, *qlens, *offsets, *kvlens, *slots;   // per request
+    int rows, batch, max_q, max_kv;
+  };
+
+  // Embedding and every transformer block; leaves the final hidden state in `x`.
+  void run_layers(const Meta& m) {
+    const int H = shape.hidden;
+    tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
+    ck(tib::embed(m.ids, m.row_pos, wte, wpe, x, m.rows, H, o));
+    tib::PagedKv kv; kv.k_pool = k_pool; kv.v_pool = v_pool; kv.table = d_table; kv.slots = m.slots;
+    kv.table_pitch = pages_per_slot; kv.layers = shape.layers; kv.heads = shape.heads; kv.head_dim = 64;
+    for (int l = 0; l < shape.layers; ++l) {
+      const Block& b = blocks[size_t(l)];
+      kv.layer = l;
+      ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, m.rows, H, 1e-5f, o));
+      gemm(norm, b.qkv, qkv, m.rows, false, nullptr, false);
+      ck(tib::kv_scatter(qkv, m.row_req, m.row_pos, m.rows, H, kv, o));
+      if (m.max_q == 1) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, kv, o));
+      else ck(tib::attention_paged(qkv, attn, m.row_start, m.qlens, m.kvlens, m.offsets, m.batch, m.max_q, m.max_kv, kv, o));
+      gemm(attn, b.proj, res, m.rows, false, x, false);             // res = x + proj(attn)
+      ck(tib::layernorm(res, nullptr, b.ln2_g, b.ln2_b, norm, m.rows, H, 1e-5f, o));
+      gemm(norm, b.fc, act, m.rows, false, nullptr, true);          // act = gelu(fc(norm))
+      gemm(act, b.proj2, x, m.rows, false, res, false);             // x = res + proj2(act)
+    }
+  }
+  // Logical operations of one pass, counted as the reference counts its separate kernels
+  // (llm/src/runtime.cu:131-165) although several of them are fused here.
+  void count_pass() {
+    const uint64_t L = uint64_t(shape.layers);
+    ++trace.forward_calls; ++trace.embedding;
+    trace.layernorm += 2 * L + 1; (int8 ? trace.gemm_int8 : trace.gemm_fp16) += 4 * L;
+    trace.kv_scatter_gather += L; trace.attention += L; trace.residual += 2 * L; trace.gelu += L;
+  }
+  void count_head(bool with_argmax) { ++trace.lm_head; ++(int8 ? trace.gemm_int8 : trace.gemm_fp16); if (with_argmax) ++trace.argmax; }
+
+  void upload_table() {
+    if (!table_dirty) return;
+    ck(cudaMemcpyAsync(d_table, table.data(), table.size() * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    table_dirty = false;
+  }
+
+  // General pass (prefill, mixed lengths, scoring).  slots/lens describe the requests; tokens are
+  // packed request after request.  LayerNorm_f of each request's last row lands in `last`, or of
+  // every row in `norm` when all_rows is set.
   void transform(const std::vector<int32_t>& ss, const std::vector<int32_t>& packed, const std::vector<int32_t>& lens, bool all_rows) {
     const int batch = int(ss.size()), H = shape.hidden;
-    int rows = 0, max_q = 0, max_kv = 0;
-    for (int b = 0; b < batch; ++b) { rows += lens[size_t(b)]; max_q = std::max(max_q, lens[size_t(b)]); }
+    Meta m{}; m.batch = batch;
+    for (int b = 0; b < batch; ++b) { m.rows += lens[size_t(b)]; m.max_q = std::max(m.max_q, lens[size_t(b)]); }
+    const int rows = m.rows;
     int32_t* ids = h_meta; int32_t* row_req = ids + rows; int32_t* row_pos = row_req + rows; int32_t* per = row_pos + rows;
     int32_t *row_start = per, *qlens = per + batch, *offsets = per + 2 * batch, *kvlens = per + 3 * batch,
             *slot_of = per + 4 * batch, *last_row = per + 5 * batch;
@@ -218,39 +270,21 @@ struct ti_llm_model {
       const int s = ss[size_t(b)], n = lens[size_t(b)], start = lengths[size_t(s)];
       reserve(s, start + n);
       row_start[b] = r; qlens[b] = n; offsets[b] = start; kvlens[b] = start + n; slot_of[b] = s; last_row[b] = r + n - 1;
-      max_kv = std::max(max_kv, start + n);
+      m.max_kv = std::max(m.max_kv, start + n);
       for (int t = 0; t < n; ++t, ++r) { ids[r] = packed[size_t(r)]; row_req[r] = b; row_pos[r] = start + t; }
     }
-    if (table_dirty) { ck(cudaMemcpyAsync(d_table, table.data(), table.size() * sizeof(int32_t), cudaMemcpyHostToDevice, stream)); table_dirty = false; }
-    const size_t meta_count = size_t(3 * rows + 6 * batch);
-    ck(cudaMemcpyAsync(d_meta, h_meta, meta_count * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
-    const int32_t *d_ids = d_meta, *d_row_req = d_meta + rows, *d_row_pos = d_meta + 2 * rows, *d_per = d_meta + 3 * rows;
-    const int32_t *d_row_start = d_per, *d_qlens = d_per + batch, *d_offsets = d_per + 2 * batch, *d_kvlens = d_per + 3 * batch,
-                  *d_slots = d_per + 4 * batch, *d_last_row = d_per + 5 * batch;
-
-    tib::LaunchOpts o; o.stream = stream;
-    ++trace.forward_calls; ++trace.embedding;
-    ck(tib::embed(d_ids, d_row_pos, wte, wpe, x, rows, H, o));
-    tib::PagedKv kv; kv.k_pool = k_pool; kv.v_pool = v_pool; kv.table = d_table; kv.slots = d_slots;
-    kv.table_pitch = pages_per_slot; kv.layers = shape.layers; kv.heads = shape.heads; kv.head_dim = 64;
-    const bool decode = max_q == 1;
-    for (int l = 0; l < shape.layers; ++l) {
-      const Block& b = blocks[size_t(l)];
-      kv.layer = l;
-      ++trace.layernorm; ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, rows, H, 1e-5f, o));
-      gemm(norm, b.qkv, qkv, rows, false, nullptr, false);
-      ++trace.kv_scatter_gather; ck(tib::kv_scatter(qkv, d_row_req, d_row_pos, rows, H, kv, o));
-      ++trace.attention;
-      if (decode) ck(tib::attention_paged_decode(qkv, attn, d_kvlens, batch, max_kv, kDecodeChunk, att_acc, att_ml, kv, o));
-      else ck(tib::attention_paged(qkv, attn, d_row_start, d_qlens, d_kvlens, d_offsets, batch, max_q, max_kv, kv, o));
-      ++trace.residual; gemm(attn, b.proj, res, rows, false, x, false);            // res = x + proj(attn)
-      ++trace.layernorm; ck(tib::layernorm(res, nullptr, b.ln2_g, b.ln2_b, norm, rows, H, 1e-5f, o));
-      ++trace.gelu; gemm(norm, b.fc, act, rows, false, nullptr, true);              // act = gelu(fc(norm))
-      ++trace.residual; gemm(act, b.proj2, x, rows, false, res, false);             // x = res + proj2(act)
-    }
-    ++trace.layernorm;
+    upload_table();
+    ck(cudaMemcpyAsync(d_meta, h_meta, size_t(3 * rows + 6 * batch) * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    const int32_t* per_d = d_meta + 3 * rows;
+    m.ids = d_meta; m.row_req = d_meta + rows; m.row_pos = d_meta + 2 * rows;
+    m.row_start = per_d; m.qlens = per_d + batch; m.offsets = per_d + 2 * batch; m.kvlens = per_d + 3 * batch; m.slots = per_d + 4 * batch;
+    // A one-token-per-request pass through this path (e.g. with logits requested) still uses the tile
+    // attention when any request is longer; decode attention needs max_q == 1.
+    count_pass();
+    run_layers(m);
+    tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
     if (all_rows) ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, norm, rows, H, 1e-5f, o));
-    else ck(tib::layernorm(x, d_last_row, lnf_g, lnf_b, last, batch, H, 1e-5f, o));
+    else ck(tib::layernorm(x, per_d + 5 * batch, lnf_g, lnf_b, last, batch, H, 1e-5f, o));
   }
 
   void finish() {
@@ -263,6 +297,77 @@ struct ti_llm_model {
     }
   }
 
+  // ------------------------------------------------------------ device-resident greedy decode
+  // A decode segment keeps its state on the GPU: d_seg = [ids | row_req | row_pos | kvlens | slots]
+  // (max_batch each) and a step counter.  One step = embedding .. lm_head .. argmax, whose winner is
+  // written straight into ids[] (next step's input) and into d_log[step][request]; a last small
+  // kernel advances positions, lengths and the counter.  Nothing returns to the host between steps,
+  // so a step can be replayed as a CUDA graph; graphs are cached per (batch, attention chunk count).
+  struct StepGraph { int batch, chunks; cudaGraphExec_t exec; };
+  std::vector<StepGraph> graphs;
+  int32_t *d_seg = nullptr, *h_seg = nullptr, *d_step = nullptr, *d_log = nullptr, *h_log = nullptr;
+  bool use_graph = true, use_pdl = false;
+
+  int32_t* seg(int field) const { return d_seg + size_t(field) * opt.max_batch; }
+
+  void enqueue_step(int batch, int max_kv) {
+    Meta m{};
+    m.ids = seg(0); m.row_req = seg(1); m.row_pos = seg(2); m.kvlens = seg(3); m.slots = seg(4);
+    m.rows = batch; m.batch = batch; m.max_q = 1; m.max_kv = max_kv;
+    run_layers(m);
+    tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
+    ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, last, batch, shape.hidden, 1e-5f, o));
+    gemm(last, head, logits, batch, true, nullptr, false);
+    ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_log, seg(0), d_step, o));
+    ck(tib::advance(seg(2), seg(3), d_step, batch, o));
+  }
+
+  cudaGraphExec_t step_graph(int batch, int chunks) {
+    for (const StepGraph& g : graphs) if (g.batch == batch && g.chunks == chunks) return g.exec;
+    cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
+    ck(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    try { enqueue_step(batch, chunks * kDecodeChunk); }
+    catch (...) { cudaStreamEndCapture(stream, &graph); if (graph) cudaGraphDestroy(graph); throw; }
+    ck(cudaStreamEndCapture(stream, &graph));
+    const cudaError_t st = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    ck(st);
+    graphs.push_back({batch, chunks, exec});
+    return exec;
+  }
+
+  // Runs `steps` greedy steps for the requests in ss, starting from input ids `first`; the ids
+  // produced land in h_log[step * batch + request] once finish() has returned.  Does not touch
+  // `lengths` (the caller advances them) but reserves the pages the steps will write.
+  // before / after, when given, are recorded around the steps on the model's stream.
+  void enqueue_segment(const std::vector<int32_t>& ss, const int32_t* first, int steps, cudaEvent_t before = nullptr,
+                       cudaEvent_t after = nullptr) {
+    const int batch = int(ss.size()), mb = opt.max_batch;
+    int max_kv = 0;
+    for (int b = 0; b < batch; ++b) {
+      const int s = ss[size_t(b)], start = lengths[size_t(s)];
+      reserve(s, start + steps);
+      h_seg[b] = first[b]; h_seg[mb + b] = b; h_seg[2 * mb + b] = start; h_seg[3 * mb + b] = start + 1; h_seg[4 * mb + b] = s;
+      max_kv = std::max(max_kv, start + steps);
+    }
+    upload_table();
+    ck(cudaMemcpyAsync(d_seg, h_seg, size_t(5) * mb * sizeof(int32_t), cudaMemcpyHostToDevice, stream));
+    ck(cudaMemsetAsync(d_step, 0, sizeof(int32_t), stream));
+    int chunks = 1;
+    while (chunks * kDecodeChunk < max_kv) chunks *= 2;            // few distinct graphs: 1, 2, 4, 8 chunks
+    if (before) ck(cudaEventRecord(before, stream));
+    if (use_graph) {
+      cudaGraphExec_t exec = step_graph(batch, chunks);
+      for (int i = 0; i < steps; ++i) ck(cudaGraphLaunch(exec, stream));
+    } else {
+      for (int i = 0; i < steps; ++i) enqueue_step(batch, chunks * kDecodeChunk);
+    }
+    if (after) ck(cudaEventRecord(after, stream));
+    ck(cudaMemcpyAsync(h_log, d_log, size_t(steps) * batch * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    for (int i = 0; i < steps; ++i) { count_pass(); count_head(true); }
+  }
+
+  // ------------------------------------------------------------ ABI bodies
   void forward(const int32_t* s, const int32_t* tokens, const int32_t* lens, int batch, int stride, float* out, int32_t* greedy,
                bool internal = false) {
     ensure_usable();
@@ -270,31 +375,42 @@ struct ti_llm_model {
       throw InvalidInput("invalid batch/host pointers/stride");
     std::vector<int32_t> ss(s, s + batch), ll(lens, lens + batch), packed;
     std::vector<char> used(size_t(opt.cache_slots) + 1, 0);
+    bool single = true;
     for (int b = 0; b < batch; ++b) {
       const int slot = s[b], n = lens[b];
       if (slot < 0 || slot >= opt.cache_slots + (internal ? 1 : 0) || used[size_t(slot)] || n < 1 || n > stride ||
           lengths[size_t(slot)] + n > opt.capacity)
         throw InvalidInput("duplicate/invalid slot, length or capacity");
-      used[size_t(slot)] = 1;
+      used[size_t(slot)] = 1; single = single && n == 1;
       for (int t = 0; t < n; ++t) {
         const int32_t id = tokens[size_t(b) * stride + t];
         if (id < 0 || id >= shape.vocab) throw InvalidInput("token ID outside GPT-2 vocabulary");
         packed.push_back(id);
       }
     }
-    transform(ss, packed, ll, false);
-    tib::LaunchOpts o; o.stream = stream;
-    if (out || greedy) {
-      ++trace.lm_head; gemm(last, head, logits, batch, true, nullptr, false);
+    if (single && greedy) {
+      // One token per request and the argmax wanted: one device-resident step.
+      enqueue_segment(ss, packed.data(), 1);
       if (out) ck(cudaMemcpy2DAsync(out, size_t(shape.vocab) * 4, logits, size_t(vpitch) * 4, size_t(shape.vocab) * 4, size_t(batch),
                                     cudaMemcpyDeviceToHost, stream));
-      if (greedy) {
-        ++trace.argmax; ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_next, nullptr, o));
-        ck(cudaMemcpyAsync(h_next, d_next, size_t(batch) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+      finish();
+      std::memcpy(greedy, h_log, size_t(batch) * sizeof(int32_t));
+    } else {
+      transform(ss, packed, ll, false);
+      tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
+      if (out || greedy) {
+        count_head(greedy != nullptr);
+        gemm(last, head, logits, batch, true, nullptr, false);
+        if (out) ck(cudaMemcpy2DAsync(out, size_t(shape.vocab) * 4, logits, size_t(vpitch) * 4, size_t(shape.vocab) * 4, size_t(batch),
+                                      cudaMemcpyDeviceToHost, stream));
+        if (greedy) {
+          ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_next, nullptr, nullptr, o));
+          ck(cudaMemcpyAsync(h_next, d_next, size_t(batch) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+        }
       }
+      finish();
+      if (greedy) std::memcpy(greedy, h_next, size_t(batch) * sizeof(int32_t));
     }
-    finish();
-    if (greedy) std::memcpy(greedy, h_next, size_t(batch) * sizeof(int32_t));
     for (int b = 0; b < batch; ++b) lengths[size_t(s[b])] += lens[b];
   }
 };
@@ -428,23 +544,60 @@ int ti_llm_greedy_batch(ti_llm_model* m, const int32_t* slots, const int32_t* pr
       if (ttft) ttft[i] = first;
       if (total && requested[i] == 1) total[i] = first;
     }
-    std::vector<int32_t> live_slots, live_ids, ones, owner, fresh;
+    // Decode in device-resident segments: each runs until the next request has all its tokens,
+    // with one host round trip per segment instead of one per token.
+    std::vector<int32_t> live_slots, live_ids, owner;
     for (;;) {
       live_slots.clear(); live_ids.clear(); owner.clear();
+      int steps = m->opt.capacity;
       for (int i = 0; i < batch; ++i)
-        if (produced[size_t(i)] < requested[i]) { live_slots.push_back(slots[i]); live_ids.push_back(next[size_t(i)]); owner.push_back(i); }
+        if (produced[size_t(i)] < requested[i]) {
+          live_slots.push_back(slots[i]); live_ids.push_back(next[size_t(i)]); owner.push_back(i);
+          steps = std::min(steps, requested[i] - produced[size_t(i)]);
+        }
       if (owner.empty()) break;
-      ones.assign(owner.size(), 1); fresh.resize(owner.size());
-      m->forward(live_slots.data(), live_ids.data(), ones.data(), int(owner.size()), 1, nullptr, fresh.data());
+      m->enqueue_segment(live_slots, live_ids.data(), steps);
+      m->finish();
       const double now = elapsed_ms(start);
-      for (size_t j = 0; j < owner.size(); ++j) {
+      const size_t n = owner.size();
+      for (size_t j = 0; j < n; ++j) {
         const int i = owner[j];
-        next[size_t(i)] = fresh[j];
-        output[size_t(i) * out_stride + produced[size_t(i)]++] = fresh[j];
+        for (int t = 0; t < steps; ++t) output[size_t(i) * out_stride + produced[size_t(i)] + t] = m->h_log[size_t(t) * n + j];
+        next[size_t(i)] = m->h_log[size_t(steps - 1) * n + j];
+        produced[size_t(i)] += steps;
+        m->lengths[size_t(slots[i])] += steps;
         if (total && produced[size_t(i)] == requested[i]) total[i] = now;
       }
     }
     if (output_lengths) for (int i = 0; i < batch; ++i) output_lengths[i] = produced[size_t(i)];
+  });
+}
+
+// Declared in include/tinyinfer_b200_ext.h: `steps` greedy steps with every intermediate on the GPU.
+int ti_b200_llm_decode_steps(ti_llm_model* m, const int32_t* slots, const int32_t* first_tokens, int32_t batch, int32_t steps,
+                             int32_t* out_tokens, double* device_ms) {
+  return guarded(m, [&] {
+    if (!slots || !first_tokens || batch < 1 || batch > m->opt.max_batch || steps < 1) throw InvalidInput("invalid decode-steps arguments");
+    std::vector<char> used(size_t(m->opt.cache_slots), 0);
+    for (int i = 0; i < batch; ++i) {
+      const int s = slots[i];
+      if (s < 0 || s >= m->opt.cache_slots || used[size_t(s)] || m->lengths[size_t(s)] < 1 || m->lengths[size_t(s)] + steps > m->opt.capacity ||
+          first_tokens[i] < 0 || first_tokens[i] >= m->shape.vocab)
+        throw InvalidInput("decode steps need distinct prefilled slots, room for the steps and valid ids");
+      used[size_t(s)] = 1;
+    }
+    cudaEvent_t before = nullptr, after = nullptr;
+    ck(cudaEventCreate(&before)); ck(cudaEventCreate(&after));
+    try {
+      m->enqueue_segment(std::vector<int32_t>(slots, slots + batch), first_tokens, steps, before, after);
+      m->finish();
+      float ms = 0.f;
+      ck(cudaEventElapsedTime(&ms, before, after));
+      if (device_ms) *device_ms = double(ms);
+    } catch (...) { cudaEventDestroy(before); cudaEventDestroy(after); throw; }
+    cudaEventDestroy(before); cudaEventDestroy(after);
+    if (out_tokens) std::memcpy(out_tokens, m->h_log, size_t(steps) * batch * sizeof(int32_t));
+    for (int i = 0; i < batch; ++i) m->lengths[size_t(slots[i])] += steps;
   });
 }
 
@@ -466,7 +619,7 @@ int ti_llm_score_window(ti_llm_model* m, const int32_t* tokens, const uint8_t* m
     ck(cudaMemsetAsync(m->d_loss, 0, size_t(length) * sizeof(double), m->stream));
     for (int row = 0; row < rows; row += kScoreRows) {
       const int n = std::min(kScoreRows, rows - row);
-      ++m->trace.lm_head;
+      m->count_head(false);
       m->gemm(static_cast<const uint16_t*>(m->norm) + size_t(row) * H, m->head, m->logits, n, true, nullptr, false);
       ++m->trace.nll;
       ck(tib::nll_rows(m->logits, m->vpitch, n, m->shape.vocab, m->d_score_tokens, m->d_score_mask, m->d_loss, row + 1, m->stream));

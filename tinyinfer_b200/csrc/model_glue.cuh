@@ -48,10 +48,10 @@ kv_scatter_kernel(const __half* qkv, const int32_t* row_req, const int32_t* row_
 }
 
 // Greedy argmax of fp32 logits, lowest id on ties (reference argmax, llm/src/runtime.cu:59-66).
-// grid = rows, block = 256.  Also stores the winner as the next step's input id when
-// `feedback` is non-null.
+// grid = rows, block = 256.  The winner of row r goes to out[(*step) * rows + r] (step = 0 when
+// `step` is null) and, when `feedback` is non-null, to feedback[r] as the next step's input id.
 __global__ void __launch_bounds__(256)
-argmax_kernel(const float* logits, long long pitch, int cols, int32_t* out, int32_t* feedback) {
+argmax_kernel(const float* logits, long long pitch, int cols, int32_t* out, int32_t* feedback, const int32_t* step) {
   __shared__ float best_v[8];
   __shared__ int best_i[8];
   pdl_wait();
@@ -73,9 +73,18 @@ argmax_kernel(const float* logits, long long pitch, int cols, int32_t* out, int3
   if (threadIdx.x == 0) {
     for (int w = 1; w < 8; ++w)
       if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
-    out[blockIdx.x] = bi;
+    out[(step ? size_t(*step) * gridDim.x : 0) + blockIdx.x] = bi;
     if (feedback) feedback[blockIdx.x] = bi;
   }
+}
+
+// End of a device-resident decode step: every request moves one position on.
+__global__ void advance_kernel(int32_t* row_pos, int32_t* kv_lengths, int32_t* step, int batch) {
+  pdl_wait();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < batch) { row_pos[b] += 1; kv_lengths[b] += 1; }
+  if (b == 0) *step += 1;
+  pdl_launch_dependents();
 }
 
 // Teacher-forced NLL of `rows` logit rows in FP64 (reference nll_rows, llm/src/runtime.cu:67-76):
