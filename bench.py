@@ -140,64 +140,78 @@ def reference_main(args, rank):
 
 
 # ---------------------------------------------------------------------------- GPU arm
-def time_kernel(fn, iters=30, warm=5):
+def graph_seconds(enqueue, launches, replays=10):
+    """Device seconds per kernel launch: `enqueue()` issues `launches` kernels on the current stream
+    through the raw C ABI; they are captured into a CUDA graph once and the graph is replayed, so no
+    host work sits between launches and the CUDA events time the GPU alone."""
     import torch
-    for _ in range(warm):
-        fn()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        enqueue()                                   # first call: function attributes, tensor-map driver entry
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        enqueue()
+    graph.replay()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(iters):
-        fn()
+    for _ in range(replays):
+        graph.replay()
     stop.record()
     torch.cuda.synchronize()
-    return start.elapsed_time(stop) / iters * 1e-3
+    return start.elapsed_time(stop) * 1e-3 / (replays * launches)
 
 
 def kernel_rooflines(cached, peak):
-    """The two kernel families that carry most of a step's bytes, timed alone on the step's shapes
-    (operator ABI, torch current stream, inputs far larger than L2 are cycled to defeat caching)."""
+    """The kernel families that carry a decode step's bytes, timed alone on the step's shapes.  Each
+    round walks distinct buffers totalling more than the 126 MB L2, so every launch streams from HBM
+    as it does inside a real step (where ~0.5 GB passes between two uses of the same weights)."""
     import torch
     from tinyinfer_b200.native_ops import NativeOps
     ops = NativeOps()
+    lib, dev = ops.lib, torch.cuda.current_device()
     out = {}
-    g = torch.Generator().manual_seed(1)
-    # decode attention over the ragged histories of one layer, distinct K/V per call (12 "layers")
-    kmax = max(cached) + 1
-    q = torch.randn((BATCH, 12, 1, 64), generator=g).half().cuda()
-    ks = [torch.randn((BATCH, 12, kmax, 64), device="cuda", dtype=torch.float16) for _ in range(12)]
-    vs = [torch.randn((BATCH, 12, kmax, 64), device="cuda", dtype=torch.float16) for _ in range(12)]
-    lengths = [t + 1 for t in cached]
-    state = {"i": 0}
+    stream = lambda: torch.cuda.current_stream().cuda_stream
+
+    def check(status):
+        if status:
+            raise RuntimeError(lib.ti_v2_last_error().decode())
+
+    # decode attention over the ragged histories, one launch per "layer" with its own K/V
+    kmax, layers = max(cached) + 1, 12
+    lengths = torch.tensor([t + 1 for t in cached], dtype=torch.int32, device="cuda")
+    q = torch.randn((BATCH, 12, 1, 64), device="cuda").half()
+    y = torch.empty_like(q)
+    kv = [(torch.randn((BATCH, 12, kmax, 64), device="cuda", dtype=torch.float16), torch.randn((BATCH, 12, kmax, 64), device="cuda", dtype=torch.float16))
+          for _ in range(layers)]
+    floats = lib.ti_b200_attention_decode_scratch_floats(BATCH, 12, kmax, 128)
+    scratch = torch.empty(floats, dtype=torch.float32, device="cuda")
     def attn():
-        i = state["i"] = (state["i"] + 1) % 12
-        ops.attention_decode(q, ks[i], vs[i], lengths, chunk=128)
-    seconds = time_kernel(attn)
-    nbytes = sum(lengths) * 12 * 64 * 2 * 2 + BATCH * 12 * 64 * 2 * 2
-    out["attention_decode (1 layer, 32 ragged requests)"] = {"seconds": seconds, "bytes": nbytes, "launches_per_step": 12}
-    del ks, vs
-    # lm_head GEMV, M = 32 (weights 38.6 MB, re-pitched to 50304 columns as the runtime does)
-    a = torch.randn((BATCH, 768), generator=g).half().cuda()
-    ws = [torch.randint(-127, 128, (768, 50304), dtype=torch.int8, device="cuda") for _ in range(6)]
-    s = (torch.rand(50304, generator=g) * 0.019 + 0.001).cuda()
-    def head():
-        i = state["i"] = (state["i"] + 1) % 6
-        ops.gemm_int8(a, ws[i], s, output_dtype=torch.float32)
-    seconds = time_kernel(head)
-    out["gemv_int8 lm_head (M=32, 768x50304)"] = {"seconds": seconds, "bytes": 768 * 50304 + 4 * 50304 + 2 * BATCH * 768 + 4 * BATCH * 50304,
-                                               "launches_per_step": 1}
-    del ws
-    # the four per-layer GEMVs, M = 32, one layer's worth of distinct weights per call
-    shapes = [(768, 2304), (768, 768), (768, 3072), (3072, 768)]
-    layers = [[(torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda"), (torch.rand(n, device="cuda") * 0.019 + 0.001),
-                torch.randn((BATCH, k), device="cuda").half()) for k, n in shapes] for _ in range(12)]
-    def block():
-        i = state["i"] = (state["i"] + 1) % 12
-        for w, sc, act in layers[i]:
-            ops.gemm_int8(act, w, sc)
-    seconds = time_kernel(block)
-    nbytes = sum(k * n + 4 * n + 2 * BATCH * k + 2 * BATCH * n for k, n in shapes)
-    out["gemv_int8 x4 of one layer (M=32)"] = {"seconds": seconds, "bytes": nbytes, "launches_per_step": 12}
+        for k, v in kv:
+            check(lib.ti_b200_attention_decode_f16(q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), lengths.data_ptr(), BATCH, 12, kmax, 64, 128,
+                                                   scratch.data_ptr(), floats, stream(), dev))
+    seconds = graph_seconds(attn, layers)
+    nbytes = int(lengths.sum().item()) * 12 * 64 * 2 * 2 + BATCH * 12 * 64 * 2 * 2
+    out["attention_decode (1 layer: 32 ragged requests x 12 heads)"] = {"seconds": seconds, "bytes": nbytes, "launches_per_step": 12}
+    del kv
+
+    def gemm_family(name, shapes, sets, fp32, per_step):
+        groups = [[(torch.randn((BATCH, k), device="cuda").half(), torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda"),
+                    torch.rand(n, device="cuda") * 0.019 + 0.001, torch.zeros(n, device="cuda", dtype=torch.float16),
+                    torch.empty((BATCH, n), device="cuda", dtype=torch.float32 if fp32 else torch.float16), k, n) for k, n in shapes]
+                  for _ in range(sets)]
+        def run():
+            for group in groups:
+                for a, w, sc, bias, yy, k, n in group:
+                    check(lib.ti_v2_gemm_ex_i8(a.data_ptr(), w.data_ptr(), sc.data_ptr(), bias.data_ptr(), yy.data_ptr(), None, BATCH, n, k, int(fp32), 0,
+                                               stream(), dev))
+        seconds = graph_seconds(run, sets * len(shapes)) * len(shapes)
+        nbytes = sum(k * n + 4 * n + 2 * n + 2 * BATCH * k + (4 if fp32 else 2) * BATCH * n for k, n in shapes)
+        out[name] = {"seconds": seconds, "bytes": nbytes, "launches_per_step": per_step}
+
+    gemm_family("gemm_int8 lm_head (M=32, 768x50304, fp32 out)", [(768, 50304)], 5, True, 1)
+    gemm_family("gemm_int8 x4 of one layer (M=32: qkv, proj, fc, proj2)", [(768, 2304), (768, 768), (768, 3072), (3072, 768)], 30, False, 12)
     for v in out.values():
         v["gbs"] = v["bytes"] / v["seconds"] / 1e9
         v["frac"] = v["gbs"] / peak
@@ -278,6 +292,11 @@ def gpu_main(args, rank, world):
         launches_per_step = 1 + 12 * (8 + (1 if chunks > 1 else 0)) + 4
         step_gbs = total_bytes / (device_ms * 1e-3) / 1e9
 
+        if args.quick:
+            if rank == 0:
+                print(json.dumps({"metric": "int8_gpt2_decode_tokens_per_s", "value": value, "unit": "tokens/s", "steps": K, "warmup": W,
+                                  "ms_per_step": device_ms / K, "gpu_launches": launches_per_step * K, "quick": True}))
+            return
         # ---- e2e: per-step reference-facing call, host ids in, host ids out ----------------------
         first, _ = prefill()
         ids = first
@@ -332,6 +351,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=7)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    parser.add_argument("--quick", action="store_true", help="only the device-resident timed steps (for profilers)")
     args = parser.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     if args.impl == "reference":

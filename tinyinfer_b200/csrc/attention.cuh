@@ -133,7 +133,9 @@ attn_tile_kernel(const AttnArgs p, const KV kv) {
     }
   }
   pdl_launch_dependents();
-  if (qi < p.q_len) {
+  // Padded layout: rows past the request's length are written as zeros.  Packed rows (row_start
+  // given): a row past the request's length belongs to another request and is left alone.
+  if (p.row_start ? active : qi < p.q_len) {
     __half* o = p.out + o_base + h * p.o_sh + (long long)qi * p.o_si;
 #pragma unroll
     for (int z = 0; z < D / 32; ++z) o[lane + 32 * z] = f2h(l > 0.f ? acc[z] / l : 0.f);

@@ -1,0 +1,264 @@
+// INT8-weight GEMM on the sm_100a tensor cores (tcgen05.mma, accumulators in tensor memory).
+//
+//   out[M,N] = A[M,K] (fp16) . fp16_rn(float(W[K,N]) * scale[N]) + bias[N]      (fp32 accumulate)
+//
+// Used from 5 rows of A upwards: at decode batch sizes it keeps the kernel HBM-bound where SIMT
+// FMAs would not (32 FMAs per weight byte), at prefill sizes it is the dense contraction.
+//
+// The problem is run transposed so that the 128 output channels of a CTA are the 128 TMEM lanes:
+//   D[n, m] += Wt[n, k] * At[k, m]      MMA shape M=128 (channels) x N=NMMA (rows of A) x K=16
+//   * A-operand: the weight tile, dequantised by CUDA cores into fp16 in shared memory, MN-major
+//     (channel-contiguous, exactly how W is stored), no swizzle: 8(k) x 8(n) core matrices of 128 B;
+//   * B-operand: NMMA rows of A, K-major, no swizzle;
+//   * D: fp32, NMMA columns of tensor memory, read back with tcgen05.ld by 4 warps.
+//
+// Pipeline of one CTA (192 threads, 2 CTAs per SM at NMMA = 32):
+//   warp 0      TMA producer: int8 tiles 64(k) x 128(n) -> ring of 4 raw stages (128-byte swizzle so the
+//               dequantisers' 16-byte column reads are bank-conflict free);
+//   warps 2-5   dequantise raw stage -> fp16 operand stage (ring of 3), copy the matching 64 columns of
+//               A next to it, fence.proxy.async, signal;  later: epilogue;
+//   warp 1      owns the TMEM allocation; one lane issues 4 tcgen05.mma per stage and commits to the
+//               barrier that releases the operand stage; a last commit publishes the accumulator.
+// K can be split over a cluster of up to 8 CTAs (NMMA <= 64); partial tiles are reduced through
+// distributed shared memory in rank order, like the SIMT kernel.  Every wait is bounded.
+#pragma once
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_simt.cuh"
+
+namespace tib {
+
+constexpr int kTcThreads = 192;
+constexpr int kTcStageK = 64;
+constexpr int kTcRawStages = 4;
+constexpr int kTcOpStages = 3;
+constexpr int kTcRawBytes = kTcStageK * 128;          // int8 tile
+constexpr int kTcOpABytes = 128 * kTcStageK * 2;      // fp16 weight tile
+
+template <int NMMA> struct TcSmem {
+  static constexpr int kOpBBytes = NMMA * kTcStageK * 2;
+  static constexpr int kRawOff = 0;                                        // 1024-aligned (TMA swizzle)
+  static constexpr int kOpAOff = kRawOff + kTcRawStages * kTcRawBytes;
+  static constexpr int kOpBOff = kOpAOff + kTcOpStages * kTcOpABytes;
+  static constexpr int kBarOff = kOpBOff + kTcOpStages * kOpBBytes;
+  static constexpr int kBytes = kBarOff + 128 + 1024;                      // barriers + slack for manual 1024 alignment
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tmem_alloc(uint32_t* slot, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t address, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+// Shared-memory matrix descriptor, no swizzle: start address, leading / stride byte offsets (16-byte
+// units), descriptor version 1.
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  return uint64_t((smem_addr >> 4) & 0x3fffu) | (uint64_t((lbo_bytes >> 4) & 0x3fffu) << 16) |
+         (uint64_t((sbo_bytes >> 4) & 0x3fffu) << 32) | (uint64_t(1) << 46);
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns -> 32 registers per thread (thread i of the warp = lane base + i).
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// grid = (N / 128 slabs, k splits [cluster y], M / NMMA tiles), block = 192.
+template <int NMMA>
+__global__ void __launch_bounds__(kTcThreads)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
+  using L = TcSmem<NMMA>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* raw = smem + L::kRawOff;
+  uint8_t* op_a = smem + L::kOpAOff;
+  uint8_t* op_b = smem + L::kOpBOff;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t *raw_full = bars, *raw_empty = bars + 4, *op_full = bars + 8, *op_empty = bars + 11, *acc_ready = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  __shared__ int s_failed;
+
+  cg::cluster_group cluster = cg::this_cluster();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int splits = int(gridDim.y), rank = int(blockIdx.y);
+  const int n0 = blockIdx.x * 128, m0 = blockIdx.z * NMMA;
+  const int k_begin = rank * p.k_chunk, k_end = min(p.k, k_begin + p.k_chunk);
+  const int stages = k_end > k_begin ? (k_end - k_begin + kTcStageK - 1) / kTcStageK : 0;
+  constexpr uint32_t kTmemCols = NMMA < 32 ? 32 : NMMA;
+
+  if (tid == 0) {
+    s_failed = 0;
+    tma_prefetch_desc(&w_map);
+    for (int s = 0; s < kTcRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 4); }
+    for (int s = 0; s < kTcOpStages; ++s) { mbar_init(&op_full[s], 4); mbar_init(&op_empty[s], 1); }
+    mbar_init(acc_ready, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (weights only: no dependency wait)
+    if (lane == 0) {
+      bool ok = true;
+      for (int i = 0; i < stages && ok; ++i) {
+        const int slot = i % kTcRawStages;
+        const uint32_t phase = uint32_t(i / kTcRawStages) & 1u;
+        ok = mbar_wait(&raw_empty[slot], phase ^ 1u, kStatusPipeTimeout);     // first round passes immediately
+        if (!ok) break;
+        mbar_expect_tx(&raw_full[slot], kTcRawBytes);
+        tma_load_2d(raw + slot * kTcRawBytes, &w_map, n0, k_begin + i * kTcStageK, &raw_full[slot]);
+      }
+      if (!ok) s_failed = 1;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 15) | (uint32_t(NMMA >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+      // weight tile, MN-major: 8-channel groups are 128 B apart (stride offset), 8-k groups 2048 B apart (leading offset)
+      constexpr uint32_t a_lbo = 2048u, a_sbo = 128u;
+      bool ok = true;
+      for (int i = 0; i < stages && ok; ++i) {
+        const int slot = i % kTcOpStages;
+        ok = mbar_wait(&op_full[slot], uint32_t(i / kTcOpStages) & 1u, kStatusPipeTimeout);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(op_a + slot * kTcOpABytes), b_addr = smem_u32(op_b + slot * L::kOpBBytes);
+#pragma unroll
+        for (int kk = 0; kk < kTcStageK / 16; ++kk) {
+          const uint64_t da = tc_desc(a_addr + kk * 2 * 2048, a_lbo, a_sbo);
+          const uint64_t db = tc_desc(b_addr + kk * 2 * (NMMA / 8) * 128, (NMMA / 8) * 128, 128);
+          tc_mma_f16(tmem_base, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&op_empty[slot]);                 // frees the operand stage when these MMAs have read it
+      }
+      if (ok) tc_commit(acc_ready); else s_failed = 1;
+    }
+  } else {
+    // ------------------------------------------------------------ dequantise + stage A rows (warps 2..5)
+    const int t = tid - 64;                                   // 0..127
+    const int r8 = t & 7, cc = (t >> 3) & 7, kg0 = t >> 6;     // k within 8-group, 16-byte chunk (16 channels), first k-group
+    float sc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { const int col = n0 + cc * 16 + j; sc[j] = col < p.n ? p.scales[col] : 1.f; }
+    pdl_wait();                                               // A comes from the previous kernel
+    bool ok = true;
+    for (int i = 0; i < stages; ++i) {
+      const int rslot = i % kTcRawStages, oslot = i % kTcOpStages;
+      if (ok) ok = mbar_wait(&raw_full[rslot], uint32_t(i / kTcRawStages) & 1u, kStatusTmaTimeout);
+      if (ok) ok = mbar_wait(&op_empty[oslot], (uint32_t(i / kTcOpStages) & 1u) ^ 1u, kStatusMmaTimeout);
+      if (ok) {
+        const uint8_t* src = raw + rslot * kTcRawBytes;
+        uint8_t* dst = op_a + oslot * kTcOpABytes;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int kg = kg0 + 2 * j, krow = kg * 8 + r8;
+          const uint4 q = *reinterpret_cast<const uint4*>(src + krow * 128 + ((cc ^ r8) << 4));
+          const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+          __half2 h[8];
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const int q0 = int(int8_t(words[w] & 0xffu)), q1 = int(int8_t((words[w] >> 8) & 0xffu));
+            const int q2 = int(int8_t((words[w] >> 16) & 0xffu)), q3 = int(int8_t(words[w] >> 24));
+            h[2 * w] = dequant2(q0, q1, sc[4 * w], sc[4 * w + 1]);
+            h[2 * w + 1] = dequant2(q2, q3, sc[4 * w + 2], sc[4 * w + 3]);
+          }
+          uint8_t* core = dst + (kg * 16 + 2 * cc) * 128 + r8 * 16;      // core matrix (k-group, channel-group), row k%8
+          *reinterpret_cast<uint4*>(core) = *reinterpret_cast<const uint4*>(&h[0]);
+          *reinterpret_cast<uint4*>(core + 128) = *reinterpret_cast<const uint4*>(&h[4]);
+        }
+        // the matching 64 columns of A: NMMA rows x 8 chunks of 8 halves, K-major core matrices
+        uint8_t* bdst = op_b + oslot * L::kOpBBytes;
+        const int k0 = k_begin + i * kTcStageK;
+#pragma unroll
+        for (int j = 0; j < NMMA / 16; ++j) {
+          const int id = t + 128 * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
+          const int row = m0 + mg * 8 + m8, kcol = k0 + kc * 8;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (row < p.m && kcol < k_end) v = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + kcol);
+          *reinterpret_cast<uint4*>(bdst + (kc * (NMMA / 8) + mg) * 128 + m8 * 16) = v;
+        }
+        fence_async_smem();                                   // generic-proxy stores -> visible to tcgen05.mma
+      }
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(&raw_empty[rslot]); mbar_arrive(&op_full[oslot]); }
+    }
+    if (!ok) s_failed = 1;
+  }
+  pdl_launch_dependents();
+
+  // ---------------------------------------------------------------- epilogue (warps 2..5 own TMEM lanes 32*(warp%4)..)
+  float* part = reinterpret_cast<float*>(smem);                // [NMMA][128] fp32, aliases the drained pipeline stages
+  bool acc_ok = true;
+  if (warp >= 2) {
+    acc_ok = stages == 0 || mbar_wait(acc_ready, 0, kStatusMmaTimeout);
+    tc_fence_after();
+    const int lane_base = 32 * (warp & 3), n_local = lane_base + lane;
+    const int col = n0 + n_local;
+#pragma unroll 1
+    for (int c0 = 0; c0 < NMMA; c0 += 32) {
+      float v[32];
+      if (acc_ok && stages > 0) tmem_load32(tmem_base + (uint32_t(lane_base) << 16) + uint32_t(c0), v);
+      else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+      if (splits > 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) part[(c0 + i) * 128 + n_local] = v[i];
+      } else if (acc_ok && col < p.n) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { const int row = m0 + c0 + i; if (row < p.m) gemv_store(p, row, col, v[i]); }
+      }
+    }
+    tc_fence_before();
+  }
+  if (splits > 1) {
+    cluster.sync();
+    const bool good = !s_failed;
+    const int cols_per_rank = 128 / splits;
+    for (int i = tid; i < NMMA * cols_per_rank; i += kTcThreads) {
+      const int m = i / cols_per_rank, c = rank * cols_per_rank + (i - m * cols_per_rank);
+      float v = 0.f;
+      for (int r = 0; r < splits; ++r) v += cluster.map_shared_rank(part, r)[m * 128 + c];
+      const int row = m0 + m, col = n0 + c;
+      if (row < p.m && col < p.n && good) gemv_store(p, row, col, v);
+    }
+    cluster.sync();
+  } else {
+    __syncthreads();
+  }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+}
+
+}  // namespace tib

@@ -4,6 +4,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -15,6 +16,7 @@ namespace tib { __device__ unsigned int g_device_status = 0; }
 #include "common.cuh"
 #include "elementwise.cuh"
 #include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
 #include "model_glue.cuh"
 
 namespace tib {
@@ -55,7 +57,7 @@ EncodeTiledFn encode_tiled() {
 
 // 2-D map over a row-major [rows, cols] matrix with `pitch` elements per row; box = (box_cols, box_rows).
 bool make_map_2d(CUtensorMap* map, const void* base, bool int8, uint64_t rows, uint64_t cols, uint64_t pitch,
-                 uint32_t box_cols, uint32_t box_rows) {
+                 uint32_t box_cols, uint32_t box_rows, bool swizzle128 = false) {
   const uint64_t esize = int8 ? 1 : 2;
   if (!encode_tiled() || reinterpret_cast<uintptr_t>(base) % 16 || (pitch * esize) % 16 || pitch * esize >= (1ull << 40) ||
       rows == 0 || cols == 0 || rows > 0xffffffffull || cols > 0xffffffffull)
@@ -64,7 +66,7 @@ bool make_map_2d(CUtensorMap* map, const void* base, bool int8, uint64_t rows, u
   const cuuint32_t box[2] = {box_cols, box_rows}, estr[2] = {1, 1};
   return encode_tiled()(map, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -93,6 +95,18 @@ cudaError_t launch_gemv_mt(int mt, const CUtensorMap& map, const GemvArgs& args,
   }
 }
 
+template <int NMMA>
+cudaError_t launch_tc(const CUtensorMap& map, const GemvArgs& args, dim3 grid, const LaunchOpts& o) {
+  static cudaError_t once = allow_smem(gemm_tc_kernel<NMMA>, TcSmem<NMMA>::kBytes);
+  if (once != cudaSuccess) return once;
+  return launch(gemm_tc_kernel<NMMA>, grid, dim3(kTcThreads), TcSmem<NMMA>::kBytes, o, int(grid.y), map, args);
+}
+
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return v ? std::atoi(v) : fallback;
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------- GEMM
@@ -102,6 +116,27 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   a.out = c.out; a.residual = static_cast<const __half*>(c.residual);
   a.lda = c.lda; a.ldo = c.ldo; a.ldw = c.ldw; a.m = c.m; a.n = c.n; a.k = c.k;
   a.out_fp32 = c.out_fp32; a.gelu = c.gelu;
+  // Tensor-core path: int8 weights, 5 or more rows of A, operands addressable by TMA / 16-byte loads.
+  static const int tc_min_rows = env_int("TINYINFER_B200_TC_MIN_ROWS", 5);      // measurement aid: where the SIMT kernel hands over
+  if (c.w_int8 && c.m >= tc_min_rows && c.k % 8 == 0 && c.lda % 8 == 0 && reinterpret_cast<uintptr_t>(c.a) % 16 == 0) {
+    CUtensorMap map; std::memset(&map, 0, sizeof map);
+    if (make_map_2d(&map, c.w, true, uint64_t(c.k), uint64_t(c.n), uint64_t(c.ldw), 128, uint32_t(kTcStageK), true)) {
+      const int nmma = c.m <= 32 ? 32 : c.m <= 64 ? 64 : c.m <= 128 ? 128 : 256;
+      const int slabs = (c.n + 127) / 128, m_tiles = (c.m + nmma - 1) / nmma;
+      int splits = 1;
+      if (nmma <= 64)
+        while (splits < 8 && slabs * m_tiles * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= 2 * kTcStageK) splits *= 2;
+      int chunk = (c.k + splits - 1) / splits;
+      a.k_chunk = (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
+      const dim3 grid(slabs, splits, m_tiles);
+      switch (nmma) {
+        case 32: return launch_tc<32>(map, a, grid, o);
+        case 64: return launch_tc<64>(map, a, grid, o);
+        case 128: return launch_tc<128>(map, a, grid, o);
+        default: return launch_tc<256>(map, a, grid, o);
+      }
+    }
+  }
   const int bn = c.w_int8 ? 128 : 64;
   const int mt = c.m >= 3 ? 4 : c.m;
   const int slabs = (c.n + bn - 1) / bn, m_tiles = (c.m + mt - 1) / mt;
