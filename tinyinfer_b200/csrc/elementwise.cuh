@@ -25,40 +25,80 @@ __device__ __forceinline__ float tree256(float (&v)[8]) {
   return __shfl_sync(0xffffffffu, x, 0);
 }
 
-// Mean and 1/sqrt(var+eps) of one row, by one warp (reference norm, elementwise.cu:15-24).
-__device__ __forceinline__ void row_stats(const __half* x, int cols, float eps, float& mean, float& inv) {
+// Mean and 1/sqrt(var+eps) of one row held in shared memory as fp32, by one warp (reference norm,
+// elementwise.cu:15-24).  Reading from shared memory keeps the replayed summation order cheap: the
+// 2 x cols/32 dependent adds of a lane wait on ~30-cycle loads instead of DRAM round trips.
+__device__ __forceinline__ void row_stats(const float* x, int cols, float eps, float& mean, float& inv) {
   const int lane = threadIdx.x & 31;
   float v[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     float s = 0.f;
-    for (int c = lane + 32 * j; c < cols; c += 256) s += h2f(x[c]);
+    for (int c = lane + 32 * j; c < cols; c += 256) s += x[c];
     v[j] = s;
   }
   mean = tree256(v) / cols;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     float s = 0.f;
-    for (int c = lane + 32 * j; c < cols; c += 256) { const float z = h2f(x[c]) - mean; s += z * z; }
+    for (int c = lane + 32 * j; c < cols; c += 256) { const float z = x[c] - mean; s += z * z; }
     v[j] = s;
   }
   inv = rsqrtf(tree256(v) / cols + eps);
 }
 
-// grid = ceil(rows / 4), block = 128: one warp per row.
+// One warp copies a row of `cols` halves into shared memory as fp32 (independent, coalesced loads).
+__device__ __forceinline__ void stage_row(const __half* x, float* dst, int cols) {
+  const int lane = threadIdx.x & 31;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (cols & 7) == 0) {
+    for (int c = lane * 8; c < cols; c += 256) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(x + c);
+      const __half* h = reinterpret_cast<const __half*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dst[c + e] = h2f(h[e]);
+    }
+  } else {
+#pragma unroll 4
+    for (int c = lane; c < cols; c += 32) dst[c] = h2f(x[c]);
+  }
+  __syncwarp();
+}
+
+constexpr int kLnMaxCols = 4096;     // rows up to this width are staged in shared memory (16 KB per warp)
+
+// grid = ceil(rows / 4), block = 128: one warp per row; dynamic shared memory 4 * min(cols, kLnMaxCols) floats.
 __global__ void __launch_bounds__(128)
 layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, const __half* b, __half* y,
                  int rows, int cols, float eps) {
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  extern __shared__ float ln_rows[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x * 4 + warp;
   pdl_wait();
   if (row >= rows) return;
   const __half* xr = x + size_t(row_index ? row_index[row] : row) * cols;   // optional gather of input rows
   __half* yr = y + size_t(row) * cols;
   float mean, inv;
-  row_stats(xr, cols, eps, mean, inv);
-  pdl_launch_dependents();
-  for (int c = lane; c < cols; c += 32)
-    yr[c] = f2h((h2f(xr[c]) - mean) * inv * h2f(g[c]) + h2f(b[c]));
+  if (cols <= kLnMaxCols) {
+    float* xs = ln_rows + size_t(warp) * cols;
+    stage_row(xr, xs, cols);
+    row_stats(xs, cols, eps, mean, inv);
+    pdl_launch_dependents();
+    for (int c = lane; c < cols; c += 32) yr[c] = f2h((xs[c] - mean) * inv * h2f(g[c]) + h2f(b[c]));
+  } else {
+    // very wide rows: same arithmetic straight from global memory
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { float s = 0.f; for (int c = lane + 32 * j; c < cols; c += 256) s += h2f(xr[c]); v[j] = s; }
+    mean = tree256(v) / cols;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s = 0.f;
+      for (int c = lane + 32 * j; c < cols; c += 256) { const float z = h2f(xr[c]) - mean; s += z * z; }
+      v[j] = s;
+    }
+    inv = rsqrtf(tree256(v) / cols + eps);
+    pdl_launch_dependents();
+    for (int c = lane; c < cols; c += 32) yr[c] = f2h((h2f(xr[c]) - mean) * inv * h2f(g[c]) + h2f(b[c]));
+  }
 }
 
 // Row softmax (reference normalized_exp, elementwise.cu:34-46), one warp per row.

@@ -171,50 +171,83 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     float sc[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) { const int col = n0 + cc * 16 + j; sc[j] = col < p.n ? p.scales[col] : 1.f; }
-    pdl_wait();                                               // A comes from the previous kernel
+    // Weight tile of raw stage -> fp16 A-operand stage (independent of any earlier kernel).
+    auto dequantise = [&](int rslot, int oslot) {
+      const uint8_t* src = raw + rslot * kTcRawBytes;
+      uint8_t* dst = op_a + oslot * kTcOpABytes;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int kg = kg0 + 2 * j, krow = kg * 8 + r8;
+        const uint4 q = *reinterpret_cast<const uint4*>(src + krow * 128 + ((cc ^ r8) << 4));
+        const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+        __half2 h[8];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const int q0 = int(int8_t(words[w] & 0xffu)), q1 = int(int8_t((words[w] >> 8) & 0xffu));
+          const int q2 = int(int8_t((words[w] >> 16) & 0xffu)), q3 = int(int8_t(words[w] >> 24));
+          h[2 * w] = dequant2(q0, q1, sc[4 * w], sc[4 * w + 1]);
+          h[2 * w + 1] = dequant2(q2, q3, sc[4 * w + 2], sc[4 * w + 3]);
+        }
+        uint8_t* core = dst + (kg * 16 + 2 * cc) * 128 + r8 * 16;      // core matrix (k-group, channel-group), row k%8
+        *reinterpret_cast<uint4*>(core) = *reinterpret_cast<const uint4*>(&h[0]);
+        *reinterpret_cast<uint4*>(core + 128) = *reinterpret_cast<const uint4*>(&h[4]);
+      }
+    };
+    // The matching 64 columns of A: NMMA rows x 8 chunks of 8 halves, as K-major core matrices.
+    uint4 a_regs[NMMA / 16];
+    auto fetch_a = [&](int i) {
+      const int k0 = k_begin + i * kTcStageK;
+#pragma unroll
+      for (int j = 0; j < NMMA / 16; ++j) {
+        const int id = t + 128 * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
+        const int row = m0 + mg * 8 + m8, kcol = k0 + kc * 8;
+        a_regs[j] = make_uint4(0, 0, 0, 0);
+        if (row < p.m && kcol < k_end) a_regs[j] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + kcol);
+      }
+    };
+    auto store_a = [&](int oslot) {
+      uint8_t* bdst = op_b + oslot * L::kOpBBytes;
+#pragma unroll
+      for (int j = 0; j < NMMA / 16; ++j) {
+        const int id = t + 128 * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
+        *reinterpret_cast<uint4*>(bdst + (kc * (NMMA / 8) + mg) * 128 + m8 * 16) = a_regs[j];
+      }
+    };
     bool ok = true;
-    for (int i = 0; i < stages; ++i) {
+    // Lead-in: the first operand stages need no release; their weights are dequantised before the
+    // dependency on the previous kernel is resolved, so under programmatic dependent launch this
+    // overlaps the tail of that kernel.
+    const int lead = min(stages, kTcOpStages);
+    for (int i = 0; i < lead; ++i) {
+      if (ok) ok = mbar_wait(&raw_full[i], 0, kStatusTmaTimeout);
+      if (ok) dequantise(i, i);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&raw_empty[i]);
+    }
+    pdl_wait();                                               // A (and the residual) come from the previous kernel
+    for (int i = 0; i < lead; ++i) {
+      fetch_a(i);
+      store_a(i);
+      fence_async_smem();                                     // generic-proxy stores -> visible to tcgen05.mma
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&op_full[i]);
+    }
+    for (int i = lead; i < stages; ++i) {
       const int rslot = i % kTcRawStages, oslot = i % kTcOpStages;
+      fetch_a(i);                                             // in flight while the barriers are awaited
       if (ok) ok = mbar_wait(&raw_full[rslot], uint32_t(i / kTcRawStages) & 1u, kStatusTmaTimeout);
       if (ok) ok = mbar_wait(&op_empty[oslot], (uint32_t(i / kTcOpStages) & 1u) ^ 1u, kStatusMmaTimeout);
       if (ok) {
-        const uint8_t* src = raw + rslot * kTcRawBytes;
-        uint8_t* dst = op_a + oslot * kTcOpABytes;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int kg = kg0 + 2 * j, krow = kg * 8 + r8;
-          const uint4 q = *reinterpret_cast<const uint4*>(src + krow * 128 + ((cc ^ r8) << 4));
-          const uint32_t words[4] = {q.x, q.y, q.z, q.w};
-          __half2 h[8];
-#pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const int q0 = int(int8_t(words[w] & 0xffu)), q1 = int(int8_t((words[w] >> 8) & 0xffu));
-            const int q2 = int(int8_t((words[w] >> 16) & 0xffu)), q3 = int(int8_t(words[w] >> 24));
-            h[2 * w] = dequant2(q0, q1, sc[4 * w], sc[4 * w + 1]);
-            h[2 * w + 1] = dequant2(q2, q3, sc[4 * w + 2], sc[4 * w + 3]);
-          }
-          uint8_t* core = dst + (kg * 16 + 2 * cc) * 128 + r8 * 16;      // core matrix (k-group, channel-group), row k%8
-          *reinterpret_cast<uint4*>(core) = *reinterpret_cast<const uint4*>(&h[0]);
-          *reinterpret_cast<uint4*>(core + 128) = *reinterpret_cast<const uint4*>(&h[4]);
-        }
-        // the matching 64 columns of A: NMMA rows x 8 chunks of 8 halves, K-major core matrices
-        uint8_t* bdst = op_b + oslot * L::kOpBBytes;
-        const int k0 = k_begin + i * kTcStageK;
-#pragma unroll
-        for (int j = 0; j < NMMA / 16; ++j) {
-          const int id = t + 128 * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
-          const int row = m0 + mg * 8 + m8, kcol = k0 + kc * 8;
-          uint4 v = make_uint4(0, 0, 0, 0);
-          if (row < p.m && kcol < k_end) v = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + kcol);
-          *reinterpret_cast<uint4*>(bdst + (kc * (NMMA / 8) + mg) * 128 + m8 * 16) = v;
-        }
-        fence_async_smem();                                   // generic-proxy stores -> visible to tcgen05.mma
+        dequantise(rslot, oslot);
+        store_a(oslot);
+        fence_async_smem();
       }
       __syncwarp();
       if (lane == 0) { mbar_arrive(&raw_empty[rslot]); mbar_arrive(&op_full[oslot]); }
     }
     if (!ok) s_failed = 1;
   }
+  pdl_wait();                 // every thread is past the dependency before the epilogue reads or writes global memory
   pdl_launch_dependents();
 
   // ---------------------------------------------------------------- epilogue (warps 2..5 own TMEM lanes 32*(warp%4)..)

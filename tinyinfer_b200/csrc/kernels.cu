@@ -230,7 +230,12 @@ cudaError_t attention_packed_decode(const void* q, const void* k, const void* v,
 // ---------------------------------------------------------------- elementwise / glue
 cudaError_t layernorm(const void* x, const int32_t* row_index, const void* g, const void* b, void* y, int rows, int cols,
                       float eps, const LaunchOpts& o) {
-  return launch(layernorm_kernel, dim3((rows + 3) / 4), dim3(128), 0, o, 1, static_cast<const __half*>(x), row_index,
+  const size_t smem = cols <= kLnMaxCols ? size_t(4) * cols * sizeof(float) : 0;
+  if (smem > 48 * 1024) {
+    static cudaError_t once = allow_smem(layernorm_kernel, 4 * kLnMaxCols * int(sizeof(float)));
+    if (once != cudaSuccess) return once;
+  }
+  return launch(layernorm_kernel, dim3((rows + 3) / 4), dim3(128), smem, o, 1, static_cast<const __half*>(x), row_index,
                 static_cast<const __half*>(g), static_cast<const __half*>(b), static_cast<__half*>(y), rows, cols, eps);
 }
 cudaError_t gelu(const void* x, void* y, long long count, cudaStream_t stream) {

@@ -306,7 +306,7 @@ struct ti_llm_model {
   struct StepGraph { int batch, chunks; cudaGraphExec_t exec; };
   std::vector<StepGraph> graphs;
   int32_t *d_seg = nullptr, *h_seg = nullptr, *d_step = nullptr, *d_log = nullptr, *h_log = nullptr;
-  bool use_graph = true, use_pdl = false;
+  bool use_graph = true, use_pdl = true;
 
   int32_t* seg(int field) const { return d_seg + size_t(field) * opt.max_batch; }
 
