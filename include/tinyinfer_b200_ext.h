@@ -34,6 +34,20 @@ int ti_b200_attention_decode_f16(const uint16_t* q, const uint16_t* k, const uin
                                  const int32_t* kv_lengths, int batch, int heads, int kv_len, int head_dim,
                                  int chunk, float* scratch, int64_t scratch_floats, uintptr_t stream, int device);
 
+/* No counterpart in the reference.  ti_b200_attention_decode_f16 for callers that cannot allocate
+ * device memory (a serving loop with a fixed memory budget, an operator hosted by a program that
+ * owns all device memory, a process at its memory limit): same inputs, outputs and results, but the
+ * scratch is a fixed 4 MiB array inside the library (ti_b200_attention_decode_static_capacity_floats()
+ * floats; every GPU that loads the library holds it until exit).  Calls no cudaMalloc / cudaFree.
+ * Problems needing more than that (see ti_b200_attention_decode_scratch_floats) are rejected with
+ * TI_V2_INVALID_ARGUMENT.  The first call on a device looks up the array's address; make it during
+ * start-up, before any stream capture on that device.  All calls on a device share the array, so
+ * calls that can overlap on the GPU race: serialise them.  Nothing in the array needs clearing. */
+long long ti_b200_attention_decode_static_capacity_floats(void);
+int ti_b200_attention_decode_static_f16(const uint16_t* q, const uint16_t* k, const uint16_t* v, uint16_t* y,
+                                        const int32_t* kv_lengths, int batch, int heads, int kv_len, int head_dim,
+                                        int chunk, uintptr_t stream, int device);
+
 /* Exported by libtinyinfer_llm.so.  Verifies manifest.json + weights.bin exactly as
  * ti_llm_create does before touching the GPU (reference llm/src/artifact.hpp:153-199; the
  * reference only reaches these checks through ti_llm_create) and reports the model shape.

@@ -50,6 +50,7 @@ def build(force: bool = False, verbose: bool = False) -> dict:
     objects = {
         "kernels": (SRC / "kernels.cu", ARCH + ["-Xptxas", "-v"] if verbose else ARCH),
         "backend_api": (SRC / "backend_api.cpp", []),
+        "attention_static_scratch": (SRC / "attention_static_scratch.cu", ARCH),
         "llm_runtime": (SRC / "llm_runtime.cpp", []),
     }
     jobs = []
@@ -62,15 +63,15 @@ def build(force: bool = False, verbose: bool = False) -> dict:
             if verbose:
                 sys.stderr.write(result.stderr)
     backend, llm, codec = LIB / "libtinyinfer_backend.so", LIB / "libtinyinfer_llm.so", LIB / "libtinyinfer_host_codec.so"
-    if force or _stale(backend, [OBJ / "kernels.o", OBJ / "backend_api.o"]):
-        _run([NVCC, "-shared", "-cudart", "shared", "-Xlinker", "-Bsymbolic", "-o", str(backend), str(OBJ / "kernels.o"),
-              str(OBJ / "backend_api.o")])
+    shared_objects = [OBJ / "kernels.o", OBJ / "backend_api.o", OBJ / "attention_static_scratch.o"]
+    if force or _stale(backend, shared_objects):
+        _run([NVCC, "-shared", "-cudart", "shared", "-Xlinker", "-Bsymbolic", "-o", str(backend), *map(str, shared_objects)])
     # The model library carries its own copy of the kernels instead of depending on the backend
     # library by name: a process may also hold another library called libtinyinfer_backend.so
     # (the parity tests load the reference build), and a by-name dependency would bind to it.
-    if force or _stale(llm, [OBJ / "llm_runtime.o", OBJ / "kernels.o", OBJ / "backend_api.o"]):
+    if force or _stale(llm, [OBJ / "llm_runtime.o", *shared_objects]):
         _run([NVCC, "-shared", "-cudart", "shared", "-Xlinker", "-Bsymbolic", "-o", str(llm), str(OBJ / "llm_runtime.o"),
-              str(OBJ / "kernels.o"), str(OBJ / "backend_api.o")])
+              *map(str, shared_objects)])
     if force or _stale(codec, [SRC / "host_codec.cpp"] + list(INCLUDE.glob("*.h"))):
         _run(["g++", "-std=c++17", "-O2", "-fno-fast-math", "-ffp-contract=off", "-fPIC", "-shared", "-Wall", "-Wextra",
               f"-I{INCLUDE}", "-o", str(codec), str(SRC / "host_codec.cpp")])

@@ -84,6 +84,21 @@ int run_gemm(const uint16_t* a, const void* b, const float* scales, const uint16
 
 }  // namespace
 
+// Helpers shared with attention_static_scratch.cu (same checks, same thread-local error text).
+namespace tib_api {
+int enter_call(int device) { return enter(device); }
+int fail_call(int status, const char* text) { return fail(status, text); }
+int cuda_call(cudaError_t st) { return cuda_result(st); }
+int check_decode_attention(const void* q, const void* k, const void* v, const void* y, const void* kv_lengths, int batch, int heads,
+                           int kv_len, int head_dim, int chunk) {
+  const int kd[4] = {batch, heads, kv_len, head_dim};
+  if (head_dim != 64 || batch > 65535 || heads > 65535 || !extent_ok(kd, 2) || chunk < 32 || chunk % 32 || !aligned_to(q, 16) ||
+      !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(y, 16) || !aligned_to(kv_lengths, 4))
+    return fail(TI_V2_INVALID_ARGUMENT, "invalid decode attention arguments (D=64, chunk multiple of 32, 16-byte aligned tensors)");
+  return TI_V2_OK;
+}
+}  // namespace tib_api
+
 extern "C" {
 
 int ti_v2_abi_version(void) { return 2; }
