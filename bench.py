@@ -284,8 +284,9 @@ def gpu_main(args, rank, world):
                 total_bytes += sum(step_bytes(weights, [t + i for t in lengths_now]) for i in range(n))
                 done += n
         barrier()
-        device_ms = max_over_ranks(device_ms)
-        value = world * BATCH * K / (device_ms * 1e-3)
+        from tinyinfer_b200 import replicas
+        _, slowest_s, value = replicas.job_throughput(BATCH * K, device_ms * 1e-3, dist, "cuda")    # sum of tokens / slowest rank
+        device_ms = slowest_s * 1e3
         chunks = 1
         while chunks * 128 < max(cached_at_start) + K:
             chunks *= 2
