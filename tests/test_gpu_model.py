@@ -203,3 +203,26 @@ def test_validation_errors_and_struct_size(model, manifest):
     assert lib.ti_llm_create(str(manifest).encode(), C.byref(bad), C.byref(handle)) == 1 and not handle
     with pytest.raises(ValueError):
         NativeModel(None, manifest, max_batch=65, cache_slots=65)
+
+
+def test_logits_do_not_depend_on_batch_composition(model):
+    """The reference's batched-vs-single and mixed-greedy gates hold there with difference exactly 0
+    (one kernel serves every M).  Same property here: bit-equal logits alone or in a ragged batch of 9,
+    at prefill and at decode, and identical greedy tokens."""
+    rng = np.random.default_rng(21)
+    prompts = [rng.integers(0, 50257, int(n)).tolist() for n in (3, 70, 1, 33, 128, 17, 64, 5, 200)]
+    model.reset_all()
+    together = logits_of(model.forward(list(range(9)), prompts))
+    step = logits_of(model.forward(list(range(9)), [[int(t)] for t in together.argmax(-1)]))
+    for i in (0, 2, 4, 8):
+        model.reset(20)
+        alone = logits_of(model.forward([20], [prompts[i]]))[0]
+        assert torch.equal(alone, together[i]), f"prefill logits of request {i} depend on the batch"
+        alone_step = logits_of(model.forward([20], [[int(together[i].argmax())]]))[0]
+        assert torch.equal(alone_step, step[i]), f"decode logits of request {i} depend on the batch"
+    model.reset_all()
+    batch_tokens = model.greedy(prompts, [12, 3, 9, 1, 6, 12, 2, 7, 4])["tokens"]
+    for i in (1, 2, 5, 7):
+        model.reset(20)
+        assert model.greedy([prompts[i]], len(batch_tokens[i]), slots=[20])["tokens"][0] == batch_tokens[i]
+    model.reset_all()

@@ -2,7 +2,8 @@
 //
 //   out[M,N] = A[M,K] (fp16) . fp16_rn(float(W[K,N]) * scale[N]) + bias[N]      (fp32 accumulate)
 //
-// Used from 5 rows of A upwards: at decode batch sizes it keeps the kernel HBM-bound where SIMT
+// Used by the operator ABI from 5 rows of A upwards and by the model runtime for every row count
+// (so that a request's logits do not depend on its batch): at decode batch sizes it keeps the kernel HBM-bound where SIMT
 // FMAs would not (32 FMAs per weight byte), at prefill sizes it is the dense contraction.
 //
 // The problem is run transposed so that the 128 output channels of a CTA are the 128 TMEM lanes:
@@ -19,7 +20,7 @@
 //               A next to it, fence.proxy.async, signal;  later: epilogue;
 //   warp 1      owns the TMEM allocation; one lane issues 4 tcgen05.mma per stage and commits to the
 //               barrier that releases the operand stage; a last commit publishes the accumulator.
-// K can be split over a cluster of up to 8 CTAs (NMMA <= 64); partial tiles are reduced through
+// K can be split over a cluster of up to 8 CTAs; partial tiles are reduced through
 // distributed shared memory in rank order, like the SIMT kernel.  Every wait is bounded.
 #pragma once
 #include <cooperative_groups.h>

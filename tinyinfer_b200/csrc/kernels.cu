@@ -118,14 +118,17 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   a.out_fp32 = c.out_fp32; a.gelu = c.gelu;
   // Tensor-core path: int8 weights, 5 or more rows of A, operands addressable by TMA / 16-byte loads.
   static const int tc_min_rows = env_int("TINYINFER_B200_TC_MIN_ROWS", 5);      // measurement aid: where the SIMT kernel hands over
-  if (c.w_int8 && c.m >= tc_min_rows && c.k % 8 == 0 && c.lda % 8 == 0 && reinterpret_cast<uintptr_t>(c.a) % 16 == 0) {
+  // With `uniform_numerics` every row count takes this path, so a row's result does not depend on
+  // how many other rows share the call (the K split below depends on N and K only).
+  if (c.w_int8 && (c.uniform_numerics || c.m >= tc_min_rows) && c.k % 8 == 0 && c.lda % 8 == 0 && reinterpret_cast<uintptr_t>(c.a) % 16 == 0) {
     CUtensorMap map; std::memset(&map, 0, sizeof map);
     if (make_map_2d(&map, c.w, true, uint64_t(c.k), uint64_t(c.n), uint64_t(c.ldw), 128, uint32_t(kTcStageK), true)) {
       const int nmma = c.m <= 32 ? 32 : c.m <= 64 ? 64 : c.m <= 128 ? 128 : 256;
       const int slabs = (c.n + 127) / 128, m_tiles = (c.m + nmma - 1) / nmma;
+      // K split chosen from the matrix alone (never from M): the summation grouping of an output
+      // element is then the same for every batch size and batch composition.
       int splits = 1;
-      if (nmma <= 64)
-        while (splits < 8 && slabs * m_tiles * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= 2 * kTcStageK) splits *= 2;
+      while (splits < 8 && slabs * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= 2 * kTcStageK) splits *= 2;
       int chunk = (c.k + splits - 1) / splits;
       a.k_chunk = (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
       const dim3 grid(slabs, splits, m_tiles);

@@ -28,6 +28,7 @@ struct GemmCall {
   void* out = nullptr; int ldo = 0; bool out_fp32 = false;
   const void* residual = nullptr;                       // fp16 [M,N] pitch ldo, or null
   bool gelu = false;
+  bool uniform_numerics = false;                         // tensor-core kernel for any row count (batch-invariant results)
   int m = 0, n = 0, k = 0;
 };
 TIB_EXPORT cudaError_t gemm(const GemmCall& call, const LaunchOpts& opts);

@@ -206,6 +206,9 @@ struct ti_llm_model {
     c.a = a; c.lda = l.k; c.w = l.w; c.ldw = l.ldw; c.w_int8 = int8; c.scales = l.scales; c.bias = l.bias;
     c.out = out; c.ldo = fp32 ? vpitch : l.n; c.out_fp32 = fp32; c.residual = residual; c.gelu = gelu;
     c.m = rows; c.n = l.n; c.k = l.k;
+    // One kernel family for every batch size: logits of a request are bit-identical whatever it is
+    // batched with, the property the reference's gates rely on (llm/gpu_correctness.py:62-66).
+    c.uniform_numerics = true;
     tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
     ck(tib::gemm(c, o));
   }
