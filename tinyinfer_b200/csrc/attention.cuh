@@ -151,6 +151,8 @@ struct DecodeArgs {
   const int32_t* kv_lengths;                         // visible keys of each request (its new token included)
   float* part_acc;                                   // scratch fp32 [batch][heads][chunks][D]
   float* part_ml;                                    // scratch fp32 [batch][heads][chunks][2]  (max, sum)
+  int* counters;                                     // optional int [batch][heads], all zero between launches: when given, the
+                                                     // last chunk CTA of a (request, head) merges the partials itself
   int batch, heads, chunk, chunks;                   // keys per CTA; grid.x
 };
 
@@ -256,6 +258,34 @@ attn_decode_kernel(const DecodeArgs p, const KV kv) {
       const size_t slot = (size_t(b) * p.heads + h) * p.chunks + blockIdx.x;
       p.part_acc[slot * D + tid] = aa;
       if (tid == 0) { p.part_ml[slot * 2] = mm; p.part_ml[slot * 2 + 1] = ll; }
+    }
+  }
+  if (p.chunks > 1 && p.counters) {
+    // Merge in the CTA that finishes last: partials are published (fence), a ticket is taken, and the
+    // holder of the last ticket reads everybody's partials.  The counter is left at zero again.
+    __shared__ int s_last;
+    const int used = max(1, min(p.chunks, (len + p.chunk - 1) / p.chunk));
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      int* counter = p.counters + b * p.heads + h;
+      s_last = atomicAdd(counter, 1) == used - 1;
+      if (s_last) *counter = 0;
+    }
+    __syncthreads();
+    if (s_last && tid < D) {
+      __threadfence();
+      const size_t base = (size_t(b) * p.heads + h) * p.chunks;
+      float mm = -CUDART_INF_F;
+      for (int c = 0; c < used; ++c) mm = fmaxf(mm, __ldcg(&p.part_ml[(base + c) * 2]));
+      float ll = 0.f, aa = 0.f;
+      for (int c = 0; c < used; ++c) {
+        const float mc = __ldcg(&p.part_ml[(base + c) * 2]);
+        const float f = mc > -CUDART_INF_F ? expf(mc - mm) : 0.f;
+        ll += __ldcg(&p.part_ml[(base + c) * 2 + 1]) * f;
+        aa += __ldcg(&p.part_acc[(base + c) * D + tid]) * f;
+      }
+      p.out[b * p.o_sb + h * p.o_sh + tid] = f2h(ll > 0.f ? aa / ll : 0.f);
     }
   }
 }

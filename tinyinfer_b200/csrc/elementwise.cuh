@@ -66,23 +66,42 @@ __device__ __forceinline__ void stage_row(const __half* x, float* dst, int cols)
 
 constexpr int kLnMaxCols = 4096;     // rows up to this width are staged in shared memory (16 KB per warp)
 
-// grid = ceil(rows / 4), block = 128: one warp per row; dynamic shared memory 4 * min(cols, kLnMaxCols) floats.
+// grid = ceil(rows / 4), block = 128: one warp per row; dynamic shared memory (for cols <= kLnMaxCols):
+// 4 rows of fp32 + gamma and beta as fp16 = 20 * cols bytes.  gamma / beta are parameters, not produced by
+// the previous kernel, so they are staged before the dependency wait and their latency is hidden.
 __global__ void __launch_bounds__(128)
 layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, const __half* b, __half* y,
                  int rows, int cols, float eps) {
   extern __shared__ float ln_rows[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x * 4 + warp;
+  const bool staged = cols <= kLnMaxCols;
+  __half* gs = reinterpret_cast<__half*>(ln_rows + size_t(4) * cols);
+  __half* bs = gs + cols;
+  if (staged) {
+    for (int c = threadIdx.x; c < cols; c += 128) { gs[c] = g[c]; bs[c] = b[c]; }
+    __syncthreads();
+  }
   pdl_wait();
   if (row >= rows) return;
   const __half* xr = x + size_t(row_index ? row_index[row] : row) * cols;   // optional gather of input rows
   __half* yr = y + size_t(row) * cols;
   float mean, inv;
-  if (cols <= kLnMaxCols) {
+  if (staged) {
     float* xs = ln_rows + size_t(warp) * cols;
     stage_row(xr, xs, cols);
     row_stats(xs, cols, eps, mean, inv);
     pdl_launch_dependents();
-    for (int c = lane; c < cols; c += 32) yr[c] = f2h((xs[c] - mean) * inv * h2f(g[c]) + h2f(b[c]));
+    if ((reinterpret_cast<uintptr_t>(yr) & 15) == 0 && (cols & 7) == 0) {
+      for (int c = lane * 8; c < cols; c += 256) {
+        uint4 packed;
+        __half* h = reinterpret_cast<__half*>(&packed);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) h[e] = f2h((xs[c + e] - mean) * inv * h2f(gs[c + e]) + h2f(bs[c + e]));
+        *reinterpret_cast<uint4*>(yr + c) = packed;
+      }
+    } else {
+      for (int c = lane; c < cols; c += 32) yr[c] = f2h((xs[c] - mean) * inv * h2f(gs[c]) + h2f(bs[c]));
+    }
   } else {
     // very wide rows: same arithmetic straight from global memory
     float v[8];

@@ -48,7 +48,20 @@ struct GemvArgs {
   int m, n, k;
   int k_chunk;                // K rows per CTA, multiple of kGemvStageRows
   int out_fp32, gelu;
+  // K/V placement (QKV projection of the model runtime; k_pool null elsewhere): columns at or past
+  // kv_hidden are the K then V thirds and go straight to their position in the paged pool
+  // ([page][layer][head][32][64], see attention.cuh) instead of `out`.
+  __half* k_pool; __half* v_pool;
+  const int32_t* kv_table; const int32_t* kv_slots; const int32_t* kv_row_req; const int32_t* kv_row_pos;
+  int kv_table_pitch, kv_layers, kv_layer, kv_heads, kv_hidden;
 };
+
+// Offset (in halves) of head 0, element 0 of row `row`'s position inside the K / V pool.
+__device__ __forceinline__ long long kv_row_base(const GemvArgs& p, int row) {
+  const int pos = p.kv_row_pos[row];
+  const int page = p.kv_table[size_t(p.kv_slots[p.kv_row_req[row]]) * p.kv_table_pitch + (pos >> 5)];
+  return ((long long)(page) * p.kv_layers + p.kv_layer) * p.kv_heads * 2048 + (pos & 31) * 64;
+}
 
 template <typename WT> struct WeightTraits;
 template <> struct WeightTraits<int8_t> { static constexpr int kCols = 16; };   // columns per 16-byte read
@@ -100,8 +113,15 @@ __device__ __forceinline__ void gemv_consume_stage(const uint8_t* stage, const _
   }
 }
 
-__device__ __forceinline__ void gemv_store(const GemvArgs& p, int row, int col, float acc) {
+// row_base: kv_row_base(p, row) when the caller has it at hand, else -1 (looked up here).
+__device__ __forceinline__ void gemv_store(const GemvArgs& p, int row, int col, float acc, long long row_base = -1) {
   const float v = acc + (p.bias ? h2f(p.bias[col]) : 0.f);
+  if (p.k_pool && col >= p.kv_hidden) {
+    const int c = col - p.kv_hidden, which = c >= p.kv_hidden, e = which ? c - p.kv_hidden : c;
+    if (row_base < 0) row_base = kv_row_base(p, row);
+    (which ? p.v_pool : p.k_pool)[row_base + (e >> 6) * 2048 + (e & 63)] = f2h(v);
+    return;
+  }
   if (p.out_fp32) { static_cast<float*>(p.out)[size_t(row) * p.ldo + col] = v; return; }
   __half h = f2h(v);
   if (p.gelu) h = f2h(gelu_tanh(h2f(h)));

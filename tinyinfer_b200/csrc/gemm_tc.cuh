@@ -194,25 +194,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         *reinterpret_cast<uint4*>(core + 128) = *reinterpret_cast<const uint4*>(&h[4]);
       }
     };
-    // The matching 64 columns of A: NMMA rows x 8 chunks of 8 halves, as K-major core matrices.
-    uint4 a_regs[NMMA / 16];
-    auto fetch_a = [&](int i) {
+    // The matching 64 columns of A: NMMA rows x 8 chunks of 8 halves, as K-major core matrices.  The
+    // global loads run kAhead stages ahead of their use (register ring), so their latency is covered by
+    // the dequantisation of the stages in between instead of sitting on every stage's critical path.
+    constexpr int kAhead = NMMA <= 64 ? 3 : 1;
+    constexpr int kPer = NMMA / 16;
+    uint4 a_ring[kAhead][kPer];
+    auto fetch_a = [&](uint4 (&dst)[kPer], int i) {
       const int k0 = k_begin + i * kTcStageK;
 #pragma unroll
-      for (int j = 0; j < NMMA / 16; ++j) {
+      for (int j = 0; j < kPer; ++j) {
         const int id = t + 128 * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
         const int row = m0 + mg * 8 + m8, kcol = k0 + kc * 8;
-        a_regs[j] = make_uint4(0, 0, 0, 0);
-        if (row < p.m && kcol < k_end) a_regs[j] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + kcol);
+        dst[j] = make_uint4(0, 0, 0, 0);
+        if (i < stages && row < p.m && kcol < k_end) dst[j] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + kcol);
       }
     };
-    auto store_a = [&](int oslot) {
+    auto store_a = [&](const uint4 (&src)[kPer], int oslot) {
       uint8_t* bdst = op_b + oslot * L::kOpBBytes;
 #pragma unroll
-      for (int j = 0; j < NMMA / 16; ++j) {
+      for (int j = 0; j < kPer; ++j) {
         const int id = t + 128 * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
-        *reinterpret_cast<uint4*>(bdst + (kc * (NMMA / 8) + mg) * 128 + m8 * 16) = a_regs[j];
+        *reinterpret_cast<uint4*>(bdst + (kc * (NMMA / 8) + mg) * 128 + m8 * 16) = src[j];
       }
+    };
+    auto rotate = [&] {
+#pragma unroll
+      for (int d = 0; d + 1 < kAhead; ++d)
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) a_ring[d][j] = a_ring[d + 1][j];
     };
     bool ok = true;
     // Lead-in: the first operand stages need no release; their weights are dequantised before the
@@ -226,23 +236,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       if (lane == 0) mbar_arrive(&raw_empty[i]);
     }
     pdl_wait();                                               // A (and the residual) come from the previous kernel
-    for (int i = 0; i < lead; ++i) {
-      fetch_a(i);
-      store_a(i);
-      fence_async_smem();                                     // generic-proxy stores -> visible to tcgen05.mma
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&op_full[i]);
+    if constexpr (kAhead == 3) {
+      // all lead stages' rows requested together: one round trip instead of three
+      fetch_a(a_ring[0], 0); fetch_a(a_ring[1], 1); fetch_a(a_ring[2], 2);
+      for (int i = 0; i < lead; ++i) {
+        store_a(a_ring[0], i);
+        rotate();
+        fetch_a(a_ring[kAhead - 1], i + kAhead);
+        fence_async_smem();                                   // generic-proxy stores -> visible to tcgen05.mma
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&op_full[i]);
+      }
+    } else {
+      for (int i = 0; i < lead; ++i) {
+        fetch_a(a_ring[0], i);
+        store_a(a_ring[0], i);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&op_full[i]);
+      }
+      fetch_a(a_ring[0], lead);
     }
+    // From here a_ring[0] holds stage i's rows, a_ring[1..] the following stages'.
     for (int i = lead; i < stages; ++i) {
       const int rslot = i % kTcRawStages, oslot = i % kTcOpStages;
-      fetch_a(i);                                             // in flight while the barriers are awaited
       if (ok) ok = mbar_wait(&raw_full[rslot], uint32_t(i / kTcRawStages) & 1u, kStatusTmaTimeout);
       if (ok) ok = mbar_wait(&op_empty[oslot], (uint32_t(i / kTcOpStages) & 1u) ^ 1u, kStatusMmaTimeout);
       if (ok) {
         dequantise(rslot, oslot);
-        store_a(oslot);
+        store_a(a_ring[0], oslot);
         fence_async_smem();
       }
+      rotate();
+      fetch_a(a_ring[kAhead - 1], i + kAhead);
       __syncwarp();
       if (lane == 0) { mbar_arrive(&raw_empty[rslot]); mbar_arrive(&op_full[oslot]); }
     }
@@ -253,8 +279,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
 
   // ---------------------------------------------------------------- epilogue (warps 2..5 own TMEM lanes 32*(warp%4)..)
   float* part = reinterpret_cast<float*>(smem);                // [NMMA][128] fp32, aliases the drained pipeline stages
+  __shared__ long long s_row_base[NMMA];                       // K/V pool offset of each row of the tile (QKV projection only)
   bool acc_ok = true;
   if (warp >= 2) {
+    if (p.k_pool) {
+      for (int i = tid - 64; i < NMMA; i += 128) s_row_base[i] = m0 + i < p.m ? kv_row_base(p, m0 + i) : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps only
+    }
     acc_ok = stages == 0 || mbar_wait(acc_ready, 0, kStatusMmaTimeout);
     tc_fence_after();
     const int lane_base = 32 * (warp & 3), n_local = lane_base + lane;
@@ -272,7 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         for (int i = 0; i < 32; ++i) part[(c0 + i) * 128 + n_local] = v[i];
       } else if (acc_ok && col < p.n) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { const int row = m0 + c0 + i; if (row < p.m) gemv_store(p, row, col, v[i]); }
+        for (int i = 0; i < 32; ++i) { const int row = m0 + c0 + i; if (row < p.m) gemv_store(p, row, col, v[i], p.k_pool ? s_row_base[c0 + i] : -1); }
       }
     }
     tc_fence_before();
@@ -280,13 +311,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   if (splits > 1) {
     cluster.sync();
     const bool good = !s_failed;
-    const int cols_per_rank = 128 / splits;
-    for (int i = tid; i < NMMA * cols_per_rank; i += kTcThreads) {
+    const int cols_per_rank = 128 / splits, total = NMMA * cols_per_rank;
+    for (int i = tid; i < total; i += kTcThreads) {
       const int m = i / cols_per_rank, c = rank * cols_per_rank + (i - m * cols_per_rank);
       float v = 0.f;
       for (int r = 0; r < splits; ++r) v += cluster.map_shared_rank(part, r)[m * 128 + c];
       const int row = m0 + m, col = n0 + c;
-      if (row < p.m && col < p.n && good) gemv_store(p, row, col, v);
+      if (row < p.m && col < p.n && good) gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1);
     }
     cluster.sync();
   } else {

@@ -116,6 +116,12 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   a.out = c.out; a.residual = static_cast<const __half*>(c.residual);
   a.lda = c.lda; a.ldo = c.ldo; a.ldw = c.ldw; a.m = c.m; a.n = c.n; a.k = c.k;
   a.out_fp32 = c.out_fp32; a.gelu = c.gelu;
+  if (c.kv) {
+    a.k_pool = static_cast<__half*>(c.kv->k_pool); a.v_pool = static_cast<__half*>(c.kv->v_pool);
+    a.kv_table = c.kv->table; a.kv_slots = c.kv->slots; a.kv_row_req = c.kv_row_req; a.kv_row_pos = c.kv_row_pos;
+    a.kv_table_pitch = c.kv->table_pitch; a.kv_layers = c.kv->layers; a.kv_layer = c.kv->layer; a.kv_heads = c.kv->heads;
+    a.kv_hidden = c.kv->heads * c.kv->head_dim;
+  }
   // Tensor-core path: int8 weights, 5 or more rows of A, operands addressable by TMA / 16-byte loads.
   static const int tc_min_rows = env_int("TINYINFER_B200_TC_MIN_ROWS", 5);      // measurement aid: where the SIMT kernel hands over
   // With `uniform_numerics` every row count takes this path, so a row's result does not depend on
@@ -129,6 +135,8 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       // element is then the same for every batch size and batch composition.
       int splits = 1;
       while (splits < 8 && slabs * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= 2 * kTcStageK) splits *= 2;
+      static const int forced_splits = env_int("TINYINFER_B200_TC_SPLITS", 0);      // measurement aid
+      if (forced_splits > 0) splits = forced_splits;
       int chunk = (c.k + splits - 1) / splits;
       a.k_chunk = (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
       const dim3 grid(slabs, splits, m_tiles);
@@ -203,16 +211,16 @@ cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start
 int decode_chunks(int max_kv, int chunk) { return std::max(1, (max_kv + chunk - 1) / chunk); }
 
 cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kl, int batch, int max_kv, int chunk,
-                                   float* scratch_acc, float* scratch_ml, const PagedKv& kv, const LaunchOpts& o) {
+                                   float* scratch_acc, float* scratch_ml, int* counters, const PagedKv& kv, const LaunchOpts& o) {
   if (kv.head_dim != 64) return cudaErrorInvalidValue;
   const int hidden = kv.heads * kv.head_dim;
   DecodeArgs p{};
   p.q = static_cast<const __half*>(qkv); p.q_sb = 3LL * hidden; p.q_sh = kv.head_dim;
   p.out = static_cast<__half*>(out); p.o_sb = hidden; p.o_sh = kv.head_dim;
-  p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml;
+  p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml; p.counters = counters;
   p.batch = batch; p.heads = kv.heads; p.chunk = chunk; p.chunks = decode_chunks(max_kv, chunk);
   cudaError_t st = launch(attn_decode_kernel<64, KvPaged>, dim3(p.chunks, kv.heads, batch), dim3(kDecodeWarps * 32), 0, o, 1, p, paged(kv));
-  if (st != cudaSuccess || p.chunks == 1) return st;
+  if (st != cudaSuccess || p.chunks == 1 || counters) return st;
   return launch(attn_combine_kernel<64>, dim3(kv.heads, batch), dim3(64), 0, o, 1, p);
 }
 
@@ -233,9 +241,9 @@ cudaError_t attention_packed_decode(const void* q, const void* k, const void* v,
 // ---------------------------------------------------------------- elementwise / glue
 cudaError_t layernorm(const void* x, const int32_t* row_index, const void* g, const void* b, void* y, int rows, int cols,
                       float eps, const LaunchOpts& o) {
-  const size_t smem = cols <= kLnMaxCols ? size_t(4) * cols * sizeof(float) : 0;
+  const size_t smem = cols <= kLnMaxCols ? size_t(20) * cols : 0;
   if (smem > 48 * 1024) {
-    static cudaError_t once = allow_smem(layernorm_kernel, 4 * kLnMaxCols * int(sizeof(float)));
+    static cudaError_t once = allow_smem(layernorm_kernel, 20 * kLnMaxCols);
     if (once != cudaSuccess) return once;
   }
   return launch(layernorm_kernel, dim3((rows + 3) / 4), dim3(128), smem, o, 1, static_cast<const __half*>(x), row_index,
@@ -258,13 +266,6 @@ cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const void* wte, c
   const int blocks = int(std::min<long long>((work + 255) / 256, 148LL * 8));
   return launch(embed_kernel, dim3(std::max(blocks, 1)), dim3(256), 0, o, 1, ids, row_pos, static_cast<const __half*>(wte),
                 static_cast<const __half*>(wpe), static_cast<__half*>(x), rows, hidden);
-}
-cudaError_t kv_scatter(const void* qkv, const int32_t* row_req, const int32_t* row_pos, int rows, int hidden,
-                       const PagedKv& kv, const LaunchOpts& o) {
-  const long long work = (long long)rows * (hidden / 8);
-  const int blocks = int(std::min<long long>((work + 255) / 256, 148LL * 8));
-  return launch(kv_scatter_kernel, dim3(std::max(blocks, 1)), dim3(256), 0, o, 1, static_cast<const __half*>(qkv), row_req,
-                row_pos, paged(kv), static_cast<__half*>(kv.k_pool), static_cast<__half*>(kv.v_pool), rows, hidden);
 }
 cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out, int32_t* feedback,
                    const int32_t* step, const LaunchOpts& o) {

@@ -18,6 +18,14 @@ struct LaunchOpts {
   bool pdl = false;              // programmatic dependent launch: prologue may overlap the previous kernel
 };
 
+// Paged KV pool of the model runtime; see attention.cuh for the page layout.
+struct PagedKv {
+  void* k_pool = nullptr; void* v_pool = nullptr;
+  const int32_t* table = nullptr;     // [slots][table_pitch]
+  const int32_t* slots = nullptr;     // [batch]
+  int table_pitch = 0, layers = 0, layer = 0, heads = 0, head_dim = 0;
+};
+
 // out[M,N] = a[M,K] . W[K,N] + bias, fused epilogue; W int8 (+scales) or fp16.
 struct GemmCall {
   const void* a = nullptr; int lda = 0;                 // fp16 [M,K]
@@ -28,6 +36,9 @@ struct GemmCall {
   void* out = nullptr; int ldo = 0; bool out_fp32 = false;
   const void* residual = nullptr;                       // fp16 [M,N] pitch ldo, or null
   bool gelu = false;
+  // QKV projection of the model runtime: when kv is set, columns [hidden, 3*hidden) (the K and V thirds)
+  // are written to row r's position kv_row_pos[r] of request kv_row_req[r] in the paged pool, not to `out`.
+  const PagedKv* kv = nullptr; const int32_t* kv_row_req = nullptr; const int32_t* kv_row_pos = nullptr;
   bool uniform_numerics = false;                         // tensor-core kernel for any row count (batch-invariant results)
   int m = 0, n = 0, k = 0;
 };
@@ -41,13 +52,6 @@ TIB_EXPORT cudaError_t attention_packed(const void* q, const void* k, const void
                                         int batch, int heads, int q_len, int kv_len, int head_dim, bool causal,
                                         const LaunchOpts& opts);
 
-// Paged KV pool of the model runtime; see attention.cuh for the page layout.
-struct PagedKv {
-  void* k_pool = nullptr; void* v_pool = nullptr;
-  const int32_t* table = nullptr;     // [slots][table_pitch]
-  const int32_t* slots = nullptr;     // [batch]
-  int table_pitch = 0, layers = 0, layer = 0, heads = 0, head_dim = 0;
-};
 // Prefill / mixed lengths: request b owns rows row_start[b] .. row_start[b]+q_lengths[b]-1 of
 // qkv[rows, 3*hidden]; attention output goes to out[rows, hidden] (heads merged).
 TIB_EXPORT cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start,
@@ -55,9 +59,11 @@ TIB_EXPORT cudaError_t attention_paged(const void* qkv, void* out, const int32_t
                                        int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& opts);
 // Decode: one row per request.  scratch_acc: fp32 [batch*heads*chunks*D], scratch_ml: fp32
 // [batch*heads*chunks*2]; chunks = ceil(max_kv / chunk).
+// counters: optional int [batch*heads], zero between launches; when given the merge of the chunk
+// partials happens inside the same kernel (no second launch).
 TIB_EXPORT cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kv_lengths,
                                               int batch, int max_kv, int chunk, float* scratch_acc, float* scratch_ml,
-                                              const PagedKv& kv, const LaunchOpts& opts);
+                                              int* counters, const PagedKv& kv, const LaunchOpts& opts);
 TIB_EXPORT int decode_chunks(int max_kv, int chunk);
 // Same decode attention over packed k/v[B,H,K,D] with q[B,H,1,D] (additive operator export).
 TIB_EXPORT cudaError_t attention_packed_decode(const void* q, const void* k, const void* v, void* y,
@@ -72,8 +78,6 @@ TIB_EXPORT cudaError_t softmax(const void* x, void* y, int rows, int cols, cudaS
 
 TIB_EXPORT cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const void* wte, const void* wpe,
                              void* x, int rows, int hidden, const LaunchOpts& opts);
-TIB_EXPORT cudaError_t kv_scatter(const void* qkv, const int32_t* row_req, const int32_t* row_pos,
-                                  int rows, int hidden, const PagedKv& kv, const LaunchOpts& opts);
 // out[(*step) * rows + r] = argmax of row r (step may be null = 0); feedback[r] too when non-null.
 TIB_EXPORT cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out,
                               int32_t* feedback, const int32_t* step, const LaunchOpts& opts);

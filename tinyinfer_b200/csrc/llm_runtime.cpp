@@ -75,6 +75,7 @@ struct ti_llm_model {
   void *x = nullptr, *res = nullptr, *norm = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr, *last = nullptr;
   float* logits = nullptr;
   float *att_acc = nullptr, *att_ml = nullptr;
+  int* att_counters = nullptr;                   // per (request, head) tickets of the decode attention, zero between launches
   // KV pool
   void *k_pool = nullptr, *v_pool = nullptr;
   int pages_per_slot = 0;
@@ -159,6 +160,8 @@ struct ti_llm_model {
     while (chunks * kDecodeChunk < opt.capacity) chunks *= 2;
     att_acc = dev<float>(size_t(opt.max_batch) * shape.heads * chunks * 64);
     att_ml = dev<float>(size_t(opt.max_batch) * shape.heads * chunks * 2);
+    att_counters = dev<int>(size_t(opt.max_batch) * shape.heads);
+    ck(cudaMemsetAsync(att_counters, 0, size_t(opt.max_batch) * shape.heads * sizeof(int), stream));
 
     pages_per_slot = (opt.capacity + tib_page_tokens() - 1) / tib_page_tokens();
     const int slots = opt.cache_slots + 1;                       // +1: private slot of score_window
@@ -201,8 +204,10 @@ struct ti_llm_model {
   }
 
   // ------------------------------------------------------------ one pass over the layers
-  void gemm(const void* a, const Linear& l, void* out, int rows, bool fp32, const void* residual, bool gelu) {
+  void gemm(const void* a, const Linear& l, void* out, int rows, bool fp32, const void* residual, bool gelu,
+            const tib::PagedKv* kv = nullptr, const int32_t* row_req = nullptr, const int32_t* row_pos = nullptr) {
     tib::GemmCall c;
+    c.kv = kv; c.kv_row_req = row_req; c.kv_row_pos = row_pos;
     c.a = a; c.lda = l.k; c.w = l.w; c.ldw = l.ldw; c.w_int8 = int8; c.scales = l.scales; c.bias = l.bias;
     c.out = out; c.ldo = fp32 ? vpitch : l.n; c.out_fp32 = fp32; c.residual = residual; c.gelu = gelu;
     c.m = rows; c.n = l.n; c.k = l.k;
@@ -231,9 +236,8 @@ struct ti_llm_model {
       const Block& b = blocks[size_t(l)];
       kv.layer = l;
       ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, m.rows, H, 1e-5f, o));
-      gemm(norm, b.qkv, qkv, m.rows, false, nullptr, false);
-      ck(tib::kv_scatter(qkv, m.row_req, m.row_pos, m.rows, H, kv, o));
-      if (m.max_q == 1) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, kv, o));
+      gemm(norm, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos);   // Q -> qkv buffer, K/V -> their pages
+      if (m.max_q == 1) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o));
       else ck(tib::attention_paged(qkv, attn, m.row_start, m.qlens, m.kvlens, m.offsets, m.batch, m.max_q, m.max_kv, kv, o));
       gemm(attn, b.proj, res, m.rows, false, x, false);             // res = x + proj(attn)
       ck(tib::layernorm(res, nullptr, b.ln2_g, b.ln2_b, norm, m.rows, H, 1e-5f, o));

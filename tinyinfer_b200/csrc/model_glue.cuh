@@ -1,5 +1,5 @@
 // Small kernels that tie the GPT-2 layers together in the model runtime: token+position
-// embedding, K/V placement into the paged pool, and the greedy argmax.  Rows are packed
+// embedding and the greedy argmax (K/V placement is an epilogue of the QKV projection).  Rows are packed
 // (no padding rows): row r belongs to request row_req[r] and sits at absolute position
 // row_pos[r] of that request.
 #pragma once
@@ -24,25 +24,6 @@ embed_kernel(const int32_t* ids, const int32_t* row_pos, const __half* wte, cons
 #pragma unroll
     for (int e = 0; e < 8; ++e) ah[e] = f2h(h2f(ah[e]) + h2f(bh[e]));
     *reinterpret_cast<uint4*>(x + size_t(r) * hidden + c) = a;
-  }
-  pdl_launch_dependents();
-}
-
-// Copies the K and V thirds of qkv[r, 3*hidden] into the paged pool at (slot, layer, head, pos)
-// (reference split_scatter, llm/src/runtime.cu:34-42; the Q third is read in place later).
-__global__ void __launch_bounds__(256)
-kv_scatter_kernel(const __half* qkv, const int32_t* row_req, const int32_t* row_pos, KvPaged kv,
-                  __half* kpool, __half* vpool, int rows, int hidden) {
-  pdl_wait();
-  const int chunks = hidden / 8, d = kv.d;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * chunks;
-       i += (long long)gridDim.x * blockDim.x) {
-    const int r = int(i / chunks), c = int(i % chunks) * 8;
-    const int h = c / d, e = c % d;
-    const size_t dst = kv.offset(row_req[r], h, row_pos[r]) + e;
-    const __half* src = qkv + size_t(r) * 3 * hidden + c;
-    *reinterpret_cast<uint4*>(kpool + dst) = *reinterpret_cast<const uint4*>(src + hidden);
-    *reinterpret_cast<uint4*>(vpool + dst) = *reinterpret_cast<const uint4*>(src + 2 * hidden);
   }
   pdl_launch_dependents();
 }
