@@ -28,21 +28,27 @@ __device__ __forceinline__ float tree256(float (&v)[8]) {
 // Mean and 1/sqrt(var+eps) of one row held in shared memory as fp32, by one warp (reference norm,
 // elementwise.cu:15-24).  Reading from shared memory keeps the replayed summation order cheap: the
 // 2 x cols/32 dependent adds of a lane wait on ~30-cycle loads instead of DRAM round trips.
-__device__ __forceinline__ void row_stats(const float* x, int cols, float eps, float& mean, float& inv) {
+__device__ __forceinline__ float row_value(const float* x, int c) { return x[c]; }
+__device__ __forceinline__ float row_value(const __half* x, int c) { return h2f(x[c]); }
+template <typename T>
+__device__ __forceinline__ void row_stats(const T* x, int cols, float eps, float& mean, float& inv) {
+  // v[j] is the partial of virtual thread lane + 32*j: columns lane + 32*j, + 256, + 512, ... added in that
+  // order.  The walk goes 256 columns at a time with the eight partials side by side, so eight independent
+  // load/add chains are in flight instead of one.
   const int lane = threadIdx.x & 31;
   float v[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float s = 0.f;
-    for (int c = lane + 32 * j; c < cols; c += 256) s += x[c];
-    v[j] = s;
+  for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  for (int base = lane; base < cols; base += 256) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const int c = base + 32 * j; if (c < cols) v[j] += row_value(x, c); }
   }
   mean = tree256(v) / cols;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    float s = 0.f;
-    for (int c = lane + 32 * j; c < cols; c += 256) { const float z = x[c] - mean; s += z * z; }
-    v[j] = s;
+  for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  for (int base = lane; base < cols; base += 256) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const int c = base + 32 * j; if (c < cols) { const float z = row_value(x, c) - mean; v[j] += z * z; } }
   }
   inv = rsqrtf(tree256(v) / cols + eps);
 }

@@ -54,6 +54,9 @@ struct GemvArgs {
   __half* k_pool; __half* v_pool;
   const int32_t* kv_table; const int32_t* kv_slots; const int32_t* kv_row_req; const int32_t* kv_row_pos;
   int kv_table_pitch, kv_layers, kv_layer, kv_heads, kv_hidden;
+  // LayerNorm prologue (tensor-core kernel, at most 32 rows, K = row width <= 768): `a` holds the rows before
+  // normalisation; the kernel computes each row's statistics and normalises while staging the operand.
+  const __half* ln_gamma; const __half* ln_beta; float ln_eps;
 };
 
 // Offset (in halves) of head 0, element 0 of row `row`'s position inside the K / V pool.

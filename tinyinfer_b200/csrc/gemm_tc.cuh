@@ -13,11 +13,11 @@
 //   * B-operand: NMMA rows of A, K-major, no swizzle;
 //   * D: fp32, NMMA columns of tensor memory, read back with tcgen05.ld by 4 warps.
 //
-// Pipeline of one CTA (192 threads, 2 CTAs per SM at NMMA = 32):
+// Pipeline of one CTA (320 threads, 2 CTAs per SM at NMMA = 32):
 //   warp 0      TMA producer: int8 tiles 64(k) x 128(n) -> ring of 4 raw stages (128-byte swizzle so the
 //               dequantisers' 16-byte column reads are bank-conflict free);
-//   warps 2-5   dequantise raw stage -> fp16 operand stage (ring of 3), copy the matching 64 columns of
-//               A next to it, fence.proxy.async, signal;  later: epilogue;
+//   warps 2-9   dequantise raw stage -> fp16 operand stage (ring of 3), copy the matching 64 columns of
+//               A next to it, fence.proxy.async, signal;  warps 2-5 later run the epilogue;
 //   warp 1      owns the TMEM allocation; one lane issues 4 tcgen05.mma per stage and commits to the
 //               barrier that releases the operand stage; a last commit publishes the accumulator.
 // K can be split over a cluster of up to 8 CTAs; partial tiles are reduced through
@@ -27,11 +27,13 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "elementwise.cuh"
 #include "gemm_simt.cuh"
 
 namespace tib {
 
-constexpr int kTcThreads = 192;
+constexpr int kTcDequantThreads = 256;                 // warps 2..9
+constexpr int kTcThreads = 64 + kTcDequantThreads;
 constexpr int kTcStageK = 64;
 constexpr int kTcRawStages = 4;
 constexpr int kTcOpStages = 3;
@@ -117,8 +119,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   if (tid == 0) {
     s_failed = 0;
     tma_prefetch_desc(&w_map);
-    for (int s = 0; s < kTcRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], 4); }
-    for (int s = 0; s < kTcOpStages; ++s) { mbar_init(&op_full[s], 4); mbar_init(&op_empty[s], 1); }
+    for (int s = 0; s < kTcRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kTcDequantThreads / 32); }
+    for (int s = 0; s < kTcOpStages; ++s) { mbar_init(&op_full[s], kTcDequantThreads / 32); mbar_init(&op_empty[s], 1); }
     mbar_init(acc_ready, 1);
     mbar_fence_init();
   }
@@ -167,7 +169,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     }
   } else {
     // ------------------------------------------------------------ dequantise + stage A rows (warps 2..5)
-    const int t = tid - 64;                                   // 0..127
+    const int t = tid - 64;                                   // 0..255
     const int r8 = t & 7, cc = (t >> 3) & 7, kg0 = t >> 6;     // k within 8-group, 16-byte chunk (16 channels), first k-group
     float sc[16];
 #pragma unroll
@@ -177,8 +179,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       const uint8_t* src = raw + rslot * kTcRawBytes;
       uint8_t* dst = op_a + oslot * kTcOpABytes;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int kg = kg0 + 2 * j, krow = kg * 8 + r8;
+      for (int j = 0; j < 2; ++j) {
+        const int kg = kg0 + 4 * j, krow = kg * 8 + r8;
         const uint4 q = *reinterpret_cast<const uint4*>(src + krow * 128 + ((cc ^ r8) << 4));
         const uint32_t words[4] = {q.x, q.y, q.z, q.w};
         __half2 h[8];
@@ -198,24 +200,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     // global loads run kAhead stages ahead of their use (register ring), so their latency is covered by
     // the dequantisation of the stages in between instead of sitting on every stage's critical path.
     constexpr int kAhead = NMMA <= 64 ? 3 : 1;
-    constexpr int kPer = NMMA / 16;
+    constexpr int kPer = NMMA * 8 / kTcDequantThreads;
     uint4 a_ring[kAhead][kPer];
     auto fetch_a = [&](uint4 (&dst)[kPer], int i) {
       const int k0 = k_begin + i * kTcStageK;
 #pragma unroll
       for (int j = 0; j < kPer; ++j) {
-        const int id = t + 128 * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
+        const int id = t + kTcDequantThreads * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
         const int row = m0 + mg * 8 + m8, kcol = k0 + kc * 8;
         dst[j] = make_uint4(0, 0, 0, 0);
         if (i < stages && row < p.m && kcol < k_end) dst[j] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + kcol);
       }
     };
-    auto store_a = [&](const uint4 (&src)[kPer], int oslot) {
+    // Optional LayerNorm of the rows (decode: NMMA == 32, K <= 768): statistics per row are computed once per CTA
+    // right after the dependency resolves, with the same summation order as layernorm_kernel, and applied here.
+    __shared__ __half s_gamma[NMMA == 32 ? 768 : 1], s_beta[NMMA == 32 ? 768 : 1];
+    __shared__ float s_mean[32], s_inv[32];
+    const bool fuse_ln = NMMA == 32 && p.ln_gamma != nullptr;
+    if (fuse_ln)
+      for (int c = k_begin + t; c < k_end; c += kTcDequantThreads) { s_gamma[c - k_begin] = p.ln_gamma[c]; s_beta[c - k_begin] = p.ln_beta[c]; }
+    auto store_a = [&](const uint4 (&src)[kPer], int oslot, int i) {
       uint8_t* bdst = op_b + oslot * L::kOpBBytes;
 #pragma unroll
       for (int j = 0; j < kPer; ++j) {
-        const int id = t + 128 * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
-        *reinterpret_cast<uint4*>(bdst + (kc * (NMMA / 8) + mg) * 128 + m8 * 16) = src[j];
+        const int id = t + kTcDequantThreads * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
+        uint4 v = src[j];
+        if (fuse_ln) {
+          const int m = mg * 8 + m8, kk = i * kTcStageK + kc * 8;      // row of the tile, k offset inside this CTA's range
+          if (k_begin + kk < k_end) {
+            __half* h = reinterpret_cast<__half*>(&v);
+            const float mean = s_mean[m & 31], inv = s_inv[m & 31];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) h[e] = f2h((h2f(h[e]) - mean) * inv * h2f(s_gamma[kk + e]) + h2f(s_beta[kk + e]));
+          }
+        }
+        *reinterpret_cast<uint4*>(bdst + (kc * (NMMA / 8) + mg) * 128 + m8 * 16) = v;
       }
     };
     auto rotate = [&] {
@@ -236,11 +255,42 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       if (lane == 0) mbar_arrive(&raw_empty[i]);
     }
     pdl_wait();                                               // A (and the residual) come from the previous kernel
+    if constexpr (NMMA == 32) {
+      if (fuse_ln) {
+        // Each of the 8 warps owns rows w, w+8, w+16, w+24: all their loads are issued together (one round
+        // trip), then each row passes through a per-warp strip of the still-empty B-operand ring.
+        __half* strip = reinterpret_cast<__half*>(op_b) + size_t(warp - 2) * p.k;
+        const int chunks = p.k / 8;
+        uint4 held[4][3];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+          for (int u = 0; u < 3; ++u) {
+            const int row = m0 + (warp - 2) + 8 * r, c = lane + 32 * u;
+            held[r][u] = make_uint4(0, 0, 0, 0);
+            if (row < p.m && c < chunks) held[r][u] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + c * 8);
+          }
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int local = (warp - 2) + 8 * r;
+          if (m0 + local < p.m) {                             // warp-uniform
+#pragma unroll
+            for (int u = 0; u < 3; ++u) { const int c = lane + 32 * u; if (c < chunks) *reinterpret_cast<uint4*>(strip + c * 8) = held[r][u]; }
+            __syncwarp();
+            float mean, inv;
+            row_stats(strip, p.k, p.ln_eps, mean, inv);
+            if (lane == 0) { s_mean[local] = mean; s_inv[local] = inv; }
+            __syncwarp();
+          } else if (lane == 0) { s_mean[local] = 0.f; s_inv[local] = 0.f; }
+        }
+        asm volatile("bar.sync 2, 256;" ::: "memory");        // the eight dequantising warps
+      }
+    }
     if constexpr (kAhead == 3) {
       // all lead stages' rows requested together: one round trip instead of three
       fetch_a(a_ring[0], 0); fetch_a(a_ring[1], 1); fetch_a(a_ring[2], 2);
       for (int i = 0; i < lead; ++i) {
-        store_a(a_ring[0], i);
+        store_a(a_ring[0], i, i);
         rotate();
         fetch_a(a_ring[kAhead - 1], i + kAhead);
         fence_async_smem();                                   // generic-proxy stores -> visible to tcgen05.mma
@@ -250,7 +300,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     } else {
       for (int i = 0; i < lead; ++i) {
         fetch_a(a_ring[0], i);
-        store_a(a_ring[0], i);
+        store_a(a_ring[0], i, i);
         fence_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(&op_full[i]);
@@ -264,7 +314,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       if (ok) ok = mbar_wait(&op_empty[oslot], (uint32_t(i / kTcOpStages) & 1u) ^ 1u, kStatusMmaTimeout);
       if (ok) {
         dequantise(rslot, oslot);
-        store_a(a_ring[0], oslot);
+        store_a(a_ring[0], oslot, i);
         fence_async_smem();
       }
       rotate();
@@ -281,7 +331,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   float* part = reinterpret_cast<float*>(smem);                // [NMMA][128] fp32, aliases the drained pipeline stages
   __shared__ long long s_row_base[NMMA];                       // K/V pool offset of each row of the tile (QKV projection only)
   bool acc_ok = true;
-  if (warp >= 2) {
+  if (warp >= 2 && warp < 6) {
     if (p.k_pool) {
       for (int i = tid - 64; i < NMMA; i += 128) s_row_base[i] = m0 + i < p.m ? kv_row_base(p, m0 + i) : 0;
       asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps only

@@ -130,11 +130,16 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
     CUtensorMap map; std::memset(&map, 0, sizeof map);
     if (make_map_2d(&map, c.w, true, uint64_t(c.k), uint64_t(c.n), uint64_t(c.ldw), 128, uint32_t(kTcStageK), true)) {
       const int nmma = c.m <= 32 ? 32 : c.m <= 64 ? 64 : c.m <= 128 ? 128 : 256;
+      if (c.ln_gamma) {
+        if (nmma != 32 || c.k > 768 || c.lda != c.k) return cudaErrorNotSupported;
+        a.ln_gamma = static_cast<const __half*>(c.ln_gamma); a.ln_beta = static_cast<const __half*>(c.ln_beta); a.ln_eps = c.ln_eps;
+      }
       const int slabs = (c.n + 127) / 128, m_tiles = (c.m + nmma - 1) / nmma;
       // K split chosen from the matrix alone (never from M): the summation grouping of an output
       // element is then the same for every batch size and batch composition.
       int splits = 1;
-      while (splits < 8 && slabs * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= 2 * kTcStageK) splits *= 2;
+      // Few stages per CTA matter more than full tiles: a stage costs about a microsecond of serial latency.
+      while (splits < 8 && slabs * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= kTcStageK) splits *= 2;
       static const int forced_splits = env_int("TINYINFER_B200_TC_SPLITS", 0);      // measurement aid
       if (forced_splits > 0) splits = forced_splits;
       int chunk = (c.k + splits - 1) / splits;
@@ -148,6 +153,7 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       }
     }
   }
+  if (c.ln_gamma) return cudaErrorNotSupported;               // only the tensor-core kernel has the LayerNorm prologue
   const int bn = c.w_int8 ? 128 : 64;
   const int mt = c.m >= 3 ? 4 : c.m;
   const int slabs = (c.n + bn - 1) / bn, m_tiles = (c.m + mt - 1) / mt;

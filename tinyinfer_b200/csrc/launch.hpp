@@ -39,6 +39,9 @@ struct GemmCall {
   // QKV projection of the model runtime: when kv is set, columns [hidden, 3*hidden) (the K and V thirds)
   // are written to row r's position kv_row_pos[r] of request kv_row_req[r] in the paged pool, not to `out`.
   const PagedKv* kv = nullptr; const int32_t* kv_row_req = nullptr; const int32_t* kv_row_pos = nullptr;
+  // LayerNorm prologue: `a` holds rows before normalisation (m <= 32, k <= 768, int8 weights reachable by TMA);
+  // gemm() returns cudaErrorNotSupported when the shape cannot take it.
+  const void* ln_gamma = nullptr; const void* ln_beta = nullptr; float ln_eps = 1e-5f;
   bool uniform_numerics = false;                         // tensor-core kernel for any row count (batch-invariant results)
   int m = 0, n = 0, k = 0;
 };

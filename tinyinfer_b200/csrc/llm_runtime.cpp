@@ -181,6 +181,8 @@ struct ti_llm_model {
     d_log = dev<int32_t>(size_t(opt.capacity) * opt.max_batch); h_log = host<int32_t>(size_t(opt.capacity) * opt.max_batch);
     if (const char* v = std::getenv("TINYINFER_B200_GRAPH")) use_graph = std::atoi(v) != 0;   // debugging aids: 0 = plain launches
     if (const char* v = std::getenv("TINYINFER_B200_PDL")) use_pdl = std::atoi(v) != 0;
+    fuse_ln = int8 && shape.hidden <= 768;
+    if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) fuse_ln = fuse_ln && std::atoi(v) != 0;
     h_status = host<unsigned int>(1); *h_status = 0;
     d_score_tokens = dev<int32_t>(size_t(opt.capacity)); d_score_mask = dev<uint8_t>(size_t(opt.capacity));
     d_loss = dev<double>(size_t(opt.capacity)); d_loss_sum = dev<double>(1);
@@ -204,10 +206,12 @@ struct ti_llm_model {
   }
 
   // ------------------------------------------------------------ one pass over the layers
+  // ln_g / ln_b: LayerNorm applied to `a` inside the GEMM (decode-sized calls only, see fuse_ln).
   void gemm(const void* a, const Linear& l, void* out, int rows, bool fp32, const void* residual, bool gelu,
-            const tib::PagedKv* kv = nullptr, const int32_t* row_req = nullptr, const int32_t* row_pos = nullptr) {
+            const tib::PagedKv* kv = nullptr, const int32_t* row_req = nullptr, const int32_t* row_pos = nullptr,
+            const void* ln_g = nullptr, const void* ln_b = nullptr) {
     tib::GemmCall c;
-    c.kv = kv; c.kv_row_req = row_req; c.kv_row_pos = row_pos;
+    c.kv = kv; c.kv_row_req = row_req; c.kv_row_pos = row_pos; c.ln_gamma = ln_g; c.ln_beta = ln_b;
     c.a = a; c.lda = l.k; c.w = l.w; c.ldw = l.ldw; c.w_int8 = int8; c.scales = l.scales; c.bias = l.bias;
     c.out = out; c.ldo = fp32 ? vpitch : l.n; c.out_fp32 = fp32; c.residual = residual; c.gelu = gelu;
     c.m = rows; c.n = l.n; c.k = l.k;
@@ -235,13 +239,22 @@ struct ti_llm_model {
     for (int l = 0; l < shape.layers; ++l) {
       const Block& b = blocks[size_t(l)];
       kv.layer = l;
-      ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, m.rows, H, 1e-5f, o));
-      gemm(norm, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos);   // Q -> qkv buffer, K/V -> their pages
+      // LayerNorm as a prologue of the consuming GEMM while one warp per row suffices (every CTA of that GEMM
+      // repeats the row statistics, so beyond 8 rows the separate kernel is cheaper).
+      const bool fused = fuse_ln && m.rows <= 8;
+      if (fused) gemm(x, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos, b.ln1_g, b.ln1_b);
+      else {
+        ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, m.rows, H, 1e-5f, o));
+        gemm(norm, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos);   // Q -> qkv buffer, K/V -> their pages
+      }
       if (m.max_q == 1) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o));
       else ck(tib::attention_paged(qkv, attn, m.row_start, m.qlens, m.kvlens, m.offsets, m.batch, m.max_q, m.max_kv, kv, o));
       gemm(attn, b.proj, res, m.rows, false, x, false);             // res = x + proj(attn)
-      ck(tib::layernorm(res, nullptr, b.ln2_g, b.ln2_b, norm, m.rows, H, 1e-5f, o));
-      gemm(norm, b.fc, act, m.rows, false, nullptr, true);          // act = gelu(fc(norm))
+      if (fused) gemm(res, b.fc, act, m.rows, false, nullptr, true, nullptr, nullptr, nullptr, b.ln2_g, b.ln2_b);
+      else {
+        ck(tib::layernorm(res, nullptr, b.ln2_g, b.ln2_b, norm, m.rows, H, 1e-5f, o));
+        gemm(norm, b.fc, act, m.rows, false, nullptr, true);        // act = gelu(fc(norm))
+      }
       gemm(act, b.proj2, x, m.rows, false, res, false);             // x = res + proj2(act)
     }
   }
@@ -314,6 +327,7 @@ struct ti_llm_model {
   std::vector<StepGraph> graphs;
   int32_t *d_seg = nullptr, *h_seg = nullptr, *d_step = nullptr, *d_log = nullptr, *h_log = nullptr;
   bool use_graph = true, use_pdl = true;
+  bool fuse_ln = false;             // int8 weights and rows of at most 768 values: LayerNorm runs inside the consuming GEMM
 
   int32_t* seg(int field) const { return d_seg + size_t(field) * opt.max_batch; }
 
@@ -323,8 +337,11 @@ struct ti_llm_model {
     m.rows = batch; m.batch = batch; m.max_q = 1; m.max_kv = max_kv;
     run_layers(m);
     tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
-    ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, last, batch, shape.hidden, 1e-5f, o));
-    gemm(last, head, logits, batch, true, nullptr, false);
+    if (fuse_ln && batch <= 8) gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b);
+    else {
+      ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, last, batch, shape.hidden, 1e-5f, o));
+      gemm(last, head, logits, batch, true, nullptr, false);
+    }
     ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_log, seg(0), d_step, o));
     ck(tib::advance(seg(2), seg(3), d_step, batch, o));
   }
