@@ -218,6 +218,45 @@ def kernel_rooflines(cached, peak):
     return out
 
 
+def operator_sweep():
+    """Standalone INT8-weight GEMV/GEMM sweep (activations fp16 N(0,1), weights uniform int8, fp16-representable
+    scales in [1e-3, 2e-2], seed 1): device time per launch from a CUDA graph, achieved GB/s on the algorithmic
+    bytes 2MK + KN + 6N + 2MN (4MN for the fp32 vocabulary projection) and TFLOP/s on 2MNK."""
+    import torch
+    from tinyinfer_b200.native_ops import NativeOps
+    ops = NativeOps()
+    lib, dev = ops.lib, torch.cuda.current_device()
+    peak, _ = peak_hbm()
+    torch.manual_seed(1)
+    rows = []
+    for k, n in ((768, 2304), (768, 768), (768, 3072), (3072, 768), (768, 50257)):
+        sets = max(2, int(260e6 // (k * n)) + 1)                         # distinct weights > L2 per round
+        ws = [torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda") for _ in range(sets)]
+        sc = (torch.rand(n, device="cuda") * 0.019 + 0.001).half().float()
+        bias = (torch.randn(n, device="cuda") * 0.1).half()
+        for m in (1, 8, 32, 128, 512):
+            a = torch.randn((m, k), device="cuda").half()
+            fp32 = n == 50257
+            y = torch.empty((m, n), device="cuda", dtype=torch.float32 if fp32 else torch.float16)
+            for gelu in ((0,) if fp32 else (0, 1)):
+                def run():
+                    for w in ws:
+                        if gelu:
+                            st = lib.ti_b200_gemm_i8_fused(a.data_ptr(), w.data_ptr(), sc.data_ptr(), bias.data_ptr(), None, y.data_ptr(), m, n, k, 0, 1,
+                                                           torch.cuda.current_stream().cuda_stream, dev)
+                        else:
+                            st = lib.ti_v2_gemm_ex_i8(a.data_ptr(), w.data_ptr(), sc.data_ptr(), bias.data_ptr(), y.data_ptr(), None, m, n, k, int(fp32), 0,
+                                                      torch.cuda.current_stream().cuda_stream, dev)
+                        if st:
+                            raise RuntimeError(lib.ti_v2_last_error().decode())
+                seconds = graph_seconds(run, sets)
+                nbytes = 2 * m * k + k * n + 6 * n + (4 if fp32 else 2) * m * n
+                rows.append({"K": k, "N": n, "M": m, "epilogue": "bias+gelu" if gelu else "bias", "us": seconds * 1e6,
+                             "GBps": nbytes / seconds / 1e9, "hbm_frac": nbytes / seconds / 1e9 / peak, "TFLOPs": 2.0 * m * n * k / seconds / 1e12})
+        del ws
+    return rows
+
+
 def gpu_main(args, rank, world):
     import torch
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -353,9 +392,16 @@ def main():
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     parser.add_argument("--quick", action="store_true", help="only the device-resident timed steps (for profilers)")
+    parser.add_argument("--sweep", action="store_true", help="operator sweep of the INT8-weight GEMV/GEMM instead of the decode benchmark")
     args = parser.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    if args.impl == "reference":
+    if args.sweep:
+        if rank == 0:
+            import torch
+            torch.cuda.set_device(0)
+            for row in operator_sweep():
+                print(json.dumps(row))
+    elif args.impl == "reference":
         reference_main(args, rank)
     else:
         gpu_main(args, rank, world)

@@ -226,3 +226,42 @@ def test_logits_do_not_depend_on_batch_composition(model):
         model.reset(20)
         assert model.greedy([prompts[i]], len(batch_tokens[i]), slots=[20])["tokens"][0] == batch_tokens[i]
     model.reset_all()
+
+
+def test_medium_shape_matches_cpu_oracle(tmp_path_factory):
+    """GPT-2 medium shape (24 layers, 16 heads, hidden 1024), seed 3: the reference runtime cannot load it
+    (compile-time 12/12/768), so the operator-composed CPU oracle is the reference here."""
+    from oracle import ti_oracle as orc
+    from tinyinfer_b200 import artifact
+    from tinyinfer_b200.runtime import NativeModel
+    manifest = artifact.write_synthetic(tmp_path_factory.mktemp("gpt2_medium_seed3"), artifact.GPT2_MEDIUM, seed=3)
+    meta, tensors = artifact.load(manifest)
+    oracle = orc.Gpt2Oracle(tensors, meta["architecture"])
+    prompt = tokens(3, 10)
+    with NativeModel(None, manifest, max_batch=8, cache_slots=8, capacity=64) as m:
+        ours = logits_of(m.forward([0], [prompt]))[0]
+        want = torch.from_numpy(oracle.forward(0, prompt))
+        assert_logits_close(ours[None], want[None], "medium prompt logits vs oracle")
+        nxt = int(want.argmax())
+        step = logits_of(m.forward([0], [[nxt]]))[0]
+        assert_logits_close(step[None], torch.from_numpy(oracle.forward(0, [nxt]))[None], "medium decode logits vs oracle")
+        m.reset_all()
+        batch = m.greedy([prompt, prompt[:4]], [6, 3])
+        m.reset_all()
+        assert m.greedy([prompt], 6)["tokens"][0] == batch["tokens"][0]
+
+
+def test_two_devices_in_one_process(manifest):
+    """One model context per GPU inside one process (what the server's workers do): both give the same tokens."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from tinyinfer_b200.runtime import NativeModel
+    prompt = tokens(4, 20)
+    with NativeModel(None, manifest, device=0, max_batch=4, cache_slots=4, capacity=128) as a, \
+            NativeModel(None, manifest, device=1, max_batch=4, cache_slots=4, capacity=128) as b:
+        ta = a.greedy([prompt, prompt[:5]], [10, 4])["tokens"]
+        tb = b.greedy([prompt, prompt[:5]], [10, 4])["tokens"]
+        assert ta == tb
+        la = logits_of(a.forward([2], [prompt]))
+        lb = logits_of(b.forward([2], [prompt]))
+        assert torch.equal(la, lb)

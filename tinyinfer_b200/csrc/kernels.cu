@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 
 #include "launch.hpp"
@@ -70,9 +71,23 @@ bool make_map_2d(CUtensorMap* map, const void* base, bool int8, uint64_t rows, u
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Opt-in to more than 48 KB of dynamic shared memory.  The attribute belongs to (kernel, device), and one
+// process may drive several GPUs (one model context per device), so it is set once per device, not once
+// per process.
 template <typename K>
 cudaError_t allow_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  static std::mutex lock;
+  static std::map<const void*, uint64_t> done;                 // kernel -> bit per device already configured
+  int device = -1;
+  cudaError_t st = cudaGetDevice(&device);
+  if (st != cudaSuccess) return st;
+  if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> hold(lock);
+  uint64_t& mask = done[reinterpret_cast<const void*>(kernel)];
+  if (mask >> device & 1) return cudaSuccess;
+  st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (st == cudaSuccess) mask |= uint64_t(1) << device;
+  return st;
 }
 
 int sm_count() {
@@ -82,8 +97,8 @@ int sm_count() {
 
 template <typename WT, int MT, bool TMA>
 cudaError_t launch_gemv(const CUtensorMap& map, const GemvArgs& args, dim3 grid, const LaunchOpts& o) {
-  static cudaError_t once = allow_smem(gemv_kernel<WT, MT, TMA>, GemvSmem::kBytes);
-  if (once != cudaSuccess) return once;
+  const cudaError_t ready = allow_smem(gemv_kernel<WT, MT, TMA>, GemvSmem::kBytes);
+  if (ready != cudaSuccess) return ready;
   return launch(gemv_kernel<WT, MT, TMA>, grid, dim3(kGemvThreads), GemvSmem::kBytes, o, int(grid.y), map, args);
 }
 template <typename WT, bool TMA>
@@ -97,8 +112,8 @@ cudaError_t launch_gemv_mt(int mt, const CUtensorMap& map, const GemvArgs& args,
 
 template <int NMMA>
 cudaError_t launch_tc(const CUtensorMap& map, const GemvArgs& args, dim3 grid, const LaunchOpts& o) {
-  static cudaError_t once = allow_smem(gemm_tc_kernel<NMMA>, TcSmem<NMMA>::kBytes);
-  if (once != cudaSuccess) return once;
+  const cudaError_t ready = allow_smem(gemm_tc_kernel<NMMA>, TcSmem<NMMA>::kBytes);
+  if (ready != cudaSuccess) return ready;
   return launch(gemm_tc_kernel<NMMA>, grid, dim3(kTcThreads), TcSmem<NMMA>::kBytes, o, int(grid.y), map, args);
 }
 
@@ -249,8 +264,8 @@ cudaError_t layernorm(const void* x, const int32_t* row_index, const void* g, co
                       float eps, const LaunchOpts& o) {
   const size_t smem = cols <= kLnMaxCols ? size_t(20) * cols : 0;
   if (smem > 48 * 1024) {
-    static cudaError_t once = allow_smem(layernorm_kernel, 20 * kLnMaxCols);
-    if (once != cudaSuccess) return once;
+    const cudaError_t ready = allow_smem(layernorm_kernel, 20 * kLnMaxCols);
+    if (ready != cudaSuccess) return ready;
   }
   return launch(layernorm_kernel, dim3((rows + 3) / 4), dim3(128), smem, o, 1, static_cast<const __half*>(x), row_index,
                 static_cast<const __half*>(g), static_cast<const __half*>(b), static_cast<__half*>(y), rows, cols, eps);
