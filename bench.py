@@ -163,6 +163,11 @@ def graph_seconds(enqueue, launches, replays=10):
     return start.elapsed_time(stop) * 1e-3 / (replays * launches)
 
 
+# DRAM traffic over algorithmic bytes of one launch, from the ncu captures summarised under profiles/
+# (attn_decode_kernel_batch32.md, gemm_tc_kernel_decode_batch32.md); None where no capture exists.
+TRAFFIC_RATIO = {"attention_decode": 25.63 / 26.6, "gemm_int8 qkv": 1.91 / 1.77, "gemm_int8 mlp fc": 2.50 / 2.36, "gemm_int8 mlp proj": 2.69 / 2.36}
+
+
 def kernel_rooflines(cached, peak):
     """The kernel families that carry a decode step's bytes, timed alone on the step's shapes.  Each
     round walks distinct buffers totalling more than the 126 MB L2, so every launch streams from HBM
@@ -211,7 +216,9 @@ def kernel_rooflines(cached, peak):
         out[name] = {"seconds": seconds, "bytes": nbytes, "launches_per_step": per_step}
 
     gemm_family("gemm_int8 lm_head (M=32, 768x50304, fp32 out)", [(768, 50304)], 5, True, 1)
-    gemm_family("gemm_int8 x4 of one layer (M=32: qkv, proj, fc, proj2)", [(768, 2304), (768, 768), (768, 3072), (3072, 768)], 30, False, 12)
+    for label, shape in (("qkv 768x2304", (768, 2304)), ("attn proj 768x768", (768, 768)), ("mlp fc 768x3072", (768, 3072)),
+                         ("mlp proj 3072x768", (3072, 768))):
+        gemm_family(f"gemm_int8 {label} (M=32)", [shape], max(24, int(260e6 // (shape[0] * shape[1])) + 1), False, 12)
     for v in out.values():
         v["gbs"] = v["bytes"] / v["seconds"] / 1e9
         v["frac"] = v["gbs"] / peak
@@ -367,8 +374,10 @@ def gpu_main(args, rank, world):
     if rank == 0:
         kernels = kernel_rooflines(cached_at_start, peak)
         top = max(kernels.items(), key=lambda kv: kv[1]["seconds"] * kv[1]["launches_per_step"])
+        ratio = next((r for key, r in TRAFFIC_RATIO.items() if top[0].startswith(key)), None)
         line["roofline"] = {"kernel": top[0], "bound": "hbm", "achieved": top[1]["gbs"], "peak": peak, "unit": "GB/s", "frac": top[1]["frac"],
-                            "traffic": None, "peak_source": peak_source,
+                            "traffic": None if ratio is None else int(top[1]["bytes"] * ratio), "algorithmic_bytes": top[1]["bytes"],
+                            "peak_source": peak_source,
                             "share_of_step": top[1]["seconds"] * top[1]["launches_per_step"] / (device_ms * 1e-3 / K)}
         line["step_roofline"] = {"bound": "hbm", "achieved": step_gbs / world if world > 1 else step_gbs, "peak": peak, "unit": "GB/s",
                                  "frac": (step_gbs / world if world > 1 else step_gbs) / peak,
