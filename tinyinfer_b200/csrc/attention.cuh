@@ -33,6 +33,8 @@ struct KvPacked {
   __device__ __forceinline__ size_t offset(int b, int h, int key) const {
     return ((size_t(b) * heads + h) * kv_len + key) * d;
   }
+  // offset of key t0 of a 32-key tile (t0 % 32 == 0); the tile's keys follow at stride d
+  __device__ __forceinline__ size_t tile_base(int b, int h, int t0) const { return offset(b, h, t0); }
 };
 struct KvPaged {
   const __half* k; const __half* v;       // page pools
@@ -43,6 +45,7 @@ struct KvPaged {
     const int page = table[size_t(slots[b]) * table_pitch + (key / kPageTokens)];
     return (((size_t(page) * layers + layer) * heads + h) * kPageTokens + (key % kPageTokens)) * d;
   }
+  __device__ __forceinline__ size_t tile_base(int b, int h, int t0) const { return offset(b, h, t0); }   // one page per tile
 };
 
 struct AttnArgs {
@@ -143,7 +146,8 @@ attn_tile_kernel(const AttnArgs p, const KV kv) {
 }
 
 // ------------------------------------------------------------------ decode kernel (Q == 1)
-constexpr int kDecodeWarps = 4;
+constexpr int kDecodeWarps = 4;          // chunked launches: 128 keys per CTA pass
+constexpr int kDecodeWarpsWhole = 8;     // one CTA per (request, head): 256 keys per pass over the whole history
 
 struct DecodeArgs {
   const __half* q; long long q_sb, q_sh;            // one query row per request
@@ -154,25 +158,57 @@ struct DecodeArgs {
   int* counters;                                     // optional int [batch][heads], all zero between launches: when given, the
                                                      // last chunk CTA of a (request, head) merges the partials itself
   int batch, heads, chunk, chunks;                   // keys per CTA; grid.x
+  // early: kv_lengths, the page table and every key but each request's newest one were written before the
+  // kernel ahead of this one started, so they are read before the dependency wait (their latency then hides
+  // behind that kernel); the newest key and the query are read after it.
+  int early;
 };
 
-// grid = (chunks, heads, batch), block = 128.
-template <int D, typename KV>
-__global__ void __launch_bounds__(kDecodeWarps * 32)
+// grid = (chunks, heads, batch), block = 32 * W.
+template <int D, typename KV, int W = kDecodeWarps>
+__global__ void __launch_bounds__(W * 32)
 attn_decode_kernel(const DecodeArgs p, const KV kv) {
+  trace_event(kTrAttnDecode, 0);
   static_assert(D == 64 || D == 128, "head_dim");
   constexpr int DP = D / 8;                           // lanes that share one key (8 dims each)
   constexpr int KPS = 32 / DP;                        // keys per warp instruction
   constexpr int STEPS = 32 / KPS;                     // instructions per 32-key tile
-  __shared__ float s_acc[kDecodeWarps][D];
-  __shared__ float s_ml[kDecodeWarps][2];
+  __shared__ float s_acc[W][D];
+  __shared__ float s_ml[W][2];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int dp = lane % DP, ksub = lane / DP;
   const int h = blockIdx.y, b = blockIdx.z;
+  const int begin = blockIdx.x * p.chunk, t_first = begin + warp * 32;
+  uint4 kreg[STEPS], vreg[STEPS];
+  // keys [lo, hi) of the tile at t0 into this lane's registers; the rest stay as they are
+  auto load_tile = [&](size_t base, int t0, int lo, int hi) {
+#pragma unroll
+    for (int i = 0; i < STEPS; ++i) {
+      const int key = t0 + i * KPS + ksub;
+      if (key >= lo && key < hi) {
+        const size_t o = base + size_t(i * KPS + ksub) * D + dp * 8;
+        kreg[i] = *reinterpret_cast<const uint4*>(kv.k + o);
+        vreg[i] = *reinterpret_cast<const uint4*>(kv.v + o);
+      }
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < STEPS; ++i) { kreg[i] = make_uint4(0, 0, 0, 0); vreg[i] = kreg[i]; }
+  int len = 0;
+  size_t base_first = 0;
+  if (p.early) {
+    len = p.kv_lengths[b];
+    const int end_early = min(len, begin + p.chunk);
+    if (t_first < end_early) {
+      base_first = kv.tile_base(b, h, t_first);
+      load_tile(base_first, t_first, t_first, min(end_early, len - 1));
+    }
+  }
   pdl_wait();
-  const int len = p.kv_lengths[b];
-  const int begin = blockIdx.x * p.chunk, end = min(len, begin + p.chunk);
-  if (begin >= end && !(blockIdx.x == 0)) return;     // nothing to do for this chunk (uniform per CTA)
+  trace_event(kTrAttnDecode, 1);
+  if (!p.early) len = p.kv_lengths[b];
+  const int end = min(len, begin + p.chunk);
+  if (begin >= end && blockIdx.x != 0) return;   // nothing to do for this chunk (uniform per CTA)
 
   const uint4 qraw = *reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + dp * 8);
   const __half2* q2 = reinterpret_cast<const __half2*>(&qraw);
@@ -180,17 +216,13 @@ attn_decode_kernel(const DecodeArgs p, const KV kv) {
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 
-  for (int t0 = begin + warp * 32; t0 < end; t0 += kDecodeWarps * 32) {
-    uint4 kreg[STEPS], vreg[STEPS];
+  for (int t0 = t_first; t0 < end; t0 += W * 32) {
+    if (t0 == t_first && p.early) {
+      load_tile(base_first, t0, max(t0, len - 1), end);          // the newest key, if this tile holds it
+    } else {
 #pragma unroll
-    for (int i = 0; i < STEPS; ++i) {
-      const int key = t0 + i * KPS + ksub;
-      kreg[i] = make_uint4(0, 0, 0, 0); vreg[i] = kreg[i];
-      if (key < end) {
-        const size_t o = kv.offset(b, h, key) + dp * 8;
-        kreg[i] = *reinterpret_cast<const uint4*>(kv.k + o);
-        vreg[i] = *reinterpret_cast<const uint4*>(kv.v + o);
-      }
+      for (int i = 0; i < STEPS; ++i) { kreg[i] = make_uint4(0, 0, 0, 0); vreg[i] = kreg[i]; }
+      load_tile(kv.tile_base(b, h, t0), t0, t0, end);
     }
     float sc[STEPS], tile_max = -CUDART_INF_F;
 #pragma unroll
@@ -245,10 +277,10 @@ attn_decode_kernel(const DecodeArgs p, const KV kv) {
   if (tid < D) {
     float mm = -CUDART_INF_F;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) mm = fmaxf(mm, s_ml[w][0]);
+    for (int w = 0; w < W; ++w) mm = fmaxf(mm, s_ml[w][0]);
     float ll = 0.f, aa = 0.f;
 #pragma unroll
-    for (int w = 0; w < kDecodeWarps; ++w) {
+    for (int w = 0; w < W; ++w) {
       const float f = s_ml[w][0] > -CUDART_INF_F ? expf(s_ml[w][0] - mm) : 0.f;
       ll += s_ml[w][1] * f; aa += s_acc[w][tid] * f;
     }

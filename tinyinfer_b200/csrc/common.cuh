@@ -110,6 +110,37 @@ __device__ __forceinline__ void fence_async_smem() {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ------------------------------------------------------------------ optional timeline (development builds only)
+// With -DTIB_TRACE block (0,0,0) of every kernel records %globaltimer at entry (0), after its dependency
+// wait (1) and at exit (2); tib::trace_dump copies the log out.  Without the macro nothing is compiled in.
+#ifdef TIB_TRACE
+__device__ unsigned long long g_trace_buf[1 << 16];   // this header is compiled into one device unit only
+__device__ unsigned int g_trace_count = 0;
+// any one thread of block (0,0,0): event `what` (< 256) of kernel `kernel`
+__device__ __forceinline__ void trace_mark(int kernel, int what) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const unsigned int i = atomicAdd(&g_trace_count, 1u);
+    if (i < (1u << 16) - 1024) g_trace_buf[i] = (unsigned long long)(kernel * 256 + what) << 48 | (t & ((1ull << 48) - 1));
+  }
+}
+__device__ __forceinline__ void trace_event(int kernel, int what) { if (threadIdx.x == 0) trace_mark(kernel, what); }
+// fire-and-forget variant for marks inside a pipeline: slot `what` of the last 1024 words, last writer wins
+__device__ __forceinline__ void trace_slot(int what) {
+  if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_trace_buf[(1 << 16) - 1024 + what] = t;
+  }
+}
+#else
+#define trace_event(kernel, what) ((void)0)
+#define trace_mark(kernel, what) ((void)0)
+#define trace_slot(what) ((void)0)
+#endif
+enum TraceKernel { kTrEmbed = 1, kTrLayerNorm, kTrGemmTc, kTrGemv, kTrAttnDecode, kTrAttnTile, kTrCombine, kTrArgmax, kTrAdvance };
+
 // ------------------------------------------------------------------ warp reductions
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

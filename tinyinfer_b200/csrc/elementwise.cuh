@@ -78,6 +78,7 @@ constexpr int kLnMaxCols = 4096;     // rows up to this width are staged in shar
 __global__ void __launch_bounds__(128)
 layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, const __half* b, __half* y,
                  int rows, int cols, float eps) {
+  trace_event(kTrLayerNorm, 0);
   extern __shared__ float ln_rows[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x * 4 + warp;
   const bool staged = cols <= kLnMaxCols;
@@ -88,6 +89,7 @@ layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, con
     __syncthreads();
   }
   pdl_wait();
+  trace_event(kTrLayerNorm, 1);
   if (row >= rows) return;
   const __half* xr = x + size_t(row_index ? row_index[row] : row) * cols;   // optional gather of input rows
   __half* yr = y + size_t(row) * cols;

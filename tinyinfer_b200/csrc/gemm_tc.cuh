@@ -35,8 +35,17 @@ namespace tib {
 constexpr int kTcDequantThreads = 256;                 // warps 2..9
 constexpr int kTcThreads = 64 + kTcDequantThreads;
 constexpr int kTcStageK = 64;
-constexpr int kTcRawStages = 4;
-constexpr int kTcOpStages = 3;
+#ifndef TIB_TC_RAW_STAGES
+#define TIB_TC_RAW_STAGES 4
+#endif
+#ifndef TIB_TC_OP_STAGES
+#define TIB_TC_OP_STAGES 3
+#endif
+#ifndef TIB_TC_AHEAD
+#define TIB_TC_AHEAD 3
+#endif
+constexpr int kTcRawStages = TIB_TC_RAW_STAGES;
+constexpr int kTcOpStages = TIB_TC_OP_STAGES;
 constexpr int kTcRawBytes = kTcStageK * 128;          // int8 tile
 constexpr int kTcOpABytes = 128 * kTcStageK * 2;      // fp16 weight tile
 
@@ -97,6 +106,8 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
 template <int NMMA>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
+  trace_event(kTrGemmTc, 0);
+  if (gridDim.x > 300 && threadIdx.x == 0) trace_slot(1);
   using L = TcSmem<NMMA>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -104,8 +115,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   uint8_t* op_a = smem + L::kOpAOff;
   uint8_t* op_b = smem + L::kOpBOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t *raw_full = bars, *raw_empty = bars + 4, *op_full = bars + 8, *op_empty = bars + 11, *acc_ready = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t *raw_full = bars, *raw_empty = raw_full + kTcRawStages, *op_full = raw_empty + kTcRawStages, *op_empty = op_full + kTcOpStages,
+           *acc_ready = op_empty + kTcOpStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  static_assert((2 * kTcRawStages + 2 * kTcOpStages + 2) * 8 <= 128, "barrier block");
+  static_assert(NMMA != 32 || kTcOpStages * L::kOpBBytes >= 8 * 768 * 2, "LayerNorm row strips live in the B-operand ring");
   __shared__ int s_failed;
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -116,6 +130,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   const int stages = k_end > k_begin ? (k_end - k_begin + kTcStageK - 1) / kTcStageK : 0;
   constexpr uint32_t kTmemCols = NMMA < 32 ? 32 : NMMA;
 
+  // Split-K launches: the (at most two) output elements this thread finishes after the cluster reduction
+  // are known now; when their bias and residual do not come from the kernel directly ahead, fetch them here.
+  EpiloguePre pre[2];
+  pre[0].valid = pre[1].valid = false;
+  if (splits > 1 && p.early_epilogue && !p.out_fp32) {
+    const int cols_per_rank = 128 / splits, total = NMMA * cols_per_rank;
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int i = tid + s * kTcThreads;
+      if (i < total) {
+        const int m = i / cols_per_rank, c = rank * cols_per_rank + (i - m * cols_per_rank);
+        const int row = m0 + m, col = n0 + c;
+        if (row < p.m && col < p.n) {
+          pre[s].bias = p.bias ? p.bias[col] : f2h(0.f);
+          pre[s].residual = p.residual && !(p.k_pool && col >= p.kv_hidden) ? p.residual[size_t(row) * p.ldo + col] : f2h(0.f);
+          pre[s].valid = true;
+        }
+      }
+    }
+  }
+  if (p.early_trigger) pdl_launch_dependents();
   if (tid == 0) {
     s_failed = 0;
     tma_prefetch_desc(&w_map);
@@ -140,7 +175,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         ok = mbar_wait(&raw_empty[slot], phase ^ 1u, kStatusPipeTimeout);     // first round passes immediately
         if (!ok) break;
         mbar_expect_tx(&raw_full[slot], kTcRawBytes);
-        tma_load_2d(raw + slot * kTcRawBytes, &w_map, n0, k_begin + i * kTcStageK, &raw_full[slot]);
+        if (p.w_slab_rows) tma_load_2d(raw + slot * kTcRawBytes, &w_map, 0, int(blockIdx.x) * p.w_slab_rows + k_begin + i * kTcStageK, &raw_full[slot]);
+        else tma_load_2d(raw + slot * kTcRawBytes, &w_map, n0, k_begin + i * kTcStageK, &raw_full[slot]);
+        if (gridDim.x > 300) trace_slot(10 + i);
       }
       if (!ok) s_failed = 1;
     }
@@ -155,6 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         const int slot = i % kTcOpStages;
         ok = mbar_wait(&op_full[slot], uint32_t(i / kTcOpStages) & 1u, kStatusPipeTimeout);
         if (!ok) break;
+        if (gridDim.x > 300) trace_slot(70 + i);
         tc_fence_after();
         const uint32_t a_addr = smem_u32(op_a + slot * kTcOpABytes), b_addr = smem_u32(op_b + slot * L::kOpBBytes);
 #pragma unroll
@@ -199,7 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     // The matching 64 columns of A: NMMA rows x 8 chunks of 8 halves, as K-major core matrices.  The
     // global loads run kAhead stages ahead of their use (register ring), so their latency is covered by
     // the dequantisation of the stages in between instead of sitting on every stage's critical path.
-    constexpr int kAhead = NMMA <= 64 ? 3 : 1;
+    constexpr int kAhead = NMMA <= 64 ? TIB_TC_AHEAD : 1;
     constexpr int kPer = NMMA * 8 / kTcDequantThreads;
     uint4 a_ring[kAhead][kPer];
     auto fetch_a = [&](uint4 (&dst)[kPer], int i) {
@@ -286,9 +324,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         asm volatile("bar.sync 2, 256;" ::: "memory");        // the eight dequantising warps
       }
     }
-    if constexpr (kAhead == 3) {
-      // all lead stages' rows requested together: one round trip instead of three
-      fetch_a(a_ring[0], 0); fetch_a(a_ring[1], 1); fetch_a(a_ring[2], 2);
+    if constexpr (kAhead > 1) {
+      // the first stages' rows are requested together: one round trip instead of one per stage
+#pragma unroll
+      for (int d = 0; d < kAhead; ++d) fetch_a(a_ring[d], d);
       for (int i = 0; i < lead; ++i) {
         store_a(a_ring[0], i, i);
         rotate();
@@ -312,6 +351,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       const int rslot = i % kTcRawStages, oslot = i % kTcOpStages;
       if (ok) ok = mbar_wait(&raw_full[rslot], uint32_t(i / kTcRawStages) & 1u, kStatusTmaTimeout);
       if (ok) ok = mbar_wait(&op_empty[oslot], (uint32_t(i / kTcOpStages) & 1u) ^ 1u, kStatusMmaTimeout);
+      if (gridDim.x > 300 && t == 0) trace_slot(30 + i);
       if (ok) {
         dequantise(rslot, oslot);
         store_a(a_ring[0], oslot, i);
@@ -321,22 +361,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       fetch_a(a_ring[kAhead - 1], i + kAhead);
       __syncwarp();
       if (lane == 0) { mbar_arrive(&raw_empty[rslot]); mbar_arrive(&op_full[oslot]); }
+      if (gridDim.x > 300 && t == 0) trace_slot(50 + i);
     }
     if (!ok) s_failed = 1;
   }
   pdl_wait();                 // every thread is past the dependency before the epilogue reads or writes global memory
+  trace_event(kTrGemmTc, 1);
   pdl_launch_dependents();
 
   // ---------------------------------------------------------------- epilogue (warps 2..5 own TMEM lanes 32*(warp%4)..)
   float* part = reinterpret_cast<float*>(smem);                // [NMMA][128] fp32, aliases the drained pipeline stages
   __shared__ long long s_row_base[NMMA];                       // K/V pool offset of each row of the tile (QKV projection only)
   bool acc_ok = true;
+  // fp32 output without a K split: staged through shared memory and written as whole 512-byte row pieces
+  const bool wide_rows = splits == 1 && p.out_fp32 && !p.k_pool && p.ldo % 4 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0;
   if (warp >= 2 && warp < 6) {
     if (p.k_pool) {
       for (int i = tid - 64; i < NMMA; i += 128) s_row_base[i] = m0 + i < p.m ? kv_row_base(p, m0 + i) : 0;
       asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps only
     }
     acc_ok = stages == 0 || mbar_wait(acc_ready, 0, kStatusMmaTimeout);
+    if (gridDim.x > 300 && tid == 64) trace_slot(90);
     tc_fence_after();
     const int lane_base = 32 * (warp & 3), n_local = lane_base + lane;
     const int col = n0 + n_local;
@@ -348,31 +393,60 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.f;
       }
+      if (gridDim.x > 300 && tid == 64) trace_slot(91);
       if (splits > 1) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) part[(c0 + i) * 128 + n_local] = v[i];
+      } else if (wide_rows) {
+        const float b = p.bias && col < p.n ? h2f(p.bias[col]) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) part[(c0 + i) * 128 + n_local] = v[i] + b;
       } else if (acc_ok && col < p.n) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) { const int row = m0 + c0 + i; if (row < p.m) gemv_store(p, row, col, v[i], p.k_pool ? s_row_base[c0 + i] : -1); }
       }
     }
+    if (wide_rows) {
+      // fp32 rows leave as 512-byte runs (one float4 per lane) instead of 32 separate 128-byte pieces per warp
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (acc_ok) {
+        for (int r = warp - 2; r < NMMA; r += 4) {
+          const int row = m0 + r, c = n0 + lane * 4;
+          if (row >= p.m) break;
+          const float4 f = *reinterpret_cast<const float4*>(part + r * 128 + lane * 4);
+          float* dst = static_cast<float*>(p.out) + size_t(row) * p.ldo + c;
+#ifdef TIB_EXP_NO_STORE
+          if (f.x != 12345.678f) continue;
+#endif
+          if (c + 3 < p.n) *reinterpret_cast<float4*>(dst) = f;
+          else {
+            if (c < p.n) dst[0] = f.x;
+            if (c + 1 < p.n) dst[1] = f.y;
+            if (c + 2 < p.n) dst[2] = f.z;
+          }
+        }
+      }
+    }
+    if (gridDim.x > 300 && tid == 64) trace_slot(92);
     tc_fence_before();
   }
   if (splits > 1) {
     cluster.sync();
     const bool good = !s_failed;
     const int cols_per_rank = 128 / splits, total = NMMA * cols_per_rank;
-    for (int i = tid; i < total; i += kTcThreads) {
+    for (int i = tid, s = 0; i < total; i += kTcThreads, ++s) {
       const int m = i / cols_per_rank, c = rank * cols_per_rank + (i - m * cols_per_rank);
       float v = 0.f;
       for (int r = 0; r < splits; ++r) v += cluster.map_shared_rank(part, r)[m * 128 + c];
       const int row = m0 + m, col = n0 + c;
-      if (row < p.m && col < p.n && good) gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1);
+      if (row < p.m && col < p.n && good) gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1, s == 0 ? &pre[0] : s == 1 ? &pre[1] : nullptr);
     }
     cluster.sync();
   } else {
     __syncthreads();
   }
+  trace_event(kTrGemmTc, 2);
+  if (gridDim.x > 300 && threadIdx.x == 0) trace_slot(99);
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 

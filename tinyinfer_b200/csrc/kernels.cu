@@ -25,14 +25,14 @@ namespace {
 
 // ---------------------------------------------------------------- generic launch helper
 template <typename... KArgs, typename... Args>
-cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, const LaunchOpts& o,
-                   int cluster_y, Args&&... args) {
+cudaError_t launch_clustered(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, const LaunchOpts& o,
+                             dim3 cluster, Args&&... args) {
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = o.stream;
   cudaLaunchAttribute attrs[2]; unsigned n = 0;
-  if (cluster_y > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attrs[n].id = cudaLaunchAttributeClusterDimension;
-    attrs[n].val.clusterDim.x = 1; attrs[n].val.clusterDim.y = unsigned(cluster_y); attrs[n].val.clusterDim.z = 1; ++n;
+    attrs[n].val.clusterDim.x = cluster.x; attrs[n].val.clusterDim.y = cluster.y; attrs[n].val.clusterDim.z = cluster.z; ++n;
   }
   if (o.pdl) {
     attrs[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -40,6 +40,11 @@ cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
   }
   cfg.attrs = attrs; cfg.numAttrs = n;
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, const LaunchOpts& o,
+                   int cluster_y, Args&&... args) {
+  return launch_clustered(kernel, grid, block, smem, o, dim3(1, unsigned(std::max(cluster_y, 1)), 1), std::forward<Args>(args)...);
 }
 
 // ---------------------------------------------------------------- tensor maps
@@ -130,7 +135,7 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   a.a = static_cast<const __half*>(c.a); a.w = c.w; a.scales = c.scales; a.bias = static_cast<const __half*>(c.bias);
   a.out = c.out; a.residual = static_cast<const __half*>(c.residual);
   a.lda = c.lda; a.ldo = c.ldo; a.ldw = c.ldw; a.m = c.m; a.n = c.n; a.k = c.k;
-  a.out_fp32 = c.out_fp32; a.gelu = c.gelu;
+  a.out_fp32 = c.out_fp32; a.gelu = c.gelu; a.early_epilogue = c.early_epilogue ? 1 : 0; a.early_trigger = c.early_trigger ? 1 : 0;
   if (c.kv) {
     a.k_pool = static_cast<__half*>(c.kv->k_pool); a.v_pool = static_cast<__half*>(c.kv->v_pool);
     a.kv_table = c.kv->table; a.kv_slots = c.kv->slots; a.kv_row_req = c.kv_row_req; a.kv_row_pos = c.kv_row_pos;
@@ -143,7 +148,12 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   // how many other rows share the call (the K split below depends on N and K only).
   if (c.w_int8 && (c.uniform_numerics || c.m >= tc_min_rows) && c.k % 8 == 0 && c.lda % 8 == 0 && reinterpret_cast<uintptr_t>(c.a) % 16 == 0) {
     CUtensorMap map; std::memset(&map, 0, sizeof map);
-    if (make_map_2d(&map, c.w, true, uint64_t(c.k), uint64_t(c.n), uint64_t(c.ldw), 128, uint32_t(kTcStageK), true)) {
+    const uint64_t slab_count = uint64_t(c.n + 127) / 128;
+    if (c.w_slab_rows && (c.w_slab_rows < c.k || c.w_slab_rows % kTcStageK)) return cudaErrorInvalidValue;
+    a.w_slab_rows = c.w_slab_rows;
+    const bool mapped = c.w_slab_rows ? make_map_2d(&map, c.w, true, slab_count * uint64_t(c.w_slab_rows), 128, 128, 128, uint32_t(kTcStageK), true)
+                                      : make_map_2d(&map, c.w, true, uint64_t(c.k), uint64_t(c.n), uint64_t(c.ldw), 128, uint32_t(kTcStageK), true);
+    if (mapped) {
       const int nmma = c.m <= 32 ? 32 : c.m <= 64 ? 64 : c.m <= 128 ? 128 : 256;
       if (c.ln_gamma) {
         if (nmma != 32 || c.k > 768 || c.lda != c.k) return cudaErrorNotSupported;
@@ -168,7 +178,7 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       }
     }
   }
-  if (c.ln_gamma) return cudaErrorNotSupported;               // only the tensor-core kernel has the LayerNorm prologue
+  if (c.ln_gamma || c.w_slab_rows) return cudaErrorNotSupported;   // only the tensor-core kernel has the LayerNorm prologue / reads tiles
   const int bn = c.w_int8 ? 128 : 64;
   const int mt = c.m >= 3 ? 4 : c.m;
   const int slabs = (c.n + bn - 1) / bn, m_tiles = (c.m + mt - 1) / mt;
@@ -184,6 +194,13 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   const dim3 grid(slabs, splits, m_tiles);
   if (c.w_int8) return tma ? launch_gemv_mt<int8_t, true>(mt, map, a, grid, o) : launch_gemv_mt<int8_t, false>(mt, map, a, grid, o);
   return tma ? launch_gemv_mt<__half, true>(mt, map, a, grid, o) : launch_gemv_mt<__half, false>(mt, map, a, grid, o);
+}
+
+cudaError_t retile_i8(const int8_t* src, long long ld, int k, int n, int8_t* dst, int slab_rows, cudaStream_t stream) {
+  if (!src || !dst || k < 1 || n < 1 || slab_rows < k) return cudaErrorInvalidValue;
+  const long long chunks = (long long)((n + 127) / 128) * slab_rows * 8;
+  retile_i8_kernel<<<unsigned((chunks + 255) / 256), 256, 0, stream>>>(src, ld, k, n, dst, slab_rows, chunks);
+  return cudaGetLastError();
 }
 
 cudaError_t sgemm(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
@@ -232,14 +249,22 @@ cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start
 int decode_chunks(int max_kv, int chunk) { return std::max(1, (max_kv + chunk - 1) / chunk); }
 
 cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kl, int batch, int max_kv, int chunk,
-                                   float* scratch_acc, float* scratch_ml, int* counters, const PagedKv& kv, const LaunchOpts& o) {
+                                   float* scratch_acc, float* scratch_ml, int* counters, const PagedKv& kv, const LaunchOpts& o,
+                                   bool early, bool whole_history) {
   if (kv.head_dim != 64) return cudaErrorInvalidValue;
   const int hidden = kv.heads * kv.head_dim;
   DecodeArgs p{};
   p.q = static_cast<const __half*>(qkv); p.q_sb = 3LL * hidden; p.q_sh = kv.head_dim;
   p.out = static_cast<__half*>(out); p.o_sb = hidden; p.o_sh = kv.head_dim;
   p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml; p.counters = counters;
-  p.batch = batch; p.heads = kv.heads; p.chunk = chunk; p.chunks = decode_chunks(max_kv, chunk);
+  p.batch = batch; p.heads = kv.heads; p.early = early ? 1 : 0;
+  if (whole_history) {
+    // One CTA of 8 warps walks the whole history of a (request, head) and merges in shared memory: no partials in
+    // global memory, no second stage, and a grid small enough to be resident at once.
+    p.chunk = 1 << 30; p.chunks = 1;
+    return launch(attn_decode_kernel<64, KvPaged, kDecodeWarpsWhole>, dim3(1, kv.heads, batch), dim3(kDecodeWarpsWhole * 32), 0, o, 1, p, paged(kv));
+  }
+  p.chunk = chunk; p.chunks = decode_chunks(max_kv, chunk);
   cudaError_t st = launch(attn_decode_kernel<64, KvPaged>, dim3(p.chunks, kv.heads, batch), dim3(kDecodeWarps * 32), 0, o, 1, p, paged(kv));
   if (st != cudaSuccess || p.chunks == 1 || counters) return st;
   return launch(attn_combine_kernel<64>, dim3(kv.heads, batch), dim3(64), 0, o, 1, p);
@@ -289,8 +314,13 @@ cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const void* wte, c
                 static_cast<const __half*>(wpe), static_cast<__half*>(x), rows, hidden);
 }
 cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out, int32_t* feedback,
-                   const int32_t* step, const LaunchOpts& o) {
-  return launch(argmax_kernel, dim3(rows), dim3(256), 0, o, 1, logits, pitch, cols, out, feedback, step);
+                   const int32_t* step, void* scratch, const LaunchOpts& o) {
+  // Enough CTAs to pull a row set of any size at memory speed: about two per SM in total.
+  int segments = 1;
+  if (scratch) segments = std::max(1, std::min({32, (2 * sm_count() + rows - 1) / rows, cols / 1024}));
+  auto* best = static_cast<unsigned long long*>(scratch);
+  auto* tickets = reinterpret_cast<unsigned int*>(best + rows);
+  return launch(argmax_kernel, dim3(rows, segments), dim3(256), 0, o, 1, logits, pitch, cols, out, feedback, step, best, tickets);
 }
 cudaError_t advance(int32_t* row_pos, int32_t* kv_lengths, int32_t* step, int batch, const LaunchOpts& o) {
   return launch(advance_kernel, dim3((batch + 63) / 64), dim3(64), 0, o, 1, row_pos, kv_lengths, step, batch);
@@ -305,6 +335,23 @@ cudaError_t sum_f64(const double* values, double* out, int length, cudaStream_t 
   sum_f64_kernel<<<1, 256, 0, stream>>>(values, out, length);
   return cudaGetLastError();
 }
+
+#ifdef TIB_TRACE
+// Development builds: copies the timeline log out and clears it; returns the number of events.
+extern "C" int ti_b200_trace_dump(unsigned long long* out, int capacity) {
+  unsigned int n = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&n, g_trace_count, sizeof n);
+  if (n > (1u << 16)) n = 1u << 16;
+  if (int(n) > capacity) n = unsigned(capacity);
+  cudaMemcpyFromSymbol(out, g_trace_buf, size_t(n) * sizeof(unsigned long long));
+  if (capacity >= (1 << 16))      // the slot marks ride in the last 1024 words
+    cudaMemcpyFromSymbol(out + (1 << 16) - 1024, g_trace_buf, 1024 * sizeof(unsigned long long), ((1 << 16) - 1024) * sizeof(unsigned long long));
+  const unsigned int zero = 0;
+  cudaMemcpyToSymbol(g_trace_count, &zero, sizeof zero);
+  return int(n);
+}
+#endif
 
 cudaError_t device_status_address(unsigned int** address) {
   return cudaGetSymbolAddress(reinterpret_cast<void**>(address), g_device_status);

@@ -31,6 +31,9 @@ struct GemmCall {
   const void* a = nullptr; int lda = 0;                 // fp16 [M,K]
   const void* w = nullptr; long long ldw = 0;           // [K,N], pitch in elements
   bool w_int8 = true;
+  // int8 only: w holds slab-major tiles [ceil(N/128)][w_slab_rows][128] (see retile_i8) instead of [K,N]; w_slab_rows >= k,
+  // multiple of 64.  Every 64-row stage of a CTA is then one contiguous 8 KB block of device memory.
+  int w_slab_rows = 0;
   const float* scales = nullptr;
   const void* bias = nullptr;                           // fp16 [N] or null
   void* out = nullptr; int ldo = 0; bool out_fp32 = false;
@@ -42,10 +45,18 @@ struct GemmCall {
   // LayerNorm prologue: `a` holds rows before normalisation (m <= 32, k <= 768, int8 weights reachable by TMA);
   // gemm() returns cudaErrorNotSupported when the shape cannot take it.
   const void* ln_gamma = nullptr; const void* ln_beta = nullptr; float ln_eps = 1e-5f;
+  // bias and residual were complete before the kernel ahead of this launch in the stream started (so they may be
+  // read ahead of the programmatic dependency wait)
+  bool early_epilogue = false;
+  // the kernel after this one has useful work ahead of its dependency wait: let it start as early as possible
+  bool early_trigger = false;
   bool uniform_numerics = false;                         // tensor-core kernel for any row count (batch-invariant results)
   int m = 0, n = 0, k = 0;
 };
 TIB_EXPORT cudaError_t gemm(const GemmCall& call, const LaunchOpts& opts);
+
+// dst[slab][row][c] = row < k && slab*128+c < n ? src[row*ld + slab*128+c] : 0, for ceil(n/128) slabs of slab_rows rows.
+TIB_EXPORT cudaError_t retile_i8(const int8_t* src, long long ld, int k, int n, int8_t* dst, int slab_rows, cudaStream_t stream);
 
 TIB_EXPORT cudaError_t sgemm(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream);
 
@@ -64,9 +75,14 @@ TIB_EXPORT cudaError_t attention_paged(const void* qkv, void* out, const int32_t
 // [batch*heads*chunks*2]; chunks = ceil(max_kv / chunk).
 // counters: optional int [batch*heads], zero between launches; when given the merge of the chunk
 // partials happens inside the same kernel (no second launch).
+// early: kv_lengths, the page table and all keys but each request's newest were complete before the kernel
+// ahead of this launch started (true inside a decode step: only the QKV projection precedes it); they are
+// then read ahead of the dependency wait.  whole_history: one CTA per (request, head) instead of one per chunk;
+// chunk, scratch and counters are not used.
 TIB_EXPORT cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kv_lengths,
                                               int batch, int max_kv, int chunk, float* scratch_acc, float* scratch_ml,
-                                              int* counters, const PagedKv& kv, const LaunchOpts& opts);
+                                              int* counters, const PagedKv& kv, const LaunchOpts& opts,
+                                              bool early = false, bool whole_history = false);
 TIB_EXPORT int decode_chunks(int max_kv, int chunk);
 // Same decode attention over packed k/v[B,H,K,D] with q[B,H,1,D] (additive operator export).
 TIB_EXPORT cudaError_t attention_packed_decode(const void* q, const void* k, const void* v, void* y,
@@ -82,8 +98,10 @@ TIB_EXPORT cudaError_t softmax(const void* x, void* y, int rows, int cols, cudaS
 TIB_EXPORT cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const void* wte, const void* wpe,
                              void* x, int rows, int hidden, const LaunchOpts& opts);
 // out[(*step) * rows + r] = argmax of row r (step may be null = 0); feedback[r] too when non-null.
+// scratch: null, or 12 * rows bytes of device memory (8-byte aligned, zero before its first use, left zero
+// by every call) that lets several CTAs share a row.
 TIB_EXPORT cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out,
-                              int32_t* feedback, const int32_t* step, const LaunchOpts& opts);
+                              int32_t* feedback, const int32_t* step, void* scratch, const LaunchOpts& opts);
 // row_pos[b]++, kv_lengths[b]++ for b < batch, and (*step)++.
 TIB_EXPORT cudaError_t advance(int32_t* row_pos, int32_t* kv_lengths, int32_t* step, int batch, const LaunchOpts& opts);
 

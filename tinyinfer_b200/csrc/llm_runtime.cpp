@@ -54,6 +54,7 @@ constexpr int kDecodeChunk = 128;    // keys per decode-attention CTA
 struct Linear {
   const void* w = nullptr; const float* scales = nullptr; const void* bias = nullptr;
   int k = 0, n = 0; long long ldw = 0;
+  int slab_rows = 0;                 // > 0: w holds slab-major tiles [ceil(n/128)][slab_rows][128] (int8 only)
 };
 struct Block { const void *ln1_g, *ln1_b, *ln2_g, *ln2_b; Linear qkv, proj, fc, proj2; };
 
@@ -149,6 +150,21 @@ struct ti_llm_model {
     ck(cudaMemcpy2DAsync(padded, size_t(vpitch) * esize, head.w, size_t(V) * esize, size_t(V) * esize, size_t(H),
                          cudaMemcpyDeviceToDevice, stream));
     head.w = padded; head.ldw = vpitch;
+    // INT8 matrices are re-tiled once into slab-major order: the 128 output channels of a CTA become
+    // one contiguous run of K x 128 bytes, so each TMA stage is a single 8 KB block of device memory
+    // instead of 64 separate 128-byte pieces one matrix row apart.
+    bool tiled = int8 && H % 8 == 0;
+    if (const char* v = std::getenv("TINYINFER_B200_TILED")) tiled = tiled && std::atoi(v) != 0;
+    if (tiled) {
+      auto retile = [&](Linear& l) {
+        const int rows = (l.k + 63) / 64 * 64;
+        int8_t* tiles = dev<int8_t>(size_t((l.n + 127) / 128) * rows * 128);
+        ck(tib::retile_i8(static_cast<const int8_t*>(l.w), l.ldw, l.k, l.n, tiles, rows, stream));
+        l.w = tiles; l.slab_rows = rows;
+      };
+      for (Block& b : blocks) { retile(b.qkv); retile(b.proj); retile(b.fc); retile(b.proj2); }
+      retile(head);
+    }
 
     max_rows = size_t(opt.max_batch) * opt.capacity;
     const size_t r = max_rows;
@@ -178,11 +194,17 @@ struct ti_llm_model {
     d_next = dev<int32_t>(size_t(opt.max_batch)); h_next = host<int32_t>(size_t(opt.max_batch));
     d_seg = dev<int32_t>(size_t(5) * opt.max_batch); h_seg = host<int32_t>(size_t(5) * opt.max_batch);
     d_step = dev<int32_t>(1);
+    d_argmax = dev<uint8_t>(size_t(12) * opt.max_batch + 8);
+    ck(cudaMemsetAsync(d_argmax, 0, size_t(12) * opt.max_batch + 8, stream));
     d_log = dev<int32_t>(size_t(opt.capacity) * opt.max_batch); h_log = host<int32_t>(size_t(opt.capacity) * opt.max_batch);
     if (const char* v = std::getenv("TINYINFER_B200_GRAPH")) use_graph = std::atoi(v) != 0;   // debugging aids: 0 = plain launches
     if (const char* v = std::getenv("TINYINFER_B200_PDL")) use_pdl = std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_EARLY_TRIGGER")) early_trigger = std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_EARLY_EPILOGUE")) early_epilogue = std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_ATTN_EARLY")) attn_early = std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_ATTN_WHOLE")) attn_whole = std::atoi(v) != 0;
     fuse_ln = int8 && shape.hidden <= 768;
-    if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) fuse_ln = fuse_ln && std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) { fuse_ln_rows = std::min(32, std::atoi(v)); fuse_ln = fuse_ln && fuse_ln_rows > 0; }
     h_status = host<unsigned int>(1); *h_status = 0;
     d_score_tokens = dev<int32_t>(size_t(opt.capacity)); d_score_mask = dev<uint8_t>(size_t(opt.capacity));
     d_loss = dev<double>(size_t(opt.capacity)); d_loss_sum = dev<double>(1);
@@ -212,12 +234,15 @@ struct ti_llm_model {
             const void* ln_g = nullptr, const void* ln_b = nullptr) {
     tib::GemmCall c;
     c.kv = kv; c.kv_row_req = row_req; c.kv_row_pos = row_pos; c.ln_gamma = ln_g; c.ln_beta = ln_b;
-    c.a = a; c.lda = l.k; c.w = l.w; c.ldw = l.ldw; c.w_int8 = int8; c.scales = l.scales; c.bias = l.bias;
+    c.a = a; c.lda = l.k; c.w = l.w; c.ldw = l.ldw; c.w_slab_rows = l.slab_rows; c.w_int8 = int8; c.scales = l.scales; c.bias = l.bias;
     c.out = out; c.ldo = fp32 ? vpitch : l.n; c.out_fp32 = fp32; c.residual = residual; c.gelu = gelu;
     c.m = rows; c.n = l.n; c.k = l.k;
     // One kernel family for every batch size: logits of a request are bit-identical whatever it is
     // batched with, the property the reference's gates rely on (llm/gpu_correctness.py:62-66).
     c.uniform_numerics = true;
+    // Residual streams are written at least two kernels before the GEMM that adds them, biases at load.
+    c.early_epilogue = early_epilogue;
+    c.early_trigger = kv != nullptr && attn_early && early_trigger;   // decode attention prefetches its history meanwhile
     tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
     ck(tib::gemm(c, o));
   }
@@ -241,13 +266,13 @@ struct ti_llm_model {
       kv.layer = l;
       // LayerNorm as a prologue of the consuming GEMM while one warp per row suffices (every CTA of that GEMM
       // repeats the row statistics, so beyond 8 rows the separate kernel is cheaper).
-      const bool fused = fuse_ln && m.rows <= 8;
+      const bool fused = fuse_ln && m.rows <= fuse_ln_rows;
       if (fused) gemm(x, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos, b.ln1_g, b.ln1_b);
       else {
         ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, m.rows, H, 1e-5f, o));
         gemm(norm, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos);   // Q -> qkv buffer, K/V -> their pages
       }
-      if (m.max_q == 1) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o));
+      if (m.max_q == 1) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o, attn_early, attn_whole));
       else ck(tib::attention_paged(qkv, attn, m.row_start, m.qlens, m.kvlens, m.offsets, m.batch, m.max_q, m.max_kv, kv, o));
       gemm(attn, b.proj, res, m.rows, false, x, false);             // res = x + proj(attn)
       if (fused) gemm(res, b.fc, act, m.rows, false, nullptr, true, nullptr, nullptr, nullptr, b.ln2_g, b.ln2_b);
@@ -325,8 +350,12 @@ struct ti_llm_model {
   // so a step can be replayed as a CUDA graph; graphs are cached per (batch, attention chunk count).
   struct StepGraph { int batch, chunks; cudaGraphExec_t exec; };
   std::vector<StepGraph> graphs;
+  uint8_t* d_argmax = nullptr;      // per-row merge words of the argmax kernel (zero between launches)
   int32_t *d_seg = nullptr, *h_seg = nullptr, *d_step = nullptr, *d_log = nullptr, *h_log = nullptr;
   bool use_graph = true, use_pdl = true;
+  bool early_epilogue = false, early_trigger = false;
+  bool attn_early = true, attn_whole = true;     // decode attention: reads ahead of the dependency wait; one CTA per (request, head)
+  int fuse_ln_rows = 8;             // largest row count whose LayerNorms run inside the consuming GEMM
   bool fuse_ln = false;             // int8 weights and rows of at most 768 values: LayerNorm runs inside the consuming GEMM
 
   int32_t* seg(int field) const { return d_seg + size_t(field) * opt.max_batch; }
@@ -337,12 +366,12 @@ struct ti_llm_model {
     m.rows = batch; m.batch = batch; m.max_q = 1; m.max_kv = max_kv;
     run_layers(m);
     tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
-    if (fuse_ln && batch <= 8) gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b);
+    if (fuse_ln && batch <= fuse_ln_rows) gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b);
     else {
       ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, last, batch, shape.hidden, 1e-5f, o));
       gemm(last, head, logits, batch, true, nullptr, false);
     }
-    ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_log, seg(0), d_step, o));
+    ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_log, seg(0), d_step, d_argmax, o));
     ck(tib::advance(seg(2), seg(3), d_step, batch, o));
   }
 
@@ -428,7 +457,7 @@ struct ti_llm_model {
         if (out) ck(cudaMemcpy2DAsync(out, size_t(shape.vocab) * 4, logits, size_t(vpitch) * 4, size_t(shape.vocab) * 4, size_t(batch),
                                       cudaMemcpyDeviceToHost, stream));
         if (greedy) {
-          ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_next, nullptr, nullptr, o));
+          ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_next, nullptr, nullptr, d_argmax, o));
           ck(cudaMemcpyAsync(h_next, d_next, size_t(batch) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
         }
       }

@@ -12,6 +12,7 @@ namespace tib {
 __global__ void __launch_bounds__(256)
 embed_kernel(const int32_t* ids, const int32_t* row_pos, const __half* wte, const __half* wpe,
              __half* x, int rows, int hidden) {
+  trace_event(kTrEmbed, 0);
   pdl_wait();
   const int chunks = hidden / 8;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * chunks;
@@ -29,18 +30,44 @@ embed_kernel(const int32_t* ids, const int32_t* row_pos, const __half* wte, cons
 }
 
 // Greedy argmax of fp32 logits, lowest id on ties (reference argmax, llm/src/runtime.cu:59-66).
-// grid = rows, block = 256.  The winner of row r goes to out[(*step) * rows + r] (step = 0 when
-// `step` is null) and, when `feedback` is non-null, to feedback[r] as the next step's input id.
+// grid = (rows, segments), block = 256.  The winner of row r (largest value, lowest index among equals)
+// goes to out[(*step) * rows + r] (step = 0 when `step` is null) and, when `feedback` is non-null, to
+// feedback[r] as the next step's input id.  With several segments per row each CTA scans one piece and
+// publishes (value, index) packed into one 64-bit word through atomicMax on best[r]; the CTA that takes
+// the last ticket of the row writes the result and leaves best[r] and tickets[r] at zero again.
+// `best` / `tickets`: rows words each, zero before the first launch; unused with one segment.
+__device__ __forceinline__ unsigned long long argmax_pack(float v, int index) {
+  const uint32_t u = __float_as_uint(v + 0.f);                      // -0 -> +0: equal values must compare equal
+  const uint32_t ordered = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return (unsigned long long)ordered << 32 | (0xffffffffu - uint32_t(index));
+}
+
 __global__ void __launch_bounds__(256)
-argmax_kernel(const float* logits, long long pitch, int cols, int32_t* out, int32_t* feedback, const int32_t* step) {
+argmax_kernel(const float* logits, long long pitch, int cols, int32_t* out, int32_t* feedback, const int32_t* step,
+              unsigned long long* best, unsigned int* tickets) {
+  trace_event(kTrArgmax, 0);
   __shared__ float best_v[8];
   __shared__ int best_i[8];
+  const int r = blockIdx.x, segments = gridDim.y;
+  const int per = ((cols + segments - 1) / segments + 3) & ~3;
+  const int begin = blockIdx.y * per, end = min(cols, begin + per);
+  const float* row = logits + (long long)r * pitch;
+  const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
   pdl_wait();
-  const float* row = logits + (long long)blockIdx.x * pitch;
+  trace_event(kTrArgmax, 1);
   float bv = -CUDART_INF_F; int bi = 0x7fffffff;
-  for (int c = threadIdx.x; c < cols; c += 256) {
-    const float v = row[c];
-    if (v > bv || (v == bv && c < bi)) { bv = v; bi = c; }
+  auto take = [&](float v, int c) { if (v > bv || (v == bv && c < bi)) { bv = v; bi = c; } };
+  if (vec) {
+    for (int c = begin + threadIdx.x * 4; c < end; c += 1024) {
+      if (c + 3 < end) {
+        const float4 v = *reinterpret_cast<const float4*>(row + c);
+        take(v.x, c); take(v.y, c + 1); take(v.z, c + 2); take(v.w, c + 3);
+      } else {
+        for (int e = c; e < end; ++e) take(row[e], e);
+      }
+    }
+  } else {
+    for (int c = begin + threadIdx.x; c < end; c += 256) take(row[c], c);
   }
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) {
@@ -54,13 +81,44 @@ argmax_kernel(const float* logits, long long pitch, int cols, int32_t* out, int3
   if (threadIdx.x == 0) {
     for (int w = 1; w < 8; ++w)
       if (best_v[w] > bv || (best_v[w] == bv && best_i[w] < bi)) { bv = best_v[w]; bi = best_i[w]; }
-    out[(step ? size_t(*step) * gridDim.x : 0) + blockIdx.x] = bi;
-    if (feedback) feedback[blockIdx.x] = bi;
+    bool write = true;
+    if (segments > 1) {
+      if (bi != 0x7fffffff) atomicMax(best + r, argmax_pack(bv, bi));
+      __threadfence();
+      write = atomicAdd(tickets + r, 1u) == unsigned(segments - 1);
+      if (write) {
+        __threadfence();
+        const unsigned long long key = atomicExch(best + r, 0ull);
+        bi = key ? int(0xffffffffu - uint32_t(key)) : 0x7fffffff;
+        tickets[r] = 0;
+      }
+    }
+    if (write) {
+      out[(step ? size_t(*step) * gridDim.x : 0) + r] = bi;
+      if (feedback) feedback[r] = bi;
+    }
   }
+}
+
+// Weights [k][ld] -> slab-major tiles [ceil(n/128)][slab_rows][128] with zero fill; one thread per 16 output bytes.
+__global__ void retile_i8_kernel(const int8_t* src, long long ld, int k, int n, int8_t* dst, int slab_rows, long long chunks) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= chunks) return;
+  const int c16 = int(i % 8);
+  const long long r = i / 8;
+  const int row = int(r % slab_rows), slab = int(r / slab_rows);
+  int8_t v[16];
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const int col = slab * 128 + c16 * 16 + e;
+    v[e] = row < k && col < n ? src[(long long)row * ld + col] : int8_t(0);
+  }
+  *reinterpret_cast<uint4*>(dst + i * 16) = *reinterpret_cast<const uint4*>(v);
 }
 
 // End of a device-resident decode step: every request moves one position on.
 __global__ void advance_kernel(int32_t* row_pos, int32_t* kv_lengths, int32_t* step, int batch) {
+  trace_event(kTrAdvance, 0);
   pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < batch) { row_pos[b] += 1; kv_lengths[b] += 1; }
