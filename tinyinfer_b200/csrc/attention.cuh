@@ -33,8 +33,10 @@ struct KvPacked {
   __device__ __forceinline__ size_t offset(int b, int h, int key) const {
     return ((size_t(b) * heads + h) * kv_len + key) * d;
   }
-  // offset of key t0 of a 32-key tile (t0 % 32 == 0); the tile's keys follow at stride d
-  __device__ __forceinline__ size_t tile_base(int b, int h, int t0) const { return offset(b, h, t0); }
+  // A 32-key tile (t0 % 32 == 0) is named by a reference that does not depend on the head; its keys follow
+  // each other at stride d from tile_offset(ref, b, h).
+  __device__ __forceinline__ int tile_ref(int, int t0) const { return t0; }
+  __device__ __forceinline__ size_t tile_offset(int ref, int b, int h) const { return offset(b, h, ref); }
 };
 struct KvPaged {
   const __half* k; const __half* v;       // page pools
@@ -45,7 +47,10 @@ struct KvPaged {
     const int page = table[size_t(slots[b]) * table_pitch + (key / kPageTokens)];
     return (((size_t(page) * layers + layer) * heads + h) * kPageTokens + (key % kPageTokens)) * d;
   }
-  __device__ __forceinline__ size_t tile_base(int b, int h, int t0) const { return offset(b, h, t0); }   // one page per tile
+  __device__ __forceinline__ int tile_ref(int b, int t0) const { return table[size_t(slots[b]) * table_pitch + t0 / kPageTokens]; }   // its page
+  __device__ __forceinline__ size_t tile_offset(int ref, int, int h) const {
+    return ((size_t(ref) * layers + layer) * heads + h) * kPageTokens * d;
+  }
 };
 
 struct AttnArgs {
@@ -162,6 +167,7 @@ struct DecodeArgs {
   // kernel ahead of this one started, so they are read before the dependency wait (their latency then hides
   // behind that kernel); the newest key and the query are read after it.
   int early;
+  int early_trigger;                                 // release the next kernel's launch before this one's own wait
 };
 
 // grid = (chunks, heads, batch), block = 32 * W.
@@ -194,21 +200,24 @@ attn_decode_kernel(const DecodeArgs p, const KV kv) {
   };
 #pragma unroll
   for (int i = 0; i < STEPS; ++i) { kreg[i] = make_uint4(0, 0, 0, 0); vreg[i] = kreg[i]; }
-  int len = 0;
-  size_t base_first = 0;
+  // Early reads: the length, the references (pages) of this warp's first four tiles, and the first tile's keys.
+  constexpr int kRefs = 4;
+  int len = 0, refs[kRefs];
+#pragma unroll
+  for (int r = 0; r < kRefs; ++r) refs[r] = 0;
   if (p.early) {
     len = p.kv_lengths[b];
     const int end_early = min(len, begin + p.chunk);
-    if (t_first < end_early) {
-      base_first = kv.tile_base(b, h, t_first);
-      load_tile(base_first, t_first, t_first, min(end_early, len - 1));
-    }
+#pragma unroll
+    for (int r = 0; r < kRefs; ++r) if (t_first + r * W * 32 < end_early) refs[r] = kv.tile_ref(b, t_first + r * W * 32);
+    if (t_first < end_early) load_tile(kv.tile_offset(refs[0], b, h), t_first, t_first, min(end_early, len - 1));
   }
+  if (p.early_trigger) pdl_launch_dependents();
   pdl_wait();
   trace_event(kTrAttnDecode, 1);
   if (!p.early) len = p.kv_lengths[b];
   const int end = min(len, begin + p.chunk);
-  if (begin >= end && blockIdx.x != 0) return;   // nothing to do for this chunk (uniform per CTA)
+  if (begin >= end && blockIdx.x != 0) return;        // nothing to do for this chunk (uniform per CTA)
 
   const uint4 qraw = *reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + dp * 8);
   const __half2* q2 = reinterpret_cast<const __half2*>(&qraw);
@@ -216,13 +225,17 @@ attn_decode_kernel(const DecodeArgs p, const KV kv) {
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 
-  for (int t0 = t_first; t0 < end; t0 += W * 32) {
-    if (t0 == t_first && p.early) {
-      load_tile(base_first, t0, max(t0, len - 1), end);          // the newest key, if this tile holds it
+  int it = 0;
+  for (int t0 = t_first; t0 < end; t0 += W * 32, ++it) {
+    if (it == 0 && p.early) {
+      load_tile(kv.tile_offset(refs[0], b, h), t0, max(t0, len - 1), end);   // the newest key, if this tile holds it
     } else {
 #pragma unroll
       for (int i = 0; i < STEPS; ++i) { kreg[i] = make_uint4(0, 0, 0, 0); vreg[i] = kreg[i]; }
-      load_tile(kv.tile_base(b, h, t0), t0, t0, end);
+      int ref;
+      if (p.early && it < kRefs) ref = it == 1 ? refs[1] : it == 2 ? refs[2] : refs[3];
+      else ref = kv.tile_ref(b, t0);
+      load_tile(kv.tile_offset(ref, b, h), t0, t0, end);
     }
     float sc[STEPS], tile_max = -CUDART_INF_F;
 #pragma unroll

@@ -77,8 +77,9 @@ constexpr int kLnMaxCols = 4096;     // rows up to this width are staged in shar
 // the previous kernel, so they are staged before the dependency wait and their latency is hidden.
 __global__ void __launch_bounds__(128)
 layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, const __half* b, __half* y,
-                 int rows, int cols, float eps) {
+                 int rows, int cols, float eps, int early_trigger) {
   trace_event(kTrLayerNorm, 0);
+  if (early_trigger) pdl_launch_dependents();
   extern __shared__ float ln_rows[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x * 4 + warp;
   const bool staged = cols <= kLnMaxCols;

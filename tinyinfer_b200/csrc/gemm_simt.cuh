@@ -48,7 +48,6 @@ struct GemvArgs {
   int m, n, k;
   int k_chunk;                // K rows per CTA, multiple of kGemvStageRows
   int early_trigger;          // release the dependent launch at once: the next kernel has work that does not need this one's output
-  int early_epilogue;         // bias and residual were complete before the kernel ahead of this launch started: read them early
   int w_slab_rows;            // tensor-core kernel: 0 = weights are [K][ldw]; else slab-major [N/128][w_slab_rows][128]
   int out_fp32, gelu;
   // K/V placement (QKV projection of the model runtime; k_pool null elsewhere): columns at or past
@@ -119,14 +118,9 @@ __device__ __forceinline__ void gemv_consume_stage(const uint8_t* stage, const _
   }
 }
 
-// Epilogue inputs of one output element fetched ahead of time (see GemvArgs::early_epilogue).
-struct EpiloguePre { __half bias, residual; bool valid; };   // raw values: nothing waits on the loads until they are used
-
 // row_base: kv_row_base(p, row) when the caller has it at hand, else -1 (looked up here).
-__device__ __forceinline__ void gemv_store(const GemvArgs& p, int row, int col, float acc, long long row_base = -1,
-                                           const EpiloguePre* pre = nullptr) {
-  const bool have = pre && pre->valid;
-  const float v = acc + (have ? h2f(pre->bias) : (p.bias ? h2f(p.bias[col]) : 0.f));
+__device__ __forceinline__ void gemv_store(const GemvArgs& p, int row, int col, float acc, long long row_base = -1) {
+  const float v = acc + (p.bias ? h2f(p.bias[col]) : 0.f);
   if (p.k_pool && col >= p.kv_hidden) {
     const int c = col - p.kv_hidden, which = c >= p.kv_hidden, e = which ? c - p.kv_hidden : c;
     if (row_base < 0) row_base = kv_row_base(p, row);
@@ -136,7 +130,7 @@ __device__ __forceinline__ void gemv_store(const GemvArgs& p, int row, int col, 
   if (p.out_fp32) { static_cast<float*>(p.out)[size_t(row) * p.ldo + col] = v; return; }
   __half h = f2h(v);
   if (p.gelu) h = f2h(gelu_tanh(h2f(h)));
-  if (p.residual) h = f2h(h2f(have ? pre->residual : p.residual[size_t(row) * p.ldo + col]) + h2f(h));
+  if (p.residual) h = f2h(h2f(p.residual[size_t(row) * p.ldo + col]) + h2f(h));
   static_cast<__half*>(p.out)[size_t(row) * p.ldo + col] = h;
 }
 

@@ -130,26 +130,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   const int stages = k_end > k_begin ? (k_end - k_begin + kTcStageK - 1) / kTcStageK : 0;
   constexpr uint32_t kTmemCols = NMMA < 32 ? 32 : NMMA;
 
-  // Split-K launches: the (at most two) output elements this thread finishes after the cluster reduction
-  // are known now; when their bias and residual do not come from the kernel directly ahead, fetch them here.
-  EpiloguePre pre[2];
-  pre[0].valid = pre[1].valid = false;
-  if (splits > 1 && p.early_epilogue && !p.out_fp32) {
-    const int cols_per_rank = 128 / splits, total = NMMA * cols_per_rank;
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      const int i = tid + s * kTcThreads;
-      if (i < total) {
-        const int m = i / cols_per_rank, c = rank * cols_per_rank + (i - m * cols_per_rank);
-        const int row = m0 + m, col = n0 + c;
-        if (row < p.m && col < p.n) {
-          pre[s].bias = p.bias ? p.bias[col] : f2h(0.f);
-          pre[s].residual = p.residual && !(p.k_pool && col >= p.kv_hidden) ? p.residual[size_t(row) * p.ldo + col] : f2h(0.f);
-          pre[s].valid = true;
-        }
-      }
-    }
-  }
   if (p.early_trigger) pdl_launch_dependents();
   if (tid == 0) {
     s_failed = 0;
@@ -434,12 +414,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     cluster.sync();
     const bool good = !s_failed;
     const int cols_per_rank = 128 / splits, total = NMMA * cols_per_rank;
-    for (int i = tid, s = 0; i < total; i += kTcThreads, ++s) {
+    for (int i = tid; i < total; i += kTcThreads) {
       const int m = i / cols_per_rank, c = rank * cols_per_rank + (i - m * cols_per_rank);
       float v = 0.f;
       for (int r = 0; r < splits; ++r) v += cluster.map_shared_rank(part, r)[m * 128 + c];
       const int row = m0 + m, col = n0 + c;
-      if (row < p.m && col < p.n && good) gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1, s == 0 ? &pre[0] : s == 1 ? &pre[1] : nullptr);
+      if (row < p.m && col < p.n && good) gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1);
     }
     cluster.sync();
   } else {

@@ -135,7 +135,7 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   a.a = static_cast<const __half*>(c.a); a.w = c.w; a.scales = c.scales; a.bias = static_cast<const __half*>(c.bias);
   a.out = c.out; a.residual = static_cast<const __half*>(c.residual);
   a.lda = c.lda; a.ldo = c.ldo; a.ldw = c.ldw; a.m = c.m; a.n = c.n; a.k = c.k;
-  a.out_fp32 = c.out_fp32; a.gelu = c.gelu; a.early_epilogue = c.early_epilogue ? 1 : 0; a.early_trigger = c.early_trigger ? 1 : 0;
+  a.out_fp32 = c.out_fp32; a.gelu = c.gelu; a.early_trigger = o.early_trigger && o.pdl ? 1 : 0;
   if (c.kv) {
     a.k_pool = static_cast<__half*>(c.kv->k_pool); a.v_pool = static_cast<__half*>(c.kv->v_pool);
     a.kv_table = c.kv->table; a.kv_slots = c.kv->slots; a.kv_row_req = c.kv_row_req; a.kv_row_pos = c.kv_row_pos;
@@ -250,14 +250,14 @@ int decode_chunks(int max_kv, int chunk) { return std::max(1, (max_kv + chunk - 
 
 cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kl, int batch, int max_kv, int chunk,
                                    float* scratch_acc, float* scratch_ml, int* counters, const PagedKv& kv, const LaunchOpts& o,
-                                   bool early, bool whole_history) {
+                                   bool early, bool whole_history, bool early_trigger) {
   if (kv.head_dim != 64) return cudaErrorInvalidValue;
   const int hidden = kv.heads * kv.head_dim;
   DecodeArgs p{};
   p.q = static_cast<const __half*>(qkv); p.q_sb = 3LL * hidden; p.q_sh = kv.head_dim;
   p.out = static_cast<__half*>(out); p.o_sb = hidden; p.o_sh = kv.head_dim;
   p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml; p.counters = counters;
-  p.batch = batch; p.heads = kv.heads; p.early = early ? 1 : 0;
+  p.batch = batch; p.heads = kv.heads; p.early = early ? 1 : 0; p.early_trigger = early_trigger ? 1 : 0;
   if (whole_history) {
     // One CTA of 8 warps walks the whole history of a (request, head) and merges in shared memory: no partials in
     // global memory, no second stage, and a grid small enough to be resident at once.
@@ -293,7 +293,7 @@ cudaError_t layernorm(const void* x, const int32_t* row_index, const void* g, co
     if (ready != cudaSuccess) return ready;
   }
   return launch(layernorm_kernel, dim3((rows + 3) / 4), dim3(128), smem, o, 1, static_cast<const __half*>(x), row_index,
-                static_cast<const __half*>(g), static_cast<const __half*>(b), static_cast<__half*>(y), rows, cols, eps);
+                static_cast<const __half*>(g), static_cast<const __half*>(b), static_cast<__half*>(y), rows, cols, eps, o.pdl && o.early_trigger ? 1 : 0);
 }
 cudaError_t gelu(const void* x, void* y, long long count, cudaStream_t stream) {
   const int vec = (reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) ? 1 : 0;

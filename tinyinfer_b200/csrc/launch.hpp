@@ -16,6 +16,10 @@ namespace tib {
 struct LaunchOpts {
   cudaStream_t stream = nullptr;
   bool pdl = false;              // programmatic dependent launch: prologue may overlap the previous kernel
+  // With pdl: release the launch of the kernel after this one at once instead of after this kernel's own dependency
+  // wait.  Only sound when that kernel reads nothing but constants (weights, parameters) ahead of its own wait.
+  // Honoured by layernorm and gemm (tensor-core path).
+  bool early_trigger = false;
 };
 
 // Paged KV pool of the model runtime; see attention.cuh for the page layout.
@@ -45,11 +49,6 @@ struct GemmCall {
   // LayerNorm prologue: `a` holds rows before normalisation (m <= 32, k <= 768, int8 weights reachable by TMA);
   // gemm() returns cudaErrorNotSupported when the shape cannot take it.
   const void* ln_gamma = nullptr; const void* ln_beta = nullptr; float ln_eps = 1e-5f;
-  // bias and residual were complete before the kernel ahead of this launch in the stream started (so they may be
-  // read ahead of the programmatic dependency wait)
-  bool early_epilogue = false;
-  // the kernel after this one has useful work ahead of its dependency wait: let it start as early as possible
-  bool early_trigger = false;
   bool uniform_numerics = false;                         // tensor-core kernel for any row count (batch-invariant results)
   int m = 0, n = 0, k = 0;
 };
@@ -78,11 +77,12 @@ TIB_EXPORT cudaError_t attention_paged(const void* qkv, void* out, const int32_t
 // early: kv_lengths, the page table and all keys but each request's newest were complete before the kernel
 // ahead of this launch started (true inside a decode step: only the QKV projection precedes it); they are
 // then read ahead of the dependency wait.  whole_history: one CTA per (request, head) instead of one per chunk;
-// chunk, scratch and counters are not used.
+// chunk, scratch and counters are not used.  early_trigger: the kernel launched after this one may start at once
+// (it must then read nothing but constants ahead of its own dependency wait).
 TIB_EXPORT cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kv_lengths,
                                               int batch, int max_kv, int chunk, float* scratch_acc, float* scratch_ml,
                                               int* counters, const PagedKv& kv, const LaunchOpts& opts,
-                                              bool early = false, bool whole_history = false);
+                                              bool early = false, bool whole_history = false, bool early_trigger = false);
 TIB_EXPORT int decode_chunks(int max_kv, int chunk);
 // Same decode attention over packed k/v[B,H,K,D] with q[B,H,1,D] (additive operator export).
 TIB_EXPORT cudaError_t attention_packed_decode(const void* q, const void* k, const void* v, void* y,

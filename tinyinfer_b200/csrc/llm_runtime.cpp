@@ -199,9 +199,10 @@ struct ti_llm_model {
     d_log = dev<int32_t>(size_t(opt.capacity) * opt.max_batch); h_log = host<int32_t>(size_t(opt.capacity) * opt.max_batch);
     if (const char* v = std::getenv("TINYINFER_B200_GRAPH")) use_graph = std::atoi(v) != 0;   // debugging aids: 0 = plain launches
     if (const char* v = std::getenv("TINYINFER_B200_PDL")) use_pdl = std::atoi(v) != 0;
-    if (const char* v = std::getenv("TINYINFER_B200_EARLY_TRIGGER")) early_trigger = std::atoi(v) != 0;
-    if (const char* v = std::getenv("TINYINFER_B200_EARLY_EPILOGUE")) early_epilogue = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_EARLY")) attn_early = std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_LN_TRIGGER")) ln_trigger = std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_GEMM_TRIGGER")) gemm_trigger = std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_ATTN_TRIGGER")) attn_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_WHOLE")) attn_whole = std::atoi(v) != 0;
     fuse_ln = int8 && shape.hidden <= 768;
     if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) { fuse_ln_rows = std::min(32, std::atoi(v)); fuse_ln = fuse_ln && fuse_ln_rows > 0; }
@@ -240,10 +241,7 @@ struct ti_llm_model {
     // One kernel family for every batch size: logits of a request are bit-identical whatever it is
     // batched with, the property the reference's gates rely on (llm/gpu_correctness.py:62-66).
     c.uniform_numerics = true;
-    // Residual streams are written at least two kernels before the GEMM that adds them, biases at load.
-    c.early_epilogue = early_epilogue;
-    c.early_trigger = kv != nullptr && attn_early && early_trigger;   // decode attention prefetches its history meanwhile
-    tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
+    tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl; o.early_trigger = gemm_trigger;
     ck(tib::gemm(c, o));
   }
 
@@ -269,15 +267,15 @@ struct ti_llm_model {
       const bool fused = fuse_ln && m.rows <= fuse_ln_rows;
       if (fused) gemm(x, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos, b.ln1_g, b.ln1_b);
       else {
-        ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, m.rows, H, 1e-5f, o));
+        ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, m.rows, H, 1e-5f, ln_opts()));
         gemm(norm, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos);   // Q -> qkv buffer, K/V -> their pages
       }
-      if (m.max_q == 1) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o, attn_early, attn_whole));
+      if (m.max_q == 1) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o, attn_early, attn_whole, attn_trigger));
       else ck(tib::attention_paged(qkv, attn, m.row_start, m.qlens, m.kvlens, m.offsets, m.batch, m.max_q, m.max_kv, kv, o));
       gemm(attn, b.proj, res, m.rows, false, x, false);             // res = x + proj(attn)
       if (fused) gemm(res, b.fc, act, m.rows, false, nullptr, true, nullptr, nullptr, nullptr, b.ln2_g, b.ln2_b);
       else {
-        ck(tib::layernorm(res, nullptr, b.ln2_g, b.ln2_b, norm, m.rows, H, 1e-5f, o));
+        ck(tib::layernorm(res, nullptr, b.ln2_g, b.ln2_b, norm, m.rows, H, 1e-5f, ln_opts()));
         gemm(norm, b.fc, act, m.rows, false, nullptr, true);        // act = gelu(fc(norm))
       }
       gemm(act, b.proj2, x, m.rows, false, res, false);             // x = res + proj2(act)
@@ -353,7 +351,12 @@ struct ti_llm_model {
   uint8_t* d_argmax = nullptr;      // per-row merge words of the argmax kernel (zero between launches)
   int32_t *d_seg = nullptr, *h_seg = nullptr, *d_step = nullptr, *d_log = nullptr, *h_log = nullptr;
   bool use_graph = true, use_pdl = true;
-  bool early_epilogue = false, early_trigger = false;
+  // Early release of the next launch (see LaunchOpts::early_trigger).  After a GEMM comes a kernel whose reads ahead
+  // of its own wait are constants or state of earlier steps (LayerNorm parameters, weights, the cache history), so it
+  // may start at once; measured: a few microseconds per step at small batches.  After a LayerNorm it did not pay.
+  bool ln_trigger = false, gemm_trigger = true;
+  tib::LaunchOpts ln_opts() const { tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl; o.early_trigger = ln_trigger; return o; }
+  bool attn_trigger = true;                      // the projection GEMM after attention prefetches its weights meanwhile
   bool attn_early = true, attn_whole = true;     // decode attention: reads ahead of the dependency wait; one CTA per (request, head)
   int fuse_ln_rows = 8;             // largest row count whose LayerNorms run inside the consuming GEMM
   bool fuse_ln = false;             // int8 weights and rows of at most 768 values: LayerNorm runs inside the consuming GEMM
@@ -368,7 +371,7 @@ struct ti_llm_model {
     tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
     if (fuse_ln && batch <= fuse_ln_rows) gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b);
     else {
-      ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, last, batch, shape.hidden, 1e-5f, o));
+      ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, last, batch, shape.hidden, 1e-5f, ln_opts()));
       gemm(last, head, logits, batch, true, nullptr, false);
     }
     ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_log, seg(0), d_step, d_argmax, o));
