@@ -190,11 +190,12 @@ def kernel_rooflines(cached, peak):
     y = torch.empty_like(q)
     kv = [(torch.randn((BATCH, 12, kmax, 64), device="cuda", dtype=torch.float16), torch.randn((BATCH, 12, kmax, 64), device="cuda", dtype=torch.float16))
           for _ in range(layers)]
-    floats = lib.ti_b200_attention_decode_scratch_floats(BATCH, 12, kmax, 128)
+    chunk = (kmax + 31) // 32 * 32          # one CTA per (request, head), as the model runtime launches it
+    floats = lib.ti_b200_attention_decode_scratch_floats(BATCH, 12, kmax, chunk)
     scratch = torch.empty(floats, dtype=torch.float32, device="cuda")
     def attn():
         for k, v in kv:
-            check(lib.ti_b200_attention_decode_f16(q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), lengths.data_ptr(), BATCH, 12, kmax, 64, 128,
+            check(lib.ti_b200_attention_decode_f16(q.data_ptr(), k.data_ptr(), v.data_ptr(), y.data_ptr(), lengths.data_ptr(), BATCH, 12, kmax, 64, chunk,
                                                    scratch.data_ptr(), floats, stream(), dev))
     seconds = graph_seconds(attn, layers)
     nbytes = int(lengths.sum().item()) * 12 * 64 * 2 * 2 + BATCH * 12 * 64 * 2 * 2

@@ -26,7 +26,8 @@ int ti_b200_gemm_i8_fused(const uint16_t* a, const int8_t* b, const float* scale
  * q[B,H,1,64] -> y[B,H,1,64], keys 0..kv_lengths[b]-1 visible.  Equals reference
  * ti_v2_attention_f16 (backend/runtime_v2.cu:82-90) with q_len 1 and
  * query_offsets = kv_lengths-1.  Each (request, head) history is cut into chunks of `chunk`
- * keys (multiple of 32) processed by separate CTAs; their partial results live in `scratch`,
+ * keys (multiple of 32) processed by separate CTAs (a chunk that covers kv_len: one CTA of eight
+ * warps walks the whole history and no partial results leave the chip); partial results live in `scratch`,
  * device memory of at least ti_b200_attention_decode_scratch_floats(...) floats, 16-byte
  * aligned, owned by the caller and private to this call until it completes. */
 int64_t ti_b200_attention_decode_scratch_floats(int batch, int heads, int kv_len, int chunk);

@@ -133,7 +133,9 @@ def test_attention_gate_cases(ops, ref, d, config, nq, nk, ql, kl, off, causal):
 
 
 @pytest.mark.parametrize("batch,heads,nk,lengths,chunk", [(2, 2, 31, [31, 19], 32), (3, 12, 700, [700, 1, 333], 128),
-                                                          (4, 12, 1024, [1024, 513, 512, 129], 128), (2, 3, 96, [0, 96], 64)])
+                                                          (4, 12, 1024, [1024, 513, 512, 129], 128), (2, 3, 96, [0, 96], 64),
+                                                          # chunk >= history: one 8-warp CTA per (request, head)
+                                                          (4, 12, 1024, [1024, 257, 256, 1], 1024), (3, 12, 700, [700, 0, 333], 704)])
 def test_decode_attention_in_place_equals_general_attention(ops, ref, batch, heads, nk, lengths, chunk):
     torch.manual_seed(nk)
     q = (torch.randn((batch, heads, 1, 64), device="cuda") * 0.5).half()

@@ -37,6 +37,7 @@ struct KvPacked {
   // each other at stride d from tile_offset(ref, b, h).
   __device__ __forceinline__ int tile_ref(int, int t0) const { return t0; }
   __device__ __forceinline__ size_t tile_offset(int ref, int b, int h) const { return offset(b, h, ref); }
+  __device__ __forceinline__ int tile_keys(int t0) const { return min(kPageTokens, kv_len - t0); }   // keys that exist in memory
 };
 struct KvPaged {
   const __half* k; const __half* v;       // page pools
@@ -51,6 +52,7 @@ struct KvPaged {
   __device__ __forceinline__ size_t tile_offset(int ref, int, int h) const {
     return ((size_t(ref) * layers + layer) * heads + h) * kPageTokens * d;
   }
+  __device__ __forceinline__ int tile_keys(int) const { return kPageTokens; }
 };
 
 struct AttnArgs {
@@ -332,6 +334,162 @@ attn_decode_kernel(const DecodeArgs p, const KV kv) {
       }
       p.out[b * p.o_sb + h * p.o_sh + tid] = f2h(ll > 0.f ? aa / ll : 0.f);
     }
+  }
+}
+
+// ------------------------------------------------------------------ decode kernel, whole history per CTA
+// grid = (heads, batch), block = 256 (8 warps), dynamic shared memory = 8 warps x (K tile + V tile) = 64 KB for D = 64,
+// so three CTAs share an SM and a 32-request x 12-head step is resident at once.  Warp w owns tiles w, w+8, ...
+// of 32 keys; a tile is contiguous in memory (a cache page, or 32 rows of a packed tensor) and arrives by two
+// bulk asynchronous copies that one lane issues and the warp awaits on its own mbarrier -- the data in flight
+// lives in shared memory, not in registers.  With `early` the first tile, the length and the page numbers are
+// requested ahead of the dependency wait; the newest key, which the kernel before this one writes, is then
+// fetched again after the wait and patched into the tile.
+constexpr int kStagedWarps = 8;
+template <int D> constexpr int staged_smem_bytes() { return kStagedWarps * 2 * kPageTokens * D * 2 + 64; }
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+template <int D, typename KV>
+__global__ void __launch_bounds__(kStagedWarps * 32)
+attn_decode_staged_kernel(const DecodeArgs p, const KV kv) {
+  trace_event(kTrAttnDecode, 0);
+  static_assert(D == 64, "head_dim");
+  constexpr int W = kStagedWarps, DP = D / 8, KPS = 32 / DP, STEPS = 32 / KPS, kTileBytes = kPageTokens * D * 2;
+  extern __shared__ __align__(128) uint8_t staged_smem[];
+  __shared__ float s_acc[W][D];
+  __shared__ float s_ml[W][2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int dp = lane % DP, ksub = lane / DP;
+  const int h = blockIdx.x, b = blockIdx.y;
+  __half* k_tile = reinterpret_cast<__half*>(staged_smem + size_t(warp) * 2 * kTileBytes);
+  __half* v_tile = k_tile + kPageTokens * D;
+  uint64_t* bar = reinterpret_cast<uint64_t*>(staged_smem + size_t(W) * 2 * kTileBytes) + warp;
+  if (lane == 0) { mbar_init(bar, 1); mbar_fence_init(); }
+  __syncwarp();
+
+  // lane 0: request tile `t0` (reference `ref`) into this warp's buffers
+  auto request = [&](int ref, int t0) {
+    const uint32_t bytes = uint32_t(kv.tile_keys(t0)) * D * 2;
+    const size_t o = kv.tile_offset(ref, b, h);
+    mbar_expect_tx(bar, 2 * bytes);
+    bulk_load(k_tile, kv.k + o, bytes, bar);
+    bulk_load(v_tile, kv.v + o, bytes, bar);
+  };
+  constexpr int kRefs = 4;
+  int len = 0, refs[kRefs] = {0, 0, 0, 0};
+  const int t_first = warp * 32;
+  bool requested = false;
+  if (p.early) {
+    len = p.kv_lengths[b];
+    if (lane == 0) {
+#pragma unroll
+      for (int r = 0; r < kRefs; ++r) if (t_first + r * W * 32 < len) refs[r] = kv.tile_ref(b, t_first + r * W * 32);
+      if (t_first < len) { request(refs[0], t_first); requested = true; }
+    }
+  }
+  if (p.early_trigger) pdl_launch_dependents();
+  pdl_wait();
+  trace_event(kTrAttnDecode, 1);
+  if (!p.early) len = p.kv_lengths[b];
+
+  const uint4 qraw = *reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + dp * 8);
+  const __half2* q2 = reinterpret_cast<const __half2*>(&qraw);
+  float m = -CUDART_INF_F, l = 0.f, acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  bool ok = true;
+
+  int it = 0;
+  for (int t0 = t_first; t0 < len; t0 += W * 32, ++it) {
+    if (lane == 0 && ok && !(it == 0 && requested)) {
+      const int ref = (p.early && it < kRefs) ? (it == 0 ? refs[0] : it == 1 ? refs[1] : it == 2 ? refs[2] : refs[3]) : kv.tile_ref(b, t0);
+      request(ref, t0);
+    }
+    if (ok) ok = mbar_wait(bar, uint32_t(it) & 1u, kStatusTmaTimeout);
+    if (p.early && it == 0 && len - 1 >= t0 && len - 1 < t0 + 32) {
+      // the newest key was (re)written by the kernel ahead of this one: fetch it again, now that it is complete
+      const int j = len - 1 - t0;
+      if (lane < 2 * DP) {
+        const int ref = __shfl_sync((1u << (2 * DP)) - 1u, refs[0], 0);
+        const size_t o = kv.tile_offset(ref, b, h) + size_t(j) * D + (lane % DP) * 8;
+        const uint4 fresh = *reinterpret_cast<const uint4*>((lane < DP ? kv.k : kv.v) + o);
+        *reinterpret_cast<uint4*>((lane < DP ? k_tile : v_tile) + j * D + (lane % DP) * 8) = fresh;
+      }
+      __syncwarp();
+    }
+    float sc[STEPS], tile_max = -CUDART_INF_F;
+#pragma unroll
+    for (int i = 0; i < STEPS; ++i) {
+      const int j = i * KPS + ksub, key = t0 + j;
+      const uint4 kraw = *reinterpret_cast<const uint4*>(k_tile + j * D + dp * 8);
+      const __half2* k2 = reinterpret_cast<const __half2*>(&kraw);
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        d = fma_f16(d, __low2half(q2[e]), __low2half(k2[e]));
+        d = fma_f16(d, __high2half(q2[e]), __high2half(k2[e]));
+      }
+#pragma unroll
+      for (int x = 1; x < DP; x <<= 1) d += __shfl_xor_sync(0xffffffffu, d, x);
+      sc[i] = (key < len && ok) ? d * rsqrtf(float(D)) : -CUDART_INF_F;
+      tile_max = fmaxf(tile_max, sc[i]);
+    }
+#pragma unroll
+    for (int x = DP; x < 32; x <<= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, x));
+    if (tile_max > -CUDART_INF_F) {                      // warp-uniform; false only after a failed copy
+      const float next = fmaxf(m, tile_max);
+      const float alpha = expf(m - next);
+      l *= alpha;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= alpha;
+#pragma unroll
+      for (int i = 0; i < STEPS; ++i) {
+        const int j = i * KPS + ksub;
+        if (t0 + j < len) {                               // memory past the history is not ours to interpret
+          const float pr = expf(sc[i] - next);
+          l += pr;
+          const uint4 vraw = *reinterpret_cast<const uint4*>(v_tile + j * D + dp * 8);
+          const __half2* v2 = reinterpret_cast<const __half2*>(&vraw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            acc[2 * e] = fmaf(pr, __low2float(v2[e]), acc[2 * e]);
+            acc[2 * e + 1] = fmaf(pr, __high2float(v2[e]), acc[2 * e + 1]);
+          }
+        }
+      }
+      m = next;
+    }
+    fence_async_smem();                                   // this warp's reads and writes of the tile, before the next copy
+    __syncwarp();                                         // every lane is done with the tile before it is overwritten
+  }
+#pragma unroll
+  for (int x = DP; x < 32; x <<= 1) {
+    l += __shfl_xor_sync(0xffffffffu, l, x);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], x);
+  }
+  if (lane < DP) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) s_acc[warp][dp * 8 + e] = acc[e];
+    if (lane == 0) { s_ml[warp][0] = m; s_ml[warp][1] = l; }
+  }
+  __syncthreads();
+  if (!p.early_trigger) pdl_launch_dependents();
+  if (tid < D) {
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < W; ++w) mm = fmaxf(mm, s_ml[w][0]);
+    float ll = 0.f, aa = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      const float f = s_ml[w][0] > -CUDART_INF_F ? expf(s_ml[w][0] - mm) : 0.f;
+      ll += s_ml[w][1] * f; aa += s_acc[w][tid] * f;
+    }
+    p.out[b * p.o_sb + h * p.o_sh + tid] = f2h(ll > 0.f ? aa / ll : 0.f);
   }
 }
 

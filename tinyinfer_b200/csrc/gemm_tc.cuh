@@ -33,10 +33,13 @@
 namespace tib {
 
 constexpr int kTcDequantThreads = 256;                 // warps 2..9
+#ifndef TIB_SLOT_GRID
+#define TIB_SLOT_GRID (gridDim.x > 300)       // development builds: which launch records pipeline marks
+#endif
 constexpr int kTcThreads = 64 + kTcDequantThreads;
 constexpr int kTcStageK = 64;
 #ifndef TIB_TC_RAW_STAGES
-#define TIB_TC_RAW_STAGES 4
+#define TIB_TC_RAW_STAGES 3
 #endif
 #ifndef TIB_TC_OP_STAGES
 #define TIB_TC_OP_STAGES 3
@@ -54,7 +57,11 @@ template <int NMMA> struct TcSmem {
   static constexpr int kRawOff = 0;                                        // 1024-aligned (TMA swizzle)
   static constexpr int kOpAOff = kRawOff + kTcRawStages * kTcRawBytes;
   static constexpr int kOpBOff = kOpAOff + kTcOpStages * kTcOpABytes;
-  static constexpr int kBarOff = kOpBOff + kTcOpStages * kOpBBytes;
+  // NMMA == 32 (decode): 16 KB where the other CTAs of a K-split cluster deposit their partial sums of the 128 / splits
+  // columns this CTA finishes, [source rank][32 rows][128 / splits] fp32.  It aliases nothing: peers write it while this
+  // CTA may still be in its main loop.
+  static constexpr int kRecvOff = kOpBOff + kTcOpStages * kOpBBytes;
+  static constexpr int kBarOff = kRecvOff + (NMMA == 32 ? 32 * 128 * 4 : 0);
   static constexpr int kBytes = kBarOff + 128 + 1024;                      // barriers + slack for manual 1024 alignment
 };
 
@@ -107,7 +114,7 @@ template <int NMMA>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   trace_event(kTrGemmTc, 0);
-  if (gridDim.x > 300 && threadIdx.x == 0) trace_slot(1);
+  if (TIB_SLOT_GRID && threadIdx.x == 0) trace_slot(1);
   using L = TcSmem<NMMA>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -157,7 +164,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         mbar_expect_tx(&raw_full[slot], kTcRawBytes);
         if (p.w_slab_rows) tma_load_2d(raw + slot * kTcRawBytes, &w_map, 0, int(blockIdx.x) * p.w_slab_rows + k_begin + i * kTcStageK, &raw_full[slot]);
         else tma_load_2d(raw + slot * kTcRawBytes, &w_map, n0, k_begin + i * kTcStageK, &raw_full[slot]);
-        if (gridDim.x > 300) trace_slot(10 + i);
+        if (TIB_SLOT_GRID) trace_slot(10 + i);
       }
       if (!ok) s_failed = 1;
     }
@@ -172,7 +179,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         const int slot = i % kTcOpStages;
         ok = mbar_wait(&op_full[slot], uint32_t(i / kTcOpStages) & 1u, kStatusPipeTimeout);
         if (!ok) break;
-        if (gridDim.x > 300) trace_slot(70 + i);
+        if (TIB_SLOT_GRID) trace_slot(70 + i);
         tc_fence_after();
         const uint32_t a_addr = smem_u32(op_a + slot * kTcOpABytes), b_addr = smem_u32(op_b + slot * L::kOpBBytes);
 #pragma unroll
@@ -273,6 +280,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       if (lane == 0) mbar_arrive(&raw_empty[i]);
     }
     pdl_wait();                                               // A (and the residual) come from the previous kernel
+    if (TIB_SLOT_GRID && t == 0) trace_slot(2);
     if constexpr (NMMA == 32) {
       if (fuse_ln) {
         // Each of the 8 warps owns rows w, w+8, w+16, w+24: all their loads are issued together (one round
@@ -315,6 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         fence_async_smem();                                   // generic-proxy stores -> visible to tcgen05.mma
         __syncwarp();
         if (lane == 0) mbar_arrive(&op_full[i]);
+        if (TIB_SLOT_GRID && t == 0) trace_slot(3 + i);
       }
     } else {
       for (int i = 0; i < lead; ++i) {
@@ -331,7 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       const int rslot = i % kTcRawStages, oslot = i % kTcOpStages;
       if (ok) ok = mbar_wait(&raw_full[rslot], uint32_t(i / kTcRawStages) & 1u, kStatusTmaTimeout);
       if (ok) ok = mbar_wait(&op_empty[oslot], (uint32_t(i / kTcOpStages) & 1u) ^ 1u, kStatusMmaTimeout);
-      if (gridDim.x > 300 && t == 0) trace_slot(30 + i);
+      if (TIB_SLOT_GRID && t == 0) trace_slot(30 + i);
       if (ok) {
         dequantise(rslot, oslot);
         store_a(a_ring[0], oslot, i);
@@ -341,7 +350,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       fetch_a(a_ring[kAhead - 1], i + kAhead);
       __syncwarp();
       if (lane == 0) { mbar_arrive(&raw_empty[rslot]); mbar_arrive(&op_full[oslot]); }
-      if (gridDim.x > 300 && t == 0) trace_slot(50 + i);
+      if (TIB_SLOT_GRID && t == 0) trace_slot(50 + i);
     }
     if (!ok) s_failed = 1;
   }
@@ -351,6 +360,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
 
   // ---------------------------------------------------------------- epilogue (warps 2..5 own TMEM lanes 32*(warp%4)..)
   float* part = reinterpret_cast<float*>(smem);                // [NMMA][128] fp32, aliases the drained pipeline stages
+  float* recv = reinterpret_cast<float*>(smem + L::kRecvOff);  // NMMA == 32 only
+  constexpr bool kPush = NMMA == 32;
   __shared__ long long s_row_base[NMMA];                       // K/V pool offset of each row of the tile (QKV projection only)
   bool acc_ok = true;
   // fp32 output without a K split: staged through shared memory and written as whole 512-byte row pieces
@@ -361,7 +372,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps only
     }
     acc_ok = stages == 0 || mbar_wait(acc_ready, 0, kStatusMmaTimeout);
-    if (gridDim.x > 300 && tid == 64) trace_slot(90);
+    if (TIB_SLOT_GRID && tid == 64) trace_slot(90);
     tc_fence_after();
     const int lane_base = 32 * (warp & 3), n_local = lane_base + lane;
     const int col = n0 + n_local;
@@ -373,8 +384,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.f;
       }
-      if (gridDim.x > 300 && tid == 64) trace_slot(91);
-      if (splits > 1) {
+      if (TIB_SLOT_GRID && tid == 64) trace_slot(91);
+      if (splits > 1 && kPush) {
+        // push: row i of channel n_local goes to the CTA that finishes that column, into the slice reserved for this rank
+        const int cpr = 128 / splits, owner = n_local / cpr;
+        float* dst = cluster.map_shared_rank(recv, owner) + (rank * 32) * cpr + (n_local - owner * cpr);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) dst[i * cpr] = v[i];
+      } else if (splits > 1) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) part[(c0 + i) * 128 + n_local] = v[i];
       } else if (wide_rows) {
@@ -407,10 +424,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         }
       }
     }
-    if (gridDim.x > 300 && tid == 64) trace_slot(92);
+    if (TIB_SLOT_GRID && tid == 64) trace_slot(92);
     tc_fence_before();
   }
-  if (splits > 1) {
+  if (splits > 1 && kPush) {
+    // Every thread knows which (at most two) elements it finishes; their bias and residual are requested now and
+    // arrive while the cluster barrier is pending.
+    const int cpr = 128 / splits, total = 32 * cpr;
+    __half pre_bias[2], pre_res[2];
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int i = tid + s * kTcThreads;
+      pre_bias[s] = pre_res[s] = f2h(0.f);
+      if (i < total) {
+        const int m = i / cpr, row = m0 + m, col = n0 + rank * cpr + (i - m * cpr);
+        if (row < p.m && col < p.n) {
+          if (p.bias) pre_bias[s] = p.bias[col];
+          if (p.residual && !p.out_fp32 && !(p.k_pool && col >= p.kv_hidden)) pre_res[s] = p.residual[size_t(row) * p.ldo + col];
+        }
+      }
+    }
+    cluster.sync();                                           // all partials have landed in their owners' memory
+    if (TIB_SLOT_GRID && tid == 64) trace_slot(93);
+    const bool good = !s_failed;
+    for (int i = tid, s = 0; i < total; i += kTcThreads, ++s) {
+      const int m = i / cpr, c = i - m * cpr;
+      float v = 0.f;
+      for (int r = 0; r < splits; ++r) v += recv[(r * 32 + m) * cpr + c];        // rank order: the sum does not depend on timing
+      const int row = m0 + m, col = n0 + rank * cpr + c;
+      if (row < p.m && col < p.n && good) {
+        if (s < 2) v += h2f(s == 0 ? pre_bias[0] : pre_bias[1]);
+        else if (p.bias) v += h2f(p.bias[col]);
+        if (p.k_pool && col >= p.kv_hidden) {
+          const int cc = col - p.kv_hidden, which = cc >= p.kv_hidden, e = which ? cc - p.kv_hidden : cc;
+          (which ? p.v_pool : p.k_pool)[s_row_base[m] + (e >> 6) * 2048 + (e & 63)] = f2h(v);
+        } else if (p.out_fp32) {
+          static_cast<float*>(p.out)[size_t(row) * p.ldo + col] = v;
+        } else {
+          __half hh = f2h(v);
+          if (p.gelu) hh = f2h(gelu_tanh(h2f(hh)));
+          if (p.residual) hh = f2h(h2f(s == 0 ? pre_res[0] : s == 1 ? pre_res[1] : p.residual[size_t(row) * p.ldo + col]) + h2f(hh));
+          static_cast<__half*>(p.out)[size_t(row) * p.ldo + col] = hh;
+        }
+      }
+    }
+    if (TIB_SLOT_GRID && tid == 64) trace_slot(94);
+    __syncthreads();                                          // nobody reads this CTA's memory remotely: no second cluster barrier
+  } else if (splits > 1) {
     cluster.sync();
     const bool good = !s_failed;
     const int cols_per_rank = 128 / splits, total = NMMA * cols_per_rank;
@@ -426,7 +486,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     __syncthreads();
   }
   trace_event(kTrGemmTc, 2);
-  if (gridDim.x > 300 && threadIdx.x == 0) trace_slot(99);
+  if (TIB_SLOT_GRID && threadIdx.x == 0) trace_slot(99);
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 

@@ -262,6 +262,12 @@ cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kl
     // One CTA of 8 warps walks the whole history of a (request, head) and merges in shared memory: no partials in
     // global memory, no second stage, and a grid small enough to be resident at once.
     p.chunk = 1 << 30; p.chunks = 1;
+    static const int staged = env_int("TINYINFER_B200_ATTN_STAGED", 1);          // measurement aid: 0 = register-resident variant
+    if (staged) {
+      const cudaError_t ready = allow_smem(attn_decode_staged_kernel<64, KvPaged>, staged_smem_bytes<64>());
+      if (ready != cudaSuccess) return ready;
+      return launch(attn_decode_staged_kernel<64, KvPaged>, dim3(kv.heads, batch), dim3(kStagedWarps * 32), staged_smem_bytes<64>(), o, 1, p, paged(kv));
+    }
     return launch(attn_decode_kernel<64, KvPaged, kDecodeWarpsWhole>, dim3(1, kv.heads, batch), dim3(kDecodeWarpsWhole * 32), 0, o, 1, p, paged(kv));
   }
   p.chunk = chunk; p.chunks = decode_chunks(max_kv, chunk);
@@ -279,6 +285,12 @@ cudaError_t attention_packed_decode(const void* q, const void* k, const void* v,
   p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml;
   p.batch = batch; p.heads = heads; p.chunk = chunk; p.chunks = decode_chunks(kv_len, chunk);
   KvPacked kv{static_cast<const __half*>(k), static_cast<const __half*>(v), heads, kv_len, 64};
+  // A chunk that spans the whole history: one CTA of 8 warps per (request, head), merged in shared memory.
+  if (p.chunks == 1 && kv_len > kDecodeWarps * 32) {
+    const cudaError_t ready = allow_smem(attn_decode_staged_kernel<64, KvPacked>, staged_smem_bytes<64>());
+    if (ready != cudaSuccess) return ready;
+    return launch(attn_decode_staged_kernel<64, KvPacked>, dim3(heads, batch), dim3(kStagedWarps * 32), staged_smem_bytes<64>(), o, 1, p, kv);
+  }
   cudaError_t st = launch(attn_decode_kernel<64, KvPacked>, dim3(p.chunks, heads, batch), dim3(kDecodeWarps * 32), 0, o, 1, p, kv);
   if (st != cudaSuccess || p.chunks == 1) return st;
   return launch(attn_combine_kernel<64>, dim3(heads, batch), dim3(64), 0, o, 1, p);
