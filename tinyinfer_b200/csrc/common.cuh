@@ -79,10 +79,38 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, uint32_t parity) {
       : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return done != 0;
 }
+// Cluster-scope forms: an address of this CTA's shared memory as seen in CTA `rank` of the cluster, a store
+// and an arrive (release) through such an address, and a wait that acquires what remote arrivers released.
+__device__ __forceinline__ uint32_t cluster_addr(const void* local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return done != 0;
+}
 // Bounded wait; false (and a recorded status) if the phase never completes.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int code) {
   for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
     if (mbar_try(bar, parity)) return true;
+  report(code);
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, unsigned int code) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin)
+    if (mbar_try_cluster(bar, parity)) return true;
   report(code);
   return false;
 }

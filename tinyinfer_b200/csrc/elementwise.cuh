@@ -39,6 +39,7 @@ __device__ __forceinline__ void row_stats(const T* x, int cols, float eps, float
   float v[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) v[j] = 0.f;
+#pragma unroll 1
   for (int base = lane; base < cols; base += 256) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) { const int c = base + 32 * j; if (c < cols) v[j] += row_value(x, c); }
@@ -46,6 +47,7 @@ __device__ __forceinline__ void row_stats(const T* x, int cols, float eps, float
   mean = tree256(v) / cols;
 #pragma unroll
   for (int j = 0; j < 8; ++j) v[j] = 0.f;
+#pragma unroll 1
   for (int base = lane; base < cols; base += 256) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) { const int c = base + 32 * j; if (c < cols) { const float z = row_value(x, c) - mean; v[j] += z * z; } }
@@ -57,6 +59,7 @@ __device__ __forceinline__ void row_stats(const T* x, int cols, float eps, float
 __device__ __forceinline__ void stage_row(const __half* x, float* dst, int cols) {
   const int lane = threadIdx.x & 31;
   if ((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (cols & 7) == 0) {
+#pragma unroll 1
     for (int c = lane * 8; c < cols; c += 256) {
       const uint4 raw = *reinterpret_cast<const uint4*>(x + c);
       const __half* h = reinterpret_cast<const __half*>(&raw);
@@ -64,7 +67,7 @@ __device__ __forceinline__ void stage_row(const __half* x, float* dst, int cols)
       for (int e = 0; e < 8; ++e) dst[c + e] = h2f(h[e]);
     }
   } else {
-#pragma unroll 4
+#pragma unroll 1
     for (int c = lane; c < cols; c += 32) dst[c] = h2f(x[c]);
   }
   __syncwarp();
@@ -86,6 +89,7 @@ layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, con
   __half* gs = reinterpret_cast<__half*>(ln_rows + size_t(4) * cols);
   __half* bs = gs + cols;
   if (staged) {
+#pragma unroll 1
     for (int c = threadIdx.x; c < cols; c += 128) { gs[c] = g[c]; bs[c] = b[c]; }
     __syncthreads();
   }
@@ -101,6 +105,7 @@ layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, con
     row_stats(xs, cols, eps, mean, inv);
     pdl_launch_dependents();
     if ((reinterpret_cast<uintptr_t>(yr) & 15) == 0 && (cols & 7) == 0) {
+#pragma unroll 1
       for (int c = lane * 8; c < cols; c += 256) {
         uint4 packed;
         __half* h = reinterpret_cast<__half*>(&packed);
@@ -109,22 +114,30 @@ layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, con
         *reinterpret_cast<uint4*>(yr + c) = packed;
       }
     } else {
+#pragma unroll 1
       for (int c = lane; c < cols; c += 32) yr[c] = f2h((xs[c] - mean) * inv * h2f(gs[c]) + h2f(bs[c]));
     }
   } else {
     // very wide rows: same arithmetic straight from global memory
     float v[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { float s = 0.f; for (int c = lane + 32 * j; c < cols; c += 256) s += h2f(xr[c]); v[j] = s; }
+    for (int j = 0; j < 8; ++j) {
+      float s = 0.f;
+#pragma unroll 1
+      for (int c = lane + 32 * j; c < cols; c += 256) s += h2f(xr[c]);
+      v[j] = s;
+    }
     mean = tree256(v) / cols;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float s = 0.f;
+#pragma unroll 1
       for (int c = lane + 32 * j; c < cols; c += 256) { const float z = h2f(xr[c]) - mean; s += z * z; }
       v[j] = s;
     }
     inv = rsqrtf(tree256(v) / cols + eps);
     pdl_launch_dependents();
+#pragma unroll 1
     for (int c = lane; c < cols; c += 32) yr[c] = f2h((h2f(xr[c]) - mean) * inv * h2f(g[c]) + h2f(b[c]));
   }
 }

@@ -119,8 +119,10 @@ __device__ __forceinline__ void gemv_consume_stage(const uint8_t* stage, const _
 }
 
 // row_base: kv_row_base(p, row) when the caller has it at hand, else -1 (looked up here).
-__device__ __forceinline__ void gemv_store(const GemvArgs& p, int row, int col, float acc, long long row_base = -1) {
-  const float v = acc + (p.bias ? h2f(p.bias[col]) : 0.f);
+// fetched: the element's bias and residual were read ahead of time (raw halves) and are passed in.
+__device__ __forceinline__ void gemv_store(const GemvArgs& p, int row, int col, float acc, long long row_base = -1,
+                                           bool fetched = false, __half bias = __half(), __half residual = __half()) {
+  const float v = acc + (fetched ? h2f(bias) : (p.bias ? h2f(p.bias[col]) : 0.f));
   if (p.k_pool && col >= p.kv_hidden) {
     const int c = col - p.kv_hidden, which = c >= p.kv_hidden, e = which ? c - p.kv_hidden : c;
     if (row_base < 0) row_base = kv_row_base(p, row);
@@ -130,7 +132,7 @@ __device__ __forceinline__ void gemv_store(const GemvArgs& p, int row, int col, 
   if (p.out_fp32) { static_cast<float*>(p.out)[size_t(row) * p.ldo + col] = v; return; }
   __half h = f2h(v);
   if (p.gelu) h = f2h(gelu_tanh(h2f(h)));
-  if (p.residual) h = f2h(h2f(p.residual[size_t(row) * p.ldo + col]) + h2f(h));
+  if (p.residual) h = f2h(h2f(fetched ? residual : p.residual[size_t(row) * p.ldo + col]) + h2f(h));
   static_cast<__half*>(p.out)[size_t(row) * p.ldo + col] = h;
 }
 

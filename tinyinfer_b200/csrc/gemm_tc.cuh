@@ -110,7 +110,9 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
 }
 
 // grid = (N / 128 slabs, k splits [cluster y], M / NMMA tiles), block = 192.
-template <int NMMA>
+// LN: LayerNorm prologue compiled in (0 = none, 1 = every CTA prepares the rows itself, 2 = rows shared out over the
+// K-split cluster); separate instantiations keep the plain GEMM free of that code.
+template <int NMMA, int LN = 0>
 __global__ void __launch_bounds__(kTcThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   trace_event(kTrGemmTc, 0);
@@ -123,9 +125,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   uint8_t* op_b = smem + L::kOpBOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t *raw_full = bars, *raw_empty = raw_full + kTcRawStages, *op_full = raw_empty + kTcRawStages, *op_empty = op_full + kTcOpStages,
-           *acc_ready = op_empty + kTcOpStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
-  static_assert((2 * kTcRawStages + 2 * kTcOpStages + 2) * 8 <= 128, "barrier block");
+           *acc_ready = op_empty + kTcOpStages, *ln_bar = acc_ready + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ln_bar + 1);
+  static_assert((2 * kTcRawStages + 2 * kTcOpStages + 3) * 8 <= 128, "barrier block");
   static_assert(NMMA != 32 || kTcOpStages * L::kOpBBytes >= 8 * 768 * 2, "LayerNorm row strips live in the B-operand ring");
   __shared__ int s_failed;
 
@@ -144,11 +146,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     for (int s = 0; s < kTcRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kTcDequantThreads / 32); }
     for (int s = 0; s < kTcOpStages; ++s) { mbar_init(&op_full[s], kTcDequantThreads / 32); mbar_init(&op_empty[s], 1); }
     mbar_init(acc_ready, 1);
+    mbar_init(ln_bar, 32);                                    // one arrival per row of the tile (LayerNorm prologue)
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
-  __syncthreads();
+  // LayerNorm prologue of more than 8 rows: the rows are shared out over the K-split cluster and the CTAs signal each
+  // other's barriers, which must exist first.  (Written as PTX: with cooperative_groups' cluster sync in this place
+  // every launch of the kernel, also those that skip it, measured half a microsecond slower.)
+  static_assert(LN <= 0 || NMMA == 32, "LayerNorm prologue: one 32-row tile");
+  const bool fuse_ln = LN < 0 ? (NMMA == 32 && p.ln_gamma != nullptr) : LN != 0;
+  const bool ln_shared = LN < 0 ? (fuse_ln && splits > 1 && p.m > 8) : LN == 2;
+  if (ln_shared) {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  } else {
+    __syncthreads();
+  }
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -239,9 +252,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     };
     // Optional LayerNorm of the rows (decode: NMMA == 32, K <= 768): statistics per row are computed once per CTA
     // right after the dependency resolves, with the same summation order as layernorm_kernel, and applied here.
-    __shared__ __half s_gamma[NMMA == 32 ? 768 : 1], s_beta[NMMA == 32 ? 768 : 1];
+    __shared__ __half s_gamma[LN != 0 && NMMA == 32 ? 768 : 1], s_beta[LN != 0 && NMMA == 32 ? 768 : 1];
     __shared__ float s_mean[32], s_inv[32];
-    const bool fuse_ln = NMMA == 32 && p.ln_gamma != nullptr;
     if (fuse_ln)
       for (int c = k_begin + t; c < k_end; c += kTcDequantThreads) { s_gamma[c - k_begin] = p.ln_gamma[c]; s_beta[c - k_begin] = p.ln_beta[c]; }
     auto store_a = [&](const uint4 (&src)[kPer], int oslot, int i) {
@@ -281,35 +293,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     }
     pdl_wait();                                               // A (and the residual) come from the previous kernel
     if (TIB_SLOT_GRID && t == 0) trace_slot(2);
-    if constexpr (NMMA == 32) {
+    if constexpr (LN != 0 && NMMA == 32) {
       if (fuse_ln) {
-        // Each of the 8 warps owns rows w, w+8, w+16, w+24: all their loads are issued together (one round
-        // trip), then each row passes through a per-warp strip of the still-empty B-operand ring.
+        // Up to 8 rows: every CTA prepares them all itself, one warp per row.  More: the 32 rows of the tile are shared
+        // out over the K-split cluster, rank r prepares rows r*R .. r*R+R-1 (R = 32 / splits), one warp per row
+        // (w, w+8, ... of them), and sends each row's mean and 1/sigma to every CTA of the cluster, followed by an
+        // arrival on that CTA's barrier (32 arrivals complete it).  Each row passes through a per-warp strip of the
+        // still-empty B-operand ring.
         __half* strip = reinterpret_cast<__half*>(op_b) + size_t(warp - 2) * p.k;
-        const int chunks = p.k / 8;
-        uint4 held[4][3];
+        const int chunks = p.k / 8, share = ln_shared ? 32 / splits : 32, first = ln_shared ? rank * share : 0;
+#pragma unroll 1
+        for (int local = warp - 2; local < share; local += 8) {   // one row per warp in the usual cases (<= 8 rows per CTA)
+          float mean = 0.f, inv = 0.f;
+          const int row = m0 + first + local;
+          if (row < p.m) {                                    // warp-uniform
+            uint4 held[3];
 #pragma unroll
-        for (int r = 0; r < 4; ++r)
+            for (int u = 0; u < 3; ++u) {
+              const int c = lane + 32 * u;
+              held[u] = make_uint4(0, 0, 0, 0);
+              if (c < chunks) held[u] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + c * 8);
+            }
 #pragma unroll
-          for (int u = 0; u < 3; ++u) {
-            const int row = m0 + (warp - 2) + 8 * r, c = lane + 32 * u;
-            held[r][u] = make_uint4(0, 0, 0, 0);
-            if (row < p.m && c < chunks) held[r][u] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + c * 8);
-          }
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const int local = (warp - 2) + 8 * r;
-          if (m0 + local < p.m) {                             // warp-uniform
-#pragma unroll
-            for (int u = 0; u < 3; ++u) { const int c = lane + 32 * u; if (c < chunks) *reinterpret_cast<uint4*>(strip + c * 8) = held[r][u]; }
+            for (int u = 0; u < 3; ++u) { const int c = lane + 32 * u; if (c < chunks) *reinterpret_cast<uint4*>(strip + c * 8) = held[u]; }
             __syncwarp();
-            float mean, inv;
             row_stats(strip, p.k, p.ln_eps, mean, inv);
-            if (lane == 0) { s_mean[local] = mean; s_inv[local] = inv; }
             __syncwarp();
-          } else if (lane == 0) { s_mean[local] = 0.f; s_inv[local] = 0.f; }
+          }
+          if (!ln_shared) {
+            if (lane == 0) { s_mean[local] = mean; s_inv[local] = inv; }
+          } else if (lane < splits) {
+            st_cluster_f32(cluster_addr(&s_mean[first + local], lane), mean);
+            st_cluster_f32(cluster_addr(&s_inv[first + local], lane), inv);
+            mbar_arrive_cluster(cluster_addr(ln_bar, lane));
+          }
         }
-        asm volatile("bar.sync 2, 256;" ::: "memory");        // the eight dequantising warps
+        if (!ln_shared) asm volatile("bar.sync 2, 256;" ::: "memory");      // the eight dequantising warps
+        else if (ok) ok = mbar_wait_cluster(ln_bar, 0, kStatusPipeTimeout);  // all 32 rows' statistics are here
       }
     }
     if constexpr (kAhead > 1) {
@@ -358,24 +378,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   trace_event(kTrGemmTc, 1);
   pdl_launch_dependents();
 
-  // ---------------------------------------------------------------- epilogue (warps 2..5 own TMEM lanes 32*(warp%4)..)
+  // ---------------------------------------------------------------- epilogue
+  // Two steps, both written as short rolled loops (a decode GEMM runs for microseconds: the instructions it has to
+  // fetch count as much as the ones it executes).  1. Warps 2..5 (TMEM lanes 32 * (warp % 4) ..) move the accumulators
+  // out: into the shared memory of the CTA that finishes the column (K split, one 32-row tile: "push"), else into this
+  // CTA's own.  2. After a barrier every thread finishes elements (row, column) of the columns this CTA owns: sum over
+  // the K ranks in rank order, bias, activation, residual, store -- one copy of that code.
   float* part = reinterpret_cast<float*>(smem);                // [NMMA][128] fp32, aliases the drained pipeline stages
-  float* recv = reinterpret_cast<float*>(smem + L::kRecvOff);  // NMMA == 32 only
+  float* recv = reinterpret_cast<float*>(smem + L::kRecvOff);  // NMMA == 32 only: [rank][32][128 / splits]
   constexpr bool kPush = NMMA == 32;
+  const bool push = kPush && splits > 1;
   __shared__ long long s_row_base[NMMA];                       // K/V pool offset of each row of the tile (QKV projection only)
   bool acc_ok = true;
-  // fp32 output without a K split: staged through shared memory and written as whole 512-byte row pieces
-  const bool wide_rows = splits == 1 && p.out_fp32 && !p.k_pool && p.ldo % 4 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0;
+  const int cpr = 128 / splits;                                // columns this CTA finishes: [rank * cpr, rank * cpr + cpr)
   if (warp >= 2 && warp < 6) {
-    if (p.k_pool) {
+    if (p.k_pool)
       for (int i = tid - 64; i < NMMA; i += 128) s_row_base[i] = m0 + i < p.m ? kv_row_base(p, m0 + i) : 0;
-      asm volatile("bar.sync 1, 128;" ::: "memory");            // the four epilogue warps only
-    }
     acc_ok = stages == 0 || mbar_wait(acc_ready, 0, kStatusMmaTimeout);
     if (TIB_SLOT_GRID && tid == 64) trace_slot(90);
     tc_fence_after();
     const int lane_base = 32 * (warp & 3), n_local = lane_base + lane;
-    const int col = n0 + n_local;
+    const int owner = n_local / cpr;
+    float* dst = push ? cluster.map_shared_rank(recv, owner) + (rank * 32) * cpr + (n_local - owner * cpr) : part + n_local;
+    const int pitch = push ? cpr : 128;
 #pragma unroll 1
     for (int c0 = 0; c0 < NMMA; c0 += 32) {
       float v[32];
@@ -385,106 +410,69 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         for (int i = 0; i < 32; ++i) v[i] = 0.f;
       }
       if (TIB_SLOT_GRID && tid == 64) trace_slot(91);
-      if (splits > 1 && kPush) {
-        // push: row i of channel n_local goes to the CTA that finishes that column, into the slice reserved for this rank
-        const int cpr = 128 / splits, owner = n_local / cpr;
-        float* dst = cluster.map_shared_rank(recv, owner) + (rank * 32) * cpr + (n_local - owner * cpr);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) dst[i * cpr] = v[i];
-      } else if (splits > 1) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) part[(c0 + i) * 128 + n_local] = v[i];
-      } else if (wide_rows) {
-        const float b = p.bias && col < p.n ? h2f(p.bias[col]) : 0.f;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) part[(c0 + i) * 128 + n_local] = v[i] + b;
-      } else if (acc_ok && col < p.n) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) { const int row = m0 + c0 + i; if (row < p.m) gemv_store(p, row, col, v[i], p.k_pool ? s_row_base[c0 + i] : -1); }
-      }
-    }
-    if (wide_rows) {
-      // fp32 rows leave as 512-byte runs (one float4 per lane) instead of 32 separate 128-byte pieces per warp
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (acc_ok) {
-        for (int r = warp - 2; r < NMMA; r += 4) {
-          const int row = m0 + r, c = n0 + lane * 4;
-          if (row >= p.m) break;
-          const float4 f = *reinterpret_cast<const float4*>(part + r * 128 + lane * 4);
-          float* dst = static_cast<float*>(p.out) + size_t(row) * p.ldo + c;
-#ifdef TIB_EXP_NO_STORE
-          if (f.x != 12345.678f) continue;
-#endif
-          if (c + 3 < p.n) *reinterpret_cast<float4*>(dst) = f;
-          else {
-            if (c < p.n) dst[0] = f.x;
-            if (c + 1 < p.n) dst[1] = f.y;
-            if (c + 2 < p.n) dst[2] = f.z;
-          }
-        }
-      }
+      for (int i = 0; i < 32; ++i) dst[(c0 + i) * pitch] = v[i];
     }
     if (TIB_SLOT_GRID && tid == 64) trace_slot(92);
     tc_fence_before();
   }
-  if (splits > 1 && kPush) {
-    // Every thread knows which (at most two) elements it finishes; their bias and residual are requested now and
-    // arrive while the cluster barrier is pending.
-    const int cpr = 128 / splits, total = 32 * cpr;
-    __half pre_bias[2], pre_res[2];
+  // The first two elements a thread will finish are known: their bias and residual are requested now and arrive while
+  // the barrier is pending.  (Both are complete: every thread is past the dependency wait.)
+  const int total = NMMA * cpr;
+  __half pre_bias[2], pre_res[2];
 #pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      const int i = tid + s * kTcThreads;
-      pre_bias[s] = pre_res[s] = f2h(0.f);
-      if (i < total) {
-        const int m = i / cpr, row = m0 + m, col = n0 + rank * cpr + (i - m * cpr);
-        if (row < p.m && col < p.n) {
-          if (p.bias) pre_bias[s] = p.bias[col];
-          if (p.residual && !p.out_fp32 && !(p.k_pool && col >= p.kv_hidden)) pre_res[s] = p.residual[size_t(row) * p.ldo + col];
-        }
+  for (int s = 0; s < 2; ++s) {
+    const int i = tid + s * kTcThreads, m = i / cpr, row = m0 + m, col = n0 + rank * cpr + (i - m * cpr);
+    pre_bias[s] = pre_res[s] = f2h(0.f);
+    if (i < total && row < p.m && col < p.n) {
+      if (p.bias) pre_bias[s] = p.bias[col];
+      if (p.residual && !p.out_fp32 && !(p.k_pool && col >= p.kv_hidden)) pre_res[s] = p.residual[size_t(row) * p.ldo + col];
+    }
+  }
+  if (splits > 1) cluster.sync(); else __syncthreads();         // all partial sums are where they will be read
+  if (TIB_SLOT_GRID && tid == 64) trace_slot(93);
+  const bool good = !s_failed;
+  const bool wide_rows = splits == 1 && p.out_fp32 && !p.k_pool && p.ldo % 4 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0;
+  if (wide_rows) {
+    // fp32 rows without a K split (vocabulary projection) leave as float4: 512-byte runs per warp
+    for (int i = tid; i < NMMA * 32; i += kTcThreads) {
+      const int m = i >> 5, c = (i & 31) * 4, row = m0 + m, col = n0 + c;
+      if (row >= p.m || !good) continue;
+      float4 f = *reinterpret_cast<const float4*>(part + m * 128 + c);
+      if (p.bias) {
+        if (col < p.n) f.x += h2f(p.bias[col]);
+        if (col + 1 < p.n) f.y += h2f(p.bias[col + 1]);
+        if (col + 2 < p.n) f.z += h2f(p.bias[col + 2]);
+        if (col + 3 < p.n) f.w += h2f(p.bias[col + 3]);
+      }
+      float* out = static_cast<float*>(p.out) + size_t(row) * p.ldo + col;
+      if (col + 3 < p.n) *reinterpret_cast<float4*>(out) = f;
+      else {
+        if (col < p.n) out[0] = f.x;
+        if (col + 1 < p.n) out[1] = f.y;
+        if (col + 2 < p.n) out[2] = f.z;
       }
     }
-    cluster.sync();                                           // all partials have landed in their owners' memory
-    if (TIB_SLOT_GRID && tid == 64) trace_slot(93);
-    const bool good = !s_failed;
+  } else {
+#pragma unroll 1
     for (int i = tid, s = 0; i < total; i += kTcThreads, ++s) {
       const int m = i / cpr, c = i - m * cpr;
       float v = 0.f;
-      for (int r = 0; r < splits; ++r) v += recv[(r * 32 + m) * cpr + c];        // rank order: the sum does not depend on timing
-      const int row = m0 + m, col = n0 + rank * cpr + c;
-      if (row < p.m && col < p.n && good) {
-        if (s < 2) v += h2f(s == 0 ? pre_bias[0] : pre_bias[1]);
-        else if (p.bias) v += h2f(p.bias[col]);
-        if (p.k_pool && col >= p.kv_hidden) {
-          const int cc = col - p.kv_hidden, which = cc >= p.kv_hidden, e = which ? cc - p.kv_hidden : cc;
-          (which ? p.v_pool : p.k_pool)[s_row_base[m] + (e >> 6) * 2048 + (e & 63)] = f2h(v);
-        } else if (p.out_fp32) {
-          static_cast<float*>(p.out)[size_t(row) * p.ldo + col] = v;
-        } else {
-          __half hh = f2h(v);
-          if (p.gelu) hh = f2h(gelu_tanh(h2f(hh)));
-          if (p.residual) hh = f2h(h2f(s == 0 ? pre_res[0] : s == 1 ? pre_res[1] : p.residual[size_t(row) * p.ldo + col]) + h2f(hh));
-          static_cast<__half*>(p.out)[size_t(row) * p.ldo + col] = hh;
-        }
+      if (push) {
+        for (int r = 0; r < splits; ++r) v += recv[(r * 32 + m) * cpr + c];
+      } else if (splits > 1) {
+        for (int r = 0; r < splits; ++r) v += cluster.map_shared_rank(part, r)[m * 128 + rank * cpr + c];
+      } else {
+        v = part[m * 128 + c];
       }
+      const int row = m0 + m, col = n0 + rank * cpr + c;
+      if (row < p.m && col < p.n && good)
+        gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1, s < 2, s == 0 ? pre_bias[0] : pre_bias[1], s == 0 ? pre_res[0] : pre_res[1]);
     }
-    if (TIB_SLOT_GRID && tid == 64) trace_slot(94);
-    __syncthreads();                                          // nobody reads this CTA's memory remotely: no second cluster barrier
-  } else if (splits > 1) {
-    cluster.sync();
-    const bool good = !s_failed;
-    const int cols_per_rank = 128 / splits, total = NMMA * cols_per_rank;
-    for (int i = tid; i < total; i += kTcThreads) {
-      const int m = i / cols_per_rank, c = rank * cols_per_rank + (i - m * cols_per_rank);
-      float v = 0.f;
-      for (int r = 0; r < splits; ++r) v += cluster.map_shared_rank(part, r)[m * 128 + c];
-      const int row = m0 + m, col = n0 + c;
-      if (row < p.m && col < p.n && good) gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1);
-    }
-    cluster.sync();
-  } else {
-    __syncthreads();
   }
+  if (TIB_SLOT_GRID && tid == 64) trace_slot(94);
+  // Pull mode: peers may still be reading this CTA's partial sums.  Push mode: nobody reads remotely after the barrier.
+  if (splits > 1 && !push) cluster.sync(); else __syncthreads();
   trace_event(kTrGemmTc, 2);
   if (TIB_SLOT_GRID && threadIdx.x == 0) trace_slot(99);
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }

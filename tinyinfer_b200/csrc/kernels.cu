@@ -115,11 +115,11 @@ cudaError_t launch_gemv_mt(int mt, const CUtensorMap& map, const GemvArgs& args,
   }
 }
 
-template <int NMMA>
+template <int NMMA, int LN = 0>
 cudaError_t launch_tc(const CUtensorMap& map, const GemvArgs& args, dim3 grid, const LaunchOpts& o) {
-  const cudaError_t ready = allow_smem(gemm_tc_kernel<NMMA>, TcSmem<NMMA>::kBytes);
+  const cudaError_t ready = allow_smem(gemm_tc_kernel<NMMA, LN>, TcSmem<NMMA>::kBytes);
   if (ready != cudaSuccess) return ready;
-  return launch(gemm_tc_kernel<NMMA>, grid, dim3(kTcThreads), TcSmem<NMMA>::kBytes, o, int(grid.y), map, args);
+  return launch(gemm_tc_kernel<NMMA, LN>, grid, dim3(kTcThreads), TcSmem<NMMA>::kBytes, o, int(grid.y), map, args);
 }
 
 int env_int(const char* name, int fallback) {
@@ -171,7 +171,13 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       a.k_chunk = (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
       const dim3 grid(slabs, splits, m_tiles);
       switch (nmma) {
-        case 32: return launch_tc<32>(map, a, grid, o);
+        case 32:
+#ifdef TIB_LN_RUNTIME
+          return launch_tc<32, -1>(map, a, grid, o);
+#endif
+          if (!c.ln_gamma) return launch_tc<32>(map, a, grid, o);
+          // up to 8 rows every CTA prepares them itself; more are shared out over the K-split cluster
+          return splits > 1 && c.m > 8 ? launch_tc<32, 2>(map, a, grid, o) : launch_tc<32, 1>(map, a, grid, o);
         case 64: return launch_tc<64>(map, a, grid, o);
         case 128: return launch_tc<128>(map, a, grid, o);
         default: return launch_tc<256>(map, a, grid, o);

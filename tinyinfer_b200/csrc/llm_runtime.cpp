@@ -262,8 +262,8 @@ struct ti_llm_model {
     for (int l = 0; l < shape.layers; ++l) {
       const Block& b = blocks[size_t(l)];
       kv.layer = l;
-      // LayerNorm as a prologue of the consuming GEMM while one warp per row suffices (every CTA of that GEMM
-      // repeats the row statistics, so beyond 8 rows the separate kernel is cheaper).
+      // LayerNorm as a prologue of the consuming GEMM for decode-sized passes (one 32-row tile): up to 8 rows every CTA
+      // computes the row statistics itself, beyond that the CTAs of a K-split cluster share the rows out.
       const bool fused = fuse_ln && m.rows <= fuse_ln_rows;
       if (fused) gemm(x, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos, b.ln1_g, b.ln1_b);
       else {
@@ -358,7 +358,7 @@ struct ti_llm_model {
   tib::LaunchOpts ln_opts() const { tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl; o.early_trigger = ln_trigger; return o; }
   bool attn_trigger = true;                      // the projection GEMM after attention prefetches its weights meanwhile
   bool attn_early = true, attn_whole = true;     // decode attention: reads ahead of the dependency wait; one CTA per (request, head)
-  int fuse_ln_rows = 8;             // largest row count whose LayerNorms run inside the consuming GEMM
+  int fuse_ln_rows = 32;            // largest row count whose LayerNorms run inside the consuming GEMM
   bool fuse_ln = false;             // int8 weights and rows of at most 768 values: LayerNorm runs inside the consuming GEMM
 
   int32_t* seg(int field) const { return d_seg + size_t(field) * opt.max_batch; }
@@ -369,7 +369,7 @@ struct ti_llm_model {
     m.rows = batch; m.batch = batch; m.max_q = 1; m.max_kv = max_kv;
     run_layers(m);
     tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
-    if (fuse_ln && batch <= fuse_ln_rows) gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b);
+    if (fuse_ln && batch <= std::min(fuse_ln_rows, 8)) gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b);
     else {
       ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, last, batch, shape.hidden, 1e-5f, ln_opts()));
       gemm(last, head, logits, batch, true, nullptr, false);
