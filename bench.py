@@ -164,8 +164,8 @@ def graph_seconds(enqueue, launches, replays=10):
 
 
 # DRAM traffic over algorithmic bytes of one launch, from the ncu captures summarised under profiles/
-# (attn_decode_kernel_batch32.md, gemm_tc_kernel_decode_batch32.md); None where no capture exists.
-TRAFFIC_RATIO = {"attention_decode": 25.63 / 26.6, "gemm_int8 qkv": 1.91 / 1.77, "gemm_int8 mlp fc": 2.50 / 2.36, "gemm_int8 mlp proj": 2.69 / 2.36}
+# (attn_decode_staged_kernel_batch32.md, gemm_tc_kernel_decode_batch32.md); None where no capture exists.
+TRAFFIC_RATIO = {"attention_decode": 27.12 / 26.6, "gemm_int8 qkv": 1.91 / 1.77, "gemm_int8 attn proj": 0.74 / 0.59, "gemm_int8 mlp fc": 2.50 / 2.36, "gemm_int8 mlp proj": 2.66 / 2.36}
 
 
 def kernel_rooflines(cached, peak):
