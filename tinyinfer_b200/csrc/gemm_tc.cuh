@@ -14,14 +14,18 @@
 //   * D: fp32, NMMA columns of tensor memory, read back with tcgen05.ld by 4 warps.
 //
 // Pipeline of one CTA (320 threads, 2 CTAs per SM at NMMA = 32):
-//   warp 0      TMA producer: int8 tiles 64(k) x 128(n) -> ring of 4 raw stages (128-byte swizzle so the
+//   warp 0      TMA producer: int8 tiles 64(k) x 128(n) -> ring of 3 raw stages (128-byte swizzle so the
 //               dequantisers' 16-byte column reads are bank-conflict free);
 //   warps 2-9   dequantise raw stage -> fp16 operand stage (ring of 3), copy the matching 64 columns of
-//               A next to it, fence.proxy.async, signal;  warps 2-5 later run the epilogue;
+//               A next to it (normalised on the way when the LayerNorm prologue is on), fence.proxy.async,
+//               signal; the first stages are dequantised ahead of the dependency wait;
 //   warp 1      owns the TMEM allocation; one lane issues 4 tcgen05.mma per stage and commits to the
-//               barrier that releases the operand stage; a last commit publishes the accumulator.
-// K can be split over a cluster of up to 8 CTAs; partial tiles are reduced through
-// distributed shared memory in rank order, like the SIMT kernel.  Every wait is bounded.
+//               barrier that releases the operand stage; a last commit publishes the accumulator;
+//   warps 2-5   move the accumulators out of TMEM; then every thread finishes output elements.
+// K can be split over a cluster of up to 8 CTAs.  One 32-row tile: each CTA pushes its partial sums into
+// the shared memory of the CTA that finishes the column (one cluster barrier, local reads); larger tiles:
+// partial tiles stay put and are read through distributed shared memory (two barriers).  Either way the
+// sum runs in rank order.  Every wait is bounded.
 #pragma once
 #include <cooperative_groups.h>
 #include <cuda.h>
@@ -109,7 +113,7 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// grid = (N / 128 slabs, k splits [cluster y], M / NMMA tiles), block = 192.
+// grid = (N / 128 slabs, k splits [cluster y], M / NMMA tiles), block = 320.
 // LN: LayerNorm prologue compiled in (0 = none, 1 = every CTA prepares the rows itself, 2 = rows shared out over the
 // K-split cluster); separate instantiations keep the plain GEMM free of that code.
 template <int NMMA, int LN = 0>
