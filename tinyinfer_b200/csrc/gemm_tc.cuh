@@ -297,6 +297,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     }
     pdl_wait();                                               // A (and the residual) come from the previous kernel
     if (TIB_SLOT_GRID && t == 0) trace_slot(2);
+    // The first stages' rows are requested together (one round trip instead of one per stage).  With the shared
+    // LayerNorm prologue they go out before it (its barrier wait covers their latency); with the local one after
+    // it (measured: ahead of it they delay the row loads the statistics wait for).
+    constexpr bool kFetchFirst = LN == 2 || LN < 0;
+    if constexpr (kAhead > 1 && kFetchFirst) {
+#pragma unroll
+      for (int d = 0; d < kAhead; ++d) fetch_a(a_ring[d], d);
+    }
     if constexpr (LN != 0 && NMMA == 32) {
       if (fuse_ln) {
         // Up to 8 rows: every CTA prepares them all itself, one warp per row.  More: the 32 rows of the tile are shared
@@ -337,9 +345,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       }
     }
     if constexpr (kAhead > 1) {
-      // the first stages' rows are requested together: one round trip instead of one per stage
+      if constexpr (!kFetchFirst) {
 #pragma unroll
-      for (int d = 0; d < kAhead; ++d) fetch_a(a_ring[d], d);
+        for (int d = 0; d < kAhead; ++d) fetch_a(a_ring[d], d);
+      }
       for (int i = 0; i < lead; ++i) {
         store_a(a_ring[0], i, i);
         rotate();
