@@ -48,6 +48,8 @@ struct GemvArgs {
   int m, n, k;
   int k_chunk;                // K rows per CTA, multiple of kGemvStageRows
   int early_trigger;          // release the dependent launch at once: the next kernel has work that does not need this one's output
+  int serial_chunks;          // tensor-core kernel, one CTA over the whole K: the K ranges of a `serial_chunks`-way split get one
+                              // accumulator each and are added in range order (same sums as the split launch); 0 = off
   int w_slab_rows;            // tensor-core kernel: 0 = weights are [K][ldw]; else slab-major [N/128][w_slab_rows][128]
   int out_fp32, gelu;
   // K/V placement (QKV projection of the model runtime; k_pool null elsewhere): columns at or past

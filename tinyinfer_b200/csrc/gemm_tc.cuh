@@ -139,9 +139,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int splits = int(gridDim.y), rank = int(blockIdx.y);
   const int n0 = blockIdx.x * 128, m0 = blockIdx.z * NMMA;
-  const int k_begin = rank * p.k_chunk, k_end = min(p.k, k_begin + p.k_chunk);
+  const bool serial_mode = NMMA >= 64 && p.serial_chunks > 1;   // many-row tiles only: the 32-row kernel carries none of it
+  const int k_begin = serial_mode ? 0 : rank * p.k_chunk, k_end = serial_mode ? p.k : min(p.k, k_begin + p.k_chunk);
   const int stages = k_end > k_begin ? (k_end - k_begin + kTcStageK - 1) / kTcStageK : 0;
-  constexpr uint32_t kTmemCols = NMMA < 32 ? 32 : NMMA;
+  // One accumulator of NMMA columns, or `serial_chunks` of them side by side (power of two, at most 512 columns).
+  const int serial = serial_mode ? p.serial_chunks : 1;
+  const uint32_t tmem_cols = uint32_t(max(32, NMMA * serial));
 
   if (p.early_trigger) pdl_launch_dependents();
   if (tid == 0) {
@@ -153,7 +156,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     mbar_init(ln_bar, 32);                                    // one arrival per row of the tile (LayerNorm prologue)
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
   tc_fence_before();
   // LayerNorm prologue of more than 8 rows: the rows are shared out over the K-split cluster and the CTAs signal each
   // other's barriers, which must exist first.  (Written as PTX: with cooperative_groups' cluster sync in this place
@@ -199,11 +202,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         if (TIB_SLOT_GRID) trace_slot(70 + i);
         tc_fence_after();
         const uint32_t a_addr = smem_u32(op_a + slot * kTcOpABytes), b_addr = smem_u32(op_b + slot * L::kOpBBytes);
+        // serial mode: K range number (i * 64) / k_chunk has its own accumulator, started afresh at the range's first stage
+        const int k_off = i * kTcStageK, chunk_id = (NMMA >= 64 && serial > 1) ? k_off / p.k_chunk : 0;
+        const bool fresh = (NMMA >= 64 && serial > 1) ? k_off == chunk_id * p.k_chunk : i == 0;
+        const uint32_t acc_col = uint32_t(chunk_id * NMMA);
 #pragma unroll
         for (int kk = 0; kk < kTcStageK / 16; ++kk) {
           const uint64_t da = tc_desc(a_addr + kk * 2 * 2048, a_lbo, a_sbo);
           const uint64_t db = tc_desc(b_addr + kk * 2 * (NMMA / 8) * 128, (NMMA / 8) * 128, 128);
-          tc_mma_f16(tmem_base, da, db, idesc, (i > 0 || kk > 0) ? 1u : 0u);
+          tc_mma_f16(tmem_base + acc_col, da, db, idesc, (!fresh || kk > 0) ? 1u : 0u);
         }
         tc_commit(&op_empty[slot]);                 // frees the operand stage when these MMAs have read it
       }
@@ -422,6 +429,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.f;
       }
+      if (NMMA >= 64 && serial > 1 && acc_ok && stages > 0) {
+        // add the other K ranges' accumulators in range order: the fp32 sums of the K-split launch
+#pragma unroll 1
+        for (int r = 1; r < serial; ++r) {
+          if (r * p.k_chunk >= p.k) break;
+          float w[32];
+          tmem_load32(tmem_base + (uint32_t(lane_base) << 16) + uint32_t(r * NMMA + c0), w);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += w[i];
+        }
+      }
       if (TIB_SLOT_GRID && tid == 64) trace_slot(91);
 #pragma unroll
       for (int i = 0; i < 32; ++i) dst[(c0 + i) * pitch] = v[i];
@@ -429,17 +447,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     if (TIB_SLOT_GRID && tid == 64) trace_slot(92);
     tc_fence_before();
   }
-  // The first two elements a thread will finish are known: their bias and residual are requested now and arrive while
-  // the barrier is pending.  (Both are complete: every thread is past the dependency wait.)
+  // Finishing works on runs of 8 columns (16-byte loads and stores of fp16) when the tile is large and the layout
+  // allows, else element by element.  The bias and residual of a thread's first run are requested now and arrive while the barrier is pending
+  // (both are complete: every thread is past the dependency wait); inside the loop the next run's are requested
+  // before the current one is finished, so a 64..256-row tile does not pay one round trip per run.
   const int total = NMMA * cpr;
+  // (compiled for tiles of 64 rows and more only: the 32-row decode kernel stays small)
+  const bool vec8 = NMMA >= 64 && NMMA * cpr >= 8 * kTcThreads &&    // small tiles: one element per thread keeps every thread busy
+                    !p.out_fp32 && cpr % 8 == 0 && p.n % 8 == 0 && p.ldo % 8 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0 &&
+                    (!p.bias || reinterpret_cast<uintptr_t>(p.bias) % 16 == 0) && (!p.residual || reinterpret_cast<uintptr_t>(p.residual) % 16 == 0) &&
+                    (!p.k_pool || p.kv_hidden % 64 == 0);
+  const int runs_per_row = cpr / 8, runs = NMMA * runs_per_row;
+  uint4 bias8 = make_uint4(0, 0, 0, 0), res8 = bias8;
+  auto request = [&](int i, uint4& b8, uint4& r8) {              // inputs of run i (vec8)
+    const int m = i / runs_per_row, row = m0 + m, col = n0 + rank * cpr + (i - m * runs_per_row) * 8;
+    b8 = make_uint4(0, 0, 0, 0); r8 = b8;
+    if (i < runs && row < p.m && col < p.n) {
+      if (p.bias) b8 = *reinterpret_cast<const uint4*>(p.bias + col);
+      if (p.residual && !(p.k_pool && col >= p.kv_hidden)) r8 = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldo + col);
+    }
+  };
   __half pre_bias[2], pre_res[2];
+  pre_bias[0] = pre_bias[1] = pre_res[0] = pre_res[1] = f2h(0.f);
+  if (NMMA >= 64 && vec8) request(tid, bias8, res8);
+  else {
 #pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    const int i = tid + s * kTcThreads, m = i / cpr, row = m0 + m, col = n0 + rank * cpr + (i - m * cpr);
-    pre_bias[s] = pre_res[s] = f2h(0.f);
-    if (i < total && row < p.m && col < p.n) {
-      if (p.bias) pre_bias[s] = p.bias[col];
-      if (p.residual && !p.out_fp32 && !(p.k_pool && col >= p.kv_hidden)) pre_res[s] = p.residual[size_t(row) * p.ldo + col];
+    for (int s = 0; s < 2; ++s) {
+      const int i = tid + s * kTcThreads, m = i / cpr, row = m0 + m, col = n0 + rank * cpr + (i - m * cpr);
+      if (i < total && row < p.m && col < p.n) {
+        if (p.bias) pre_bias[s] = p.bias[col];
+        if (p.residual && !p.out_fp32 && !(p.k_pool && col >= p.kv_hidden)) pre_res[s] = p.residual[size_t(row) * p.ldo + col];
+      }
     }
   }
   if (splits > 1) cluster.sync(); else __syncthreads();         // all partial sums are where they will be read
@@ -466,6 +504,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         if (col + 2 < p.n) out[2] = f.z;
       }
     }
+  } else if (NMMA >= 64 && vec8) {
+#pragma unroll 1
+    for (int i = tid; i < runs; i += kTcThreads) {
+      uint4 next_b, next_r;
+      request(i + kTcThreads, next_b, next_r);
+      const int m = i / runs_per_row, c = (i - m * runs_per_row) * 8;
+      const int row = m0 + m, col = n0 + rank * cpr + c;
+      float v[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = 0.f;
+      if (push) {
+        for (int r = 0; r < splits; ++r) {
+          const float4 lo = *reinterpret_cast<const float4*>(recv + (r * 32 + m) * cpr + c), hi = *reinterpret_cast<const float4*>(recv + (r * 32 + m) * cpr + c + 4);
+          v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w; v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+        }
+      } else if (splits > 1) {
+        for (int r = 0; r < splits; ++r) {
+          const float* src = cluster.map_shared_rank(part, r) + m * 128 + rank * cpr + c;
+          const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
+          v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w; v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
+        }
+      } else {
+        const float4 lo = *reinterpret_cast<const float4*>(part + m * 128 + c), hi = *reinterpret_cast<const float4*>(part + m * 128 + c + 4);
+        v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+      }
+      if (row < p.m && col < p.n && good) {
+        const __half* b = reinterpret_cast<const __half*>(&bias8);
+        const __half* rr = reinterpret_cast<const __half*>(&res8);
+        const bool to_cache = p.k_pool && col >= p.kv_hidden;
+        uint4 packed;
+        __half* h = reinterpret_cast<__half*>(&packed);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          __half t = f2h(v[e] + h2f(b[e]));                    // the rounding points of gemv_store
+          if (!to_cache) {
+            if (p.gelu) t = f2h(gelu_tanh(h2f(t)));
+            if (p.residual) t = f2h(h2f(rr[e]) + h2f(t));
+          }
+          h[e] = t;
+        }
+        if (to_cache) {
+          const int cc = col - p.kv_hidden, which = cc >= p.kv_hidden, e0 = which ? cc - p.kv_hidden : cc;
+          *reinterpret_cast<uint4*>((which ? p.v_pool : p.k_pool) + s_row_base[m] + (e0 >> 6) * 2048 + (e0 & 63)) = packed;
+        } else {
+          *reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + size_t(row) * p.ldo + col) = packed;
+        }
+      }
+      bias8 = next_b; res8 = next_r;
+    }
   } else {
 #pragma unroll 1
     for (int i = tid, s = 0; i < total; i += kTcThreads, ++s) {
@@ -488,7 +575,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   if (splits > 1 && !push) cluster.sync(); else __syncthreads();
   trace_event(kTrGemmTc, 2);
   if (TIB_SLOT_GRID && threadIdx.x == 0) trace_slot(99);
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, tmem_cols); }
 }
 
 }  // namespace tib

@@ -169,6 +169,20 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       if (forced_splits > 0) splits = forced_splits;
       int chunk = (c.k + splits - 1) / splits;
       a.k_chunk = (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
+      // Many rows (prefill): a cluster reduction of 64..256-row partial tiles would cost more than the MMAs.  One CTA
+      // then walks the whole K with one TMEM accumulator per K range and adds them in range order -- the very sums
+      // of the split launch, so a row's result still does not depend on how many rows share the call.
+      const int wide = std::min(256, 512 / splits);
+      static const int serial_ok = env_int("TINYINFER_B200_TC_SERIAL", 1);       // measurement aid
+      if (serial_ok && splits > 1 && c.m > 32 && !c.ln_gamma && slabs * ((c.m + wide - 1) / wide) >= sm_count()) {
+        a.serial_chunks = splits;
+        const dim3 grid(slabs, 1, (c.m + wide - 1) / wide);
+        switch (wide) {
+          case 64: return launch_tc<64>(map, a, grid, o);
+          case 128: return launch_tc<128>(map, a, grid, o);
+          default: return launch_tc<256>(map, a, grid, o);
+        }
+      }
       const dim3 grid(slabs, splits, m_tiles);
       switch (nmma) {
         case 32:
