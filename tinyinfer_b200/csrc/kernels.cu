@@ -154,12 +154,7 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
     const bool mapped = c.w_slab_rows ? make_map_2d(&map, c.w, true, slab_count * uint64_t(c.w_slab_rows), 128, 128, 128, uint32_t(kTcStageK), true)
                                       : make_map_2d(&map, c.w, true, uint64_t(c.k), uint64_t(c.n), uint64_t(c.ldw), 128, uint32_t(kTcStageK), true);
     if (mapped) {
-      const int nmma = c.m <= 32 ? 32 : c.m <= 64 ? 64 : c.m <= 128 ? 128 : 256;
-      if (c.ln_gamma) {
-        if (nmma != 32 || c.k > 768 || c.lda != c.k) return cudaErrorNotSupported;
-        a.ln_gamma = static_cast<const __half*>(c.ln_gamma); a.ln_beta = static_cast<const __half*>(c.ln_beta); a.ln_eps = c.ln_eps;
-      }
-      const int slabs = (c.n + 127) / 128, m_tiles = (c.m + nmma - 1) / nmma;
+      const int slabs = (c.n + 127) / 128;
       // K split chosen from the matrix alone (never from M): the summation grouping of an output
       // element is then the same for every batch size and batch composition.
       int splits = 1;
@@ -167,6 +162,16 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       while (splits < 8 && slabs * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= kTcStageK) splits *= 2;
       static const int forced_splits = env_int("TINYINFER_B200_TC_SPLITS", 0);      // measurement aid
       if (forced_splits > 0) splits = forced_splits;
+      // Up to 128 rows of a K-split matrix: tiles of 32 rows (the decode kernel with its one-barrier reduction and
+      // LayerNorm prologue), as many of them along grid.z as the rows need; the weights of the second and later tiles
+      // come from L2.  Without a K split (vocabulary projection) one wider tile dequantises the weights once.
+      static const int tile32_rows = env_int("TINYINFER_B200_TC_TILE32_ROWS", 128);   // measurement aid
+      const int nmma = c.m <= 32 || (splits > 1 && c.m <= tile32_rows) ? 32 : c.m <= 64 ? 64 : c.m <= 128 ? 128 : 256;
+      if (c.ln_gamma) {
+        if (nmma != 32 || c.k > 768 || c.lda != c.k) return cudaErrorNotSupported;
+        a.ln_gamma = static_cast<const __half*>(c.ln_gamma); a.ln_beta = static_cast<const __half*>(c.ln_beta); a.ln_eps = c.ln_eps;
+      }
+      const int m_tiles = (c.m + nmma - 1) / nmma;
       int chunk = (c.k + splits - 1) / splits;
       a.k_chunk = (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
       // Many rows (prefill): a cluster reduction of 64..256-row partial tiles would cost more than the MMAs.  One CTA

@@ -205,7 +205,7 @@ struct ti_llm_model {
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_TRIGGER")) attn_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_WHOLE")) attn_whole = std::atoi(v) != 0;
     fuse_ln = int8 && shape.hidden <= 768;
-    if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) { fuse_ln_rows = std::min(32, std::atoi(v)); fuse_ln = fuse_ln && fuse_ln_rows > 0; }
+    if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) { fuse_ln_rows = std::min(128, std::atoi(v)); fuse_ln = fuse_ln && fuse_ln_rows > 0; }
     h_status = host<unsigned int>(1); *h_status = 0;
     d_score_tokens = dev<int32_t>(size_t(opt.capacity)); d_score_mask = dev<uint8_t>(size_t(opt.capacity));
     d_loss = dev<double>(size_t(opt.capacity)); d_loss_sum = dev<double>(1);
@@ -358,7 +358,7 @@ struct ti_llm_model {
   tib::LaunchOpts ln_opts() const { tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl; o.early_trigger = ln_trigger; return o; }
   bool attn_trigger = true;                      // the projection GEMM after attention prefetches its weights meanwhile
   bool attn_early = true, attn_whole = true;     // decode attention: reads ahead of the dependency wait; one CTA per (request, head)
-  int fuse_ln_rows = 32;            // largest row count whose LayerNorms run inside the consuming GEMM
+  int fuse_ln_rows = 128;            // largest row count whose LayerNorms run inside the consuming GEMM
   bool fuse_ln = false;             // int8 weights and rows of at most 768 values: LayerNorm runs inside the consuming GEMM
 
   int32_t* seg(int field) const { return d_seg + size_t(field) * opt.max_batch; }
