@@ -56,16 +56,19 @@ constexpr int kTcOpStages = TIB_TC_OP_STAGES;
 constexpr int kTcRawBytes = kTcStageK * 128;          // int8 tile
 constexpr int kTcOpABytes = 128 * kTcStageK * 2;      // fp16 weight tile
 
-template <int NMMA> struct TcSmem {
+// OPS: operand stages.  LEAN (one 32-row tile without K split or LayerNorm, i.e. the vocabulary projection): two operand
+// stages and no receive region -- 65 KB, so that three CTAs share an SM and 393 column slabs run as one wave.
+template <int NMMA, bool LEAN = false> struct TcSmem {
+  static constexpr int kOps = LEAN ? 2 : kTcOpStages;
   static constexpr int kOpBBytes = NMMA * kTcStageK * 2;
   static constexpr int kRawOff = 0;                                        // 1024-aligned (TMA swizzle)
   static constexpr int kOpAOff = kRawOff + kTcRawStages * kTcRawBytes;
-  static constexpr int kOpBOff = kOpAOff + kTcOpStages * kTcOpABytes;
+  static constexpr int kOpBOff = kOpAOff + kOps * kTcOpABytes;
   // NMMA == 32 (decode): 16 KB where the other CTAs of a K-split cluster deposit their partial sums of the 128 / splits
   // columns this CTA finishes, [source rank][32 rows][128 / splits] fp32.  It aliases nothing: peers write it while this
   // CTA may still be in its main loop.
-  static constexpr int kRecvOff = kOpBOff + kTcOpStages * kOpBBytes;
-  static constexpr int kBarOff = kRecvOff + (NMMA == 32 ? 32 * 128 * 4 : 0);
+  static constexpr int kRecvOff = kOpBOff + kOps * kOpBBytes;
+  static constexpr int kBarOff = kRecvOff + (NMMA == 32 && !LEAN ? 32 * 128 * 4 : 0);
   static constexpr int kBytes = kBarOff + 128 + 1024;                      // barriers + slack for manual 1024 alignment
 };
 
@@ -116,23 +119,25 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
 // grid = (N / 128 slabs, k splits [cluster y], M / NMMA tiles), block = 320.
 // LN: LayerNorm prologue compiled in (0 = none, 1 = every CTA prepares the rows itself, 2 = rows shared out over the
 // K-split cluster); separate instantiations keep the plain GEMM free of that code.
-template <int NMMA, int LN = 0>
-__global__ void __launch_bounds__(kTcThreads)
+template <int NMMA, int LN = 0, bool LEAN = false>
+__global__ void __launch_bounds__(kTcThreads, LEAN ? 3 : NMMA == 32 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   trace_event(kTrGemmTc, 0);
   if (TIB_SLOT_GRID && threadIdx.x == 0) trace_slot(1);
-  using L = TcSmem<NMMA>;
+  using L = TcSmem<NMMA, LEAN>;
+  constexpr int kOps = L::kOps;
+  static_assert(!LEAN || (NMMA == 32 && LN == 0), "lean layout: plain 32-row tiles");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* raw = smem + L::kRawOff;
   uint8_t* op_a = smem + L::kOpAOff;
   uint8_t* op_b = smem + L::kOpBOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t *raw_full = bars, *raw_empty = raw_full + kTcRawStages, *op_full = raw_empty + kTcRawStages, *op_empty = op_full + kTcOpStages,
-           *acc_ready = op_empty + kTcOpStages, *ln_bar = acc_ready + 1;
+  uint64_t *raw_full = bars, *raw_empty = raw_full + kTcRawStages, *op_full = raw_empty + kTcRawStages, *op_empty = op_full + kOps,
+           *acc_ready = op_empty + kOps, *ln_bar = acc_ready + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ln_bar + 1);
-  static_assert((2 * kTcRawStages + 2 * kTcOpStages + 3) * 8 <= 128, "barrier block");
-  static_assert(NMMA != 32 || kTcOpStages * L::kOpBBytes >= 8 * 768 * 2, "LayerNorm row strips live in the B-operand ring");
+  static_assert((2 * kTcRawStages + 2 * kOps + 3) * 8 <= 128, "barrier block");
+  static_assert(LN == 0 || kOps * L::kOpBBytes >= 8 * 768 * 2, "LayerNorm row strips live in the B-operand ring");
   __shared__ int s_failed;
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -151,7 +156,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     s_failed = 0;
     tma_prefetch_desc(&w_map);
     for (int s = 0; s < kTcRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kTcDequantThreads / 32); }
-    for (int s = 0; s < kTcOpStages; ++s) { mbar_init(&op_full[s], kTcDequantThreads / 32); mbar_init(&op_empty[s], 1); }
+    for (int s = 0; s < kOps; ++s) { mbar_init(&op_full[s], kTcDequantThreads / 32); mbar_init(&op_empty[s], 1); }
     mbar_init(acc_ready, 1);
     mbar_init(ln_bar, 32);                                    // one arrival per row of the tile (LayerNorm prologue)
     mbar_fence_init();
@@ -196,8 +201,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       constexpr uint32_t a_lbo = 2048u, a_sbo = 128u;
       bool ok = true;
       for (int i = 0; i < stages && ok; ++i) {
-        const int slot = i % kTcOpStages;
-        ok = mbar_wait(&op_full[slot], uint32_t(i / kTcOpStages) & 1u, kStatusPipeTimeout);
+        const int slot = i % kOps;
+        ok = mbar_wait(&op_full[slot], uint32_t(i / kOps) & 1u, kStatusPipeTimeout);
         if (!ok) break;
         if (TIB_SLOT_GRID) trace_slot(70 + i);
         tc_fence_after();
@@ -295,7 +300,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     // Lead-in: the first operand stages need no release; their weights are dequantised before the
     // dependency on the previous kernel is resolved, so under programmatic dependent launch this
     // overlaps the tail of that kernel.
-    const int lead = min(stages, kTcOpStages);
+    const int lead = min(stages, kOps);
     for (int i = 0; i < lead; ++i) {
       if (ok) ok = mbar_wait(&raw_full[i], 0, kStatusTmaTimeout);
       if (ok) dequantise(i, i);
@@ -377,9 +382,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     }
     // From here a_ring[0] holds stage i's rows, a_ring[1..] the following stages'.
     for (int i = lead; i < stages; ++i) {
-      const int rslot = i % kTcRawStages, oslot = i % kTcOpStages;
+      const int rslot = i % kTcRawStages, oslot = i % kOps;
       if (ok) ok = mbar_wait(&raw_full[rslot], uint32_t(i / kTcRawStages) & 1u, kStatusTmaTimeout);
-      if (ok) ok = mbar_wait(&op_empty[oslot], (uint32_t(i / kTcOpStages) & 1u) ^ 1u, kStatusMmaTimeout);
+      if (ok) ok = mbar_wait(&op_empty[oslot], (uint32_t(i / kOps) & 1u) ^ 1u, kStatusMmaTimeout);
       if (TIB_SLOT_GRID && t == 0) trace_slot(30 + i);
       if (ok) {
         dequantise(rslot, oslot);
@@ -406,7 +411,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   // the K ranks in rank order, bias, activation, residual, store -- one copy of that code.
   float* part = reinterpret_cast<float*>(smem);                // [NMMA][128] fp32, aliases the drained pipeline stages
   float* recv = reinterpret_cast<float*>(smem + L::kRecvOff);  // NMMA == 32 only: [rank][32][128 / splits]
-  constexpr bool kPush = NMMA == 32;
+  constexpr bool kPush = NMMA == 32 && !LEAN;
   const bool push = kPush && splits > 1;
   __shared__ long long s_row_base[NMMA];                       // K/V pool offset of each row of the tile (QKV projection only)
   bool acc_ok = true;

@@ -115,11 +115,11 @@ cudaError_t launch_gemv_mt(int mt, const CUtensorMap& map, const GemvArgs& args,
   }
 }
 
-template <int NMMA, int LN = 0>
+template <int NMMA, int LN = 0, bool LEAN = false>
 cudaError_t launch_tc(const CUtensorMap& map, const GemvArgs& args, dim3 grid, const LaunchOpts& o) {
-  const cudaError_t ready = allow_smem(gemm_tc_kernel<NMMA, LN>, TcSmem<NMMA>::kBytes);
+  const cudaError_t ready = allow_smem(gemm_tc_kernel<NMMA, LN, LEAN>, TcSmem<NMMA, LEAN>::kBytes);
   if (ready != cudaSuccess) return ready;
-  return launch(gemm_tc_kernel<NMMA, LN>, grid, dim3(kTcThreads), TcSmem<NMMA>::kBytes, o, int(grid.y), map, args);
+  return launch(gemm_tc_kernel<NMMA, LN, LEAN>, grid, dim3(kTcThreads), TcSmem<NMMA, LEAN>::kBytes, o, int(grid.y), map, args);
 }
 
 int env_int(const char* name, int fallback) {
@@ -189,11 +189,14 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
         }
       }
       const dim3 grid(slabs, splits, m_tiles);
+      static const int lean_ok = env_int("TINYINFER_B200_TC_LEAN", 1);           // measurement aid
       switch (nmma) {
         case 32:
 #ifdef TIB_LN_RUNTIME
           return launch_tc<32, -1>(map, a, grid, o);
 #endif
+          // no K split, many slabs (vocabulary projection): the lean layout runs three CTAs per SM
+          if (!c.ln_gamma && splits == 1 && lean_ok && slabs > 2 * sm_count()) return launch_tc<32, 0, true>(map, a, grid, o);
           if (!c.ln_gamma) return launch_tc<32>(map, a, grid, o);
           // up to 8 rows every CTA prepares them itself; more are shared out over the K-split cluster
           return splits > 1 && c.m > 8 ? launch_tc<32, 2>(map, a, grid, o) : launch_tc<32, 1>(map, a, grid, o);
