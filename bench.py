@@ -336,10 +336,10 @@ def gpu_main(args, rank, world):
         from tinyinfer_b200 import replicas
         _, slowest_s, value = replicas.job_throughput(BATCH * K, device_ms * 1e-3, dist, "cuda")    # sum of tokens / slowest rank
         device_ms = slowest_s * 1e3
-        chunks = 1
-        while chunks * 128 < max(cached_at_start) + K:
-            chunks *= 2
-        launches_per_step = 1 + 12 * (8 + (1 if chunks > 1 else 0)) + 4
+        # kernels of one decode step: embed, 12 x (QKV GEMM with LayerNorm prologue and K/V placement, attention, projection
+        # GEMM, FC GEMM with LayerNorm prologue, projection GEMM), final LayerNorm (a prologue of the vocabulary GEMM up to
+        # 8 rows), vocabulary GEMM, argmax, advance
+        launches_per_step = 1 + 12 * 5 + (0 if BATCH <= 8 else 1) + 3
         step_gbs = total_bytes / (device_ms * 1e-3) / 1e9
 
         if args.quick:
