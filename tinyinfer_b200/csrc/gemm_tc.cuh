@@ -59,7 +59,7 @@ constexpr int kTcOpABytes = 128 * kTcStageK * 2;      // fp16 weight tile
 // OPS: operand stages.  LEAN (one 32-row tile without K split or LayerNorm, i.e. the vocabulary projection): two operand
 // stages and no receive region -- 65 KB, so that three CTAs share an SM and 393 column slabs run as one wave.
 template <int NMMA, bool LEAN = false> struct TcSmem {
-  static constexpr int kOps = LEAN ? 2 : kTcOpStages;
+  static constexpr int kOps = LEAN || NMMA == 64 ? 2 : kTcOpStages;      // 64-row tiles: two stages keep two CTAs per SM
   static constexpr int kOpBBytes = NMMA * kTcStageK * 2;
   static constexpr int kRawOff = 0;                                        // 1024-aligned (TMA swizzle)
   static constexpr int kOpAOff = kRawOff + kTcRawStages * kTcRawBytes;
@@ -68,7 +68,7 @@ template <int NMMA, bool LEAN = false> struct TcSmem {
   // columns this CTA finishes, [source rank][32 rows][128 / splits] fp32.  It aliases nothing: peers write it while this
   // CTA may still be in its main loop.
   static constexpr int kRecvOff = kOpBOff + kOps * kOpBBytes;
-  static constexpr int kBarOff = kRecvOff + (NMMA == 32 && !LEAN ? 32 * 128 * 4 : 0);
+  static constexpr int kBarOff = kRecvOff + (NMMA <= 64 && !LEAN ? NMMA * 128 * 4 : 0);
   static constexpr int kBytes = kBarOff + 128 + 1024;                      // barriers + slack for manual 1024 alignment
 };
 
@@ -120,7 +120,7 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
 // LN: LayerNorm prologue compiled in (0 = none, 1 = every CTA prepares the rows itself, 2 = rows shared out over the
 // K-split cluster); separate instantiations keep the plain GEMM free of that code.
 template <int NMMA, int LN = 0, bool LEAN = false>
-__global__ void __launch_bounds__(kTcThreads, LEAN ? 3 : NMMA == 32 ? 2 : 1)
+__global__ void __launch_bounds__(kTcThreads, LEAN ? 3 : NMMA <= 64 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   trace_event(kTrGemmTc, 0);
   if (TIB_SLOT_GRID && threadIdx.x == 0) trace_slot(1);
@@ -158,7 +158,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     for (int s = 0; s < kTcRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kTcDequantThreads / 32); }
     for (int s = 0; s < kOps; ++s) { mbar_init(&op_full[s], kTcDequantThreads / 32); mbar_init(&op_empty[s], 1); }
     mbar_init(acc_ready, 1);
-    mbar_init(ln_bar, 32);                                    // one arrival per row of the tile (LayerNorm prologue)
+    mbar_init(ln_bar, NMMA);                                  // one arrival per row of the tile (LayerNorm prologue)
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
@@ -166,8 +166,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   // LayerNorm prologue of more than 8 rows: the rows are shared out over the K-split cluster and the CTAs signal each
   // other's barriers, which must exist first.  (Written as PTX: with cooperative_groups' cluster sync in this place
   // every launch of the kernel, also those that skip it, measured half a microsecond slower.)
-  static_assert(LN <= 0 || NMMA == 32, "LayerNorm prologue: one 32-row tile");
-  const bool fuse_ln = LN < 0 ? (NMMA == 32 && p.ln_gamma != nullptr) : LN != 0;
+  static_assert(LN <= 0 || NMMA <= 64, "LayerNorm prologue: tiles of 32 or 64 rows");
+  const bool fuse_ln = LN < 0 ? (NMMA <= 64 && p.ln_gamma != nullptr) : LN != 0;
   const bool ln_shared = LN < 0 ? (fuse_ln && splits > 1 && p.m > 8) : LN == 2;
   if (ln_shared) {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -268,8 +268,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     };
     // Optional LayerNorm of the rows (decode: NMMA == 32, K <= 768): statistics per row are computed once per CTA
     // right after the dependency resolves, with the same summation order as layernorm_kernel, and applied here.
-    __shared__ __half s_gamma[LN != 0 && NMMA == 32 ? 768 : 1], s_beta[LN != 0 && NMMA == 32 ? 768 : 1];
-    __shared__ float s_mean[32], s_inv[32];
+    __shared__ __half s_gamma[LN != 0 && NMMA <= 64 ? 768 : 1], s_beta[LN != 0 && NMMA <= 64 ? 768 : 1];
+    __shared__ float s_mean[64], s_inv[64];
     if (fuse_ln)
       for (int c = k_begin + t; c < k_end; c += kTcDequantThreads) { s_gamma[c - k_begin] = p.ln_gamma[c]; s_beta[c - k_begin] = p.ln_beta[c]; }
     auto store_a = [&](const uint4 (&src)[kPer], int oslot, int i) {
@@ -282,7 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
           const int m = mg * 8 + m8, kk = i * kTcStageK + kc * 8;      // row of the tile, k offset inside this CTA's range
           if (k_begin + kk < k_end) {
             __half* h = reinterpret_cast<__half*>(&v);
-            const float mean = s_mean[m & 31], inv = s_inv[m & 31];
+            const float mean = s_mean[m & 63], inv = s_inv[m & 63];
 #pragma unroll
             for (int e = 0; e < 8; ++e) h[e] = f2h((h2f(h[e]) - mean) * inv * h2f(s_gamma[kk + e]) + h2f(s_beta[kk + e]));
           }
@@ -317,7 +317,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
 #pragma unroll
       for (int d = 0; d < kAhead; ++d) fetch_a(a_ring[d], d);
     }
-    if constexpr (LN != 0 && NMMA == 32) {
+    if constexpr (LN != 0 && NMMA <= 64) {
       if (fuse_ln) {
         // Up to 8 rows: every CTA prepares them all itself, one warp per row.  More: the 32 rows of the tile are shared
         // out over the K-split cluster, rank r prepares rows r*R .. r*R+R-1 (R = 32 / splits), one warp per row
@@ -325,7 +325,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         // arrival on that CTA's barrier (32 arrivals complete it).  Each row passes through a per-warp strip of the
         // still-empty B-operand ring.
         __half* strip = reinterpret_cast<__half*>(op_b) + size_t(warp - 2) * p.k;
-        const int chunks = p.k / 8, share = ln_shared ? 32 / splits : 32, first = ln_shared ? rank * share : 0;
+        const int chunks = p.k / 8, share = ln_shared ? NMMA / splits : NMMA, first = ln_shared ? rank * share : 0;
 #pragma unroll 1
         for (int local = warp - 2; local < share; local += 8) {   // one row per warp in the usual cases (<= 8 rows per CTA)
           float mean = 0.f, inv = 0.f;
@@ -411,7 +411,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   // the K ranks in rank order, bias, activation, residual, store -- one copy of that code.
   float* part = reinterpret_cast<float*>(smem);                // [NMMA][128] fp32, aliases the drained pipeline stages
   float* recv = reinterpret_cast<float*>(smem + L::kRecvOff);  // NMMA == 32 only: [rank][32][128 / splits]
-  constexpr bool kPush = NMMA == 32 && !LEAN;
+  constexpr bool kPush = NMMA <= 64 && !LEAN;
   const bool push = kPush && splits > 1;
   __shared__ long long s_row_base[NMMA];                       // K/V pool offset of each row of the tile (QKV projection only)
   bool acc_ok = true;
@@ -424,7 +424,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     tc_fence_after();
     const int lane_base = 32 * (warp & 3), n_local = lane_base + lane;
     const int owner = n_local / cpr;
-    float* dst = push ? cluster.map_shared_rank(recv, owner) + (rank * 32) * cpr + (n_local - owner * cpr) : part + n_local;
+    float* dst = push ? cluster.map_shared_rank(recv, owner) + (rank * NMMA) * cpr + (n_local - owner * cpr) : part + n_local;
     const int pitch = push ? cpr : 128;
 #pragma unroll 1
     for (int c0 = 0; c0 < NMMA; c0 += 32) {
@@ -472,12 +472,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       if (p.residual && !(p.k_pool && col >= p.kv_hidden)) r8 = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldo + col);
     }
   };
-  __half pre_bias[2], pre_res[2];
-  pre_bias[0] = pre_bias[1] = pre_res[0] = pre_res[1] = f2h(0.f);
+  constexpr int kPre = NMMA <= 32 ? 2 : 4;                      // elements per thread of a split 32 / 64-row tile
+  __half pre_bias[kPre], pre_res[kPre];
+#pragma unroll
+  for (int s = 0; s < kPre; ++s) pre_bias[s] = pre_res[s] = f2h(0.f);
   if (NMMA >= 64 && vec8) request(tid, bias8, res8);
   else {
 #pragma unroll
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kPre; ++s) {
       const int i = tid + s * kTcThreads, m = i / cpr, row = m0 + m, col = n0 + rank * cpr + (i - m * cpr);
       if (i < total && row < p.m && col < p.n) {
         if (p.bias) pre_bias[s] = p.bias[col];
@@ -521,7 +523,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       for (int e = 0; e < 8; ++e) v[e] = 0.f;
       if (push) {
         for (int r = 0; r < splits; ++r) {
-          const float4 lo = *reinterpret_cast<const float4*>(recv + (r * 32 + m) * cpr + c), hi = *reinterpret_cast<const float4*>(recv + (r * 32 + m) * cpr + c + 4);
+          const float4 lo = *reinterpret_cast<const float4*>(recv + (r * NMMA + m) * cpr + c), hi = *reinterpret_cast<const float4*>(recv + (r * NMMA + m) * cpr + c + 4);
           v[0] += lo.x; v[1] += lo.y; v[2] += lo.z; v[3] += lo.w; v[4] += hi.x; v[5] += hi.y; v[6] += hi.z; v[7] += hi.w;
         }
       } else if (splits > 1) {
@@ -564,15 +566,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       const int m = i / cpr, c = i - m * cpr;
       float v = 0.f;
       if (push) {
-        for (int r = 0; r < splits; ++r) v += recv[(r * 32 + m) * cpr + c];
+        for (int r = 0; r < splits; ++r) v += recv[(r * NMMA + m) * cpr + c];
       } else if (splits > 1) {
         for (int r = 0; r < splits; ++r) v += cluster.map_shared_rank(part, r)[m * 128 + rank * cpr + c];
       } else {
         v = part[m * 128 + c];
       }
       const int row = m0 + m, col = n0 + rank * cpr + c;
-      if (row < p.m && col < p.n && good)
-        gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1, s < 2, s == 0 ? pre_bias[0] : pre_bias[1], s == 0 ? pre_res[0] : pre_res[1]);
+      if (row < p.m && col < p.n && good) {
+        __half b = pre_bias[0], r = pre_res[0];
+#pragma unroll
+        for (int q = 1; q < kPre; ++q) if (s == q) { b = pre_bias[q]; r = pre_res[q]; }
+        gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1, s < kPre, b, r);
+      }
     }
   }
   if (TIB_SLOT_GRID && tid == 64) trace_slot(94);

@@ -162,13 +162,12 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       while (splits < 8 && slabs * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= kTcStageK) splits *= 2;
       static const int forced_splits = env_int("TINYINFER_B200_TC_SPLITS", 0);      // measurement aid
       if (forced_splits > 0) splits = forced_splits;
-      // Up to 128 rows of a K-split matrix: tiles of 32 rows (the decode kernel with its one-barrier reduction and
-      // LayerNorm prologue), as many of them along grid.z as the rows need; the weights of the second and later tiles
-      // come from L2.  Without a K split (vocabulary projection) one wider tile dequantises the weights once.
-      static const int tile32_rows = env_int("TINYINFER_B200_TC_TILE32_ROWS", 128);   // measurement aid
-      const int nmma = c.m <= 32 || (splits > 1 && c.m <= tile32_rows) ? 32 : c.m <= 64 ? 64 : c.m <= 128 ? 128 : 256;
+      // 33..128 rows of a K-split matrix: tiles of 64 rows in the decode kernel's form (push reduction, LayerNorm
+      // prologue, two CTAs per SM), so that a 64-request step still runs every GEMM as one wave of clusters.
+      static const int tile64_rows = env_int("TINYINFER_B200_TC_TILE64_ROWS", 128);   // measurement aid
+      const int nmma = c.m <= 32 ? 32 : (c.m <= 64 || (splits > 1 && c.m <= tile64_rows)) ? 64 : c.m <= 128 ? 128 : 256;
       if (c.ln_gamma) {
-        if (nmma != 32 || c.k > 768 || c.lda != c.k) return cudaErrorNotSupported;
+        if (nmma > 64 || (nmma == 64 && splits == 1) || c.k > 768 || c.lda != c.k) return cudaErrorNotSupported;
         a.ln_gamma = static_cast<const __half*>(c.ln_gamma); a.ln_beta = static_cast<const __half*>(c.ln_beta); a.ln_eps = c.ln_eps;
       }
       const int m_tiles = (c.m + nmma - 1) / nmma;
@@ -200,7 +199,7 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
           if (!c.ln_gamma) return launch_tc<32>(map, a, grid, o);
           // up to 8 rows every CTA prepares them itself; more are shared out over the K-split cluster
           return splits > 1 && c.m > 8 ? launch_tc<32, 2>(map, a, grid, o) : launch_tc<32, 1>(map, a, grid, o);
-        case 64: return launch_tc<64>(map, a, grid, o);
+        case 64: return c.ln_gamma ? launch_tc<64, 2>(map, a, grid, o) : launch_tc<64>(map, a, grid, o);
         case 128: return launch_tc<128>(map, a, grid, o);
         default: return launch_tc<256>(map, a, grid, o);
       }
