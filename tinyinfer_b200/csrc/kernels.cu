@@ -162,9 +162,10 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       while (splits < 8 && slabs * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= kTcStageK) splits *= 2;
       static const int forced_splits = env_int("TINYINFER_B200_TC_SPLITS", 0);      // measurement aid
       if (forced_splits > 0) splits = forced_splits;
-      // 33..128 rows of a K-split matrix: tiles of 64 rows in the decode kernel's form (push reduction, LayerNorm
-      // prologue, two CTAs per SM), so that a 64-request step still runs every GEMM as one wave of clusters.
-      static const int tile64_rows = env_int("TINYINFER_B200_TC_TILE64_ROWS", 128);   // measurement aid
+      // 33..1024 rows of a K-split matrix: tiles of 64 rows in the decode kernel's form (push reduction, LayerNorm
+      // prologue, two CTAs per SM): a 64-request step still runs every GEMM as one wave of clusters, and a single prompt's
+      // prefill (measured at 150..900 rows) is faster than with 256-row tiles reduced by remote reads.
+      static const int tile64_rows = env_int("TINYINFER_B200_TC_TILE64_ROWS", 1024);   // measurement aid
       const int nmma = c.m <= 32 ? 32 : (c.m <= 64 || (splits > 1 && c.m <= tile64_rows)) ? 64 : c.m <= 128 ? 128 : 256;
       if (c.ln_gamma) {
         if (nmma > 64 || (nmma == 64 && splits == 1) || c.k > 768 || c.lda != c.k) return cudaErrorNotSupported;
