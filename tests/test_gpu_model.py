@@ -228,6 +228,27 @@ def test_logits_do_not_depend_on_batch_composition(model):
     model.reset_all()
 
 
+def test_admissions_folded_into_a_decode_step_change_nothing(model):
+    """The server appends the prompts of newly admitted requests to the decode step of the running ones (one pass).
+    Running requests must get bit-identical logits whether or not prompts ride along (their attention takes the
+    decode kernel in both cases), and the newcomers the same logits as in a pass of their own."""
+    rng = np.random.default_rng(33)
+    running = [rng.integers(0, 50257, int(n)).tolist() for n in (40, 300, 97)]
+    newcomers = [rng.integers(0, 50257, int(n)).tolist() for n in (150, 1, 31)]
+    model.reset_all()
+    ids = [int(t) for t in logits_of(model.forward([0, 1, 2], running)).argmax(-1)]
+    step_alone = logits_of(model.forward([0, 1, 2], [[t] for t in ids]))
+    prefill_alone = logits_of(model.forward([3, 4, 5], newcomers))
+    model.reset_all()
+    model.forward([0, 1, 2], running, return_logits=False)
+    order = [3, 0, 4, 1, 2, 5]
+    rows = [newcomers[0], [ids[0]], newcomers[1], [ids[1]], [ids[2]], newcomers[2]]
+    mixed = logits_of(model.forward(order, rows))
+    assert torch.equal(mixed[[1, 3, 4]], step_alone), "a running request's logits depend on the admissions in its step"
+    assert torch.equal(mixed[[0, 2, 5]], prefill_alone), "a prompt's logits depend on the decode rows it travels with"
+    model.reset_all()
+
+
 def test_medium_shape_matches_cpu_oracle(tmp_path_factory):
     """GPT-2 medium shape (24 layers, 16 heads, hidden 1024), seed 3: the reference runtime cannot load it
     (compile-time 12/12/768), so the operator-composed CPU oracle is the reference here."""

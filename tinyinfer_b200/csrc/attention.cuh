@@ -61,6 +61,7 @@ struct AttnArgs {
   const int32_t* row_start;                        // optional: request b starts at row row_start[b] (replaces b*q_sb, b*o_sb)
   const int32_t* q_lengths; const int32_t* kv_lengths; const int32_t* offsets;
   int batch, heads, q_len, kv_len, causal;
+  int skip_single;                                 // requests with exactly one query row are left to the decode kernel
 };
 
 // ------------------------------------------------------------------ tiled kernel (Q >= 1)
@@ -77,6 +78,7 @@ attn_tile_kernel(const AttnArgs p, const KV kv) {
   const int h = blockIdx.y, b = blockIdx.z, qi = blockIdx.x * kAttnTileQ + warp;
   pdl_wait();
   const int q_valid = max(0, min(p.q_len, p.q_lengths[b]));
+  if (p.skip_single && p.q_lengths[b] == 1) return;               // uniform per CTA; nothing is written for this request here
   const int kv_valid = max(0, min(p.kv_len, p.kv_lengths[b]));
   const long long off = p.offsets[b];
   const long long q_base = p.row_start ? p.row_start[b] * p.q_si : b * p.q_sb;
@@ -168,6 +170,9 @@ struct DecodeArgs {
   // early: kv_lengths, the page table and every key but each request's newest one were written before the
   // kernel ahead of this one started, so they are read before the dependency wait (their latency then hides
   // behind that kernel); the newest key and the query are read after it.
+  // Mixed passes of the model runtime (prompts and single tokens in one call): request b's row is row_start[b] instead
+  // of b, and requests whose q_lengths[b] is not 1 are left to the tile kernel.  Both null in a pure decode step.
+  const int32_t* row_start; const int32_t* q_lengths;
   int early;
   int early_trigger;                                 // release the next kernel's launch before this one's own wait
 };
@@ -395,8 +400,10 @@ attn_decode_staged_kernel(const DecodeArgs p, const KV kv) {
   pdl_wait();
   trace_event(kTrAttnDecode, 1);
   if (!p.early) len = p.kv_lengths[b];
+  if (p.q_lengths && p.q_lengths[b] != 1) return;      // uniform per CTA (never combined with `early`: nothing is in flight)
+  const long long row = p.row_start ? p.row_start[b] : b;
 
-  const uint4 qraw = *reinterpret_cast<const uint4*>(p.q + b * p.q_sb + h * p.q_sh + dp * 8);
+  const uint4 qraw = *reinterpret_cast<const uint4*>(p.q + row * p.q_sb + h * p.q_sh + dp * 8);
   const __half2* q2 = reinterpret_cast<const __half2*>(&qraw);
   float m = -CUDART_INF_F, l = 0.f, acc[8];
 #pragma unroll
@@ -489,7 +496,7 @@ attn_decode_staged_kernel(const DecodeArgs p, const KV kv) {
       const float f = s_ml[w][0] > -CUDART_INF_F ? expf(s_ml[w][0] - mm) : 0.f;
       ll += s_ml[w][1] * f; aa += s_acc[w][tid] * f;
     }
-    p.out[b * p.o_sb + h * p.o_sh + tid] = f2h(ll > 0.f ? aa / ll : 0.f);
+    p.out[row * p.o_sb + h * p.o_sh + tid] = f2h(ll > 0.f ? aa / ll : 0.f);
   }
 }
 

@@ -260,7 +260,7 @@ static KvPaged paged(const PagedKv& kv) {
 }
 
 cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start, const int32_t* ql, const int32_t* kl,
-                            const int32_t* off, int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& o) {
+                            const int32_t* off, int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& o, bool skip_single) {
   if (kv.head_dim != 64) return cudaErrorInvalidValue;
   const int hidden = kv.heads * kv.head_dim;
   AttnArgs p{};
@@ -269,7 +269,7 @@ cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start
   p.o_sb = 0; p.o_sh = kv.head_dim; p.o_si = hidden;
   p.row_start = row_start;
   p.q_lengths = ql; p.kv_lengths = kl; p.offsets = off;
-  p.batch = batch; p.heads = kv.heads; p.q_len = max_q; p.kv_len = max_kv; p.causal = 1;
+  p.batch = batch; p.heads = kv.heads; p.q_len = max_q; p.kv_len = max_kv; p.causal = 1; p.skip_single = skip_single ? 1 : 0;
   const dim3 grid((max_q + kAttnTileQ - 1) / kAttnTileQ, kv.heads, batch);
   return launch(attn_tile_kernel<64, KvPaged>, grid, dim3(256), 0, o, 1, p, paged(kv));
 }
@@ -278,14 +278,16 @@ int decode_chunks(int max_kv, int chunk) { return std::max(1, (max_kv + chunk - 
 
 cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kl, int batch, int max_kv, int chunk,
                                    float* scratch_acc, float* scratch_ml, int* counters, const PagedKv& kv, const LaunchOpts& o,
-                                   bool early, bool whole_history, bool early_trigger) {
+                                   bool early, bool whole_history, bool early_trigger, const int32_t* row_start, const int32_t* q_lengths) {
   if (kv.head_dim != 64) return cudaErrorInvalidValue;
   const int hidden = kv.heads * kv.head_dim;
   DecodeArgs p{};
   p.q = static_cast<const __half*>(qkv); p.q_sb = 3LL * hidden; p.q_sh = kv.head_dim;
   p.out = static_cast<__half*>(out); p.o_sb = hidden; p.o_sh = kv.head_dim;
   p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml; p.counters = counters;
-  p.batch = batch; p.heads = kv.heads; p.early = early ? 1 : 0; p.early_trigger = early_trigger ? 1 : 0;
+  p.batch = batch; p.heads = kv.heads; p.early = early && !q_lengths ? 1 : 0; p.early_trigger = early_trigger ? 1 : 0;
+  p.row_start = row_start; p.q_lengths = q_lengths;
+  if ((row_start || q_lengths) && !whole_history) return cudaErrorNotSupported;
   if (whole_history) {
     // One CTA of 8 warps walks the whole history of a (request, head) and merges in shared memory: no partials in
     // global memory, no second stage, and a grid small enough to be resident at once.

@@ -69,7 +69,8 @@ TIB_EXPORT cudaError_t attention_packed(const void* q, const void* k, const void
 // qkv[rows, 3*hidden]; attention output goes to out[rows, hidden] (heads merged).
 TIB_EXPORT cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start,
                                        const int32_t* q_lengths, const int32_t* kv_lengths, const int32_t* offsets,
-                                       int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& opts);
+                                       int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& opts,
+                                       bool skip_single = false);
 // Decode: one row per request.  scratch_acc: fp32 [batch*heads*chunks*D], scratch_ml: fp32
 // [batch*heads*chunks*2]; chunks = ceil(max_kv / chunk).
 // counters: optional int [batch*heads], zero between launches; when given the merge of the chunk
@@ -78,11 +79,14 @@ TIB_EXPORT cudaError_t attention_paged(const void* qkv, void* out, const int32_t
 // ahead of this launch started (true inside a decode step: only the QKV projection precedes it); they are
 // then read ahead of the dependency wait.  whole_history: one CTA per (request, head) instead of one per chunk;
 // chunk, scratch and counters are not used.  early_trigger: the kernel launched after this one may start at once
-// (it must then read nothing but constants ahead of its own dependency wait).
+// (it must then read nothing but constants ahead of its own dependency wait).  row_start / q_lengths (whole_history
+// only): a pass that mixes prompts and single tokens -- request b's row is row_start[b], requests with q_lengths[b] != 1
+// are skipped (attention_paged with skip_single handles them).
 TIB_EXPORT cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kv_lengths,
                                               int batch, int max_kv, int chunk, float* scratch_acc, float* scratch_ml,
                                               int* counters, const PagedKv& kv, const LaunchOpts& opts,
-                                              bool early = false, bool whole_history = false, bool early_trigger = false);
+                                              bool early = false, bool whole_history = false, bool early_trigger = false,
+                                              const int32_t* row_start = nullptr, const int32_t* q_lengths = nullptr);
 TIB_EXPORT int decode_chunks(int max_kv, int chunk);
 // Same decode attention over packed k/v[B,H,K,D] with q[B,H,1,D] (additive operator export).
 TIB_EXPORT cudaError_t attention_packed_decode(const void* q, const void* k, const void* v, void* y,

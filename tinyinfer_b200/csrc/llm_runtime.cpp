@@ -202,6 +202,7 @@ struct ti_llm_model {
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_EARLY")) attn_early = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_LN_TRIGGER")) ln_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_GEMM_TRIGGER")) gemm_trigger = std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_MIXED_ATTN")) mixed_attention = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_TRIGGER")) attn_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_WHOLE")) attn_whole = std::atoi(v) != 0;
     fuse_ln = int8 && shape.hidden <= 768;
@@ -250,6 +251,7 @@ struct ti_llm_model {
     const int32_t *ids, *row_req, *row_pos;                       // per row
     const int32_t *row_start, *qlens, *offsets, *kvlens, *slots;   // per request
     int rows, batch, max_q, max_kv;
+    int singles;                                                  // requests with exactly one row in this pass
   };
 
   // Embedding and every transformer block; leaves the final hidden state in `x`.
@@ -270,8 +272,17 @@ struct ti_llm_model {
         ck(tib::layernorm(x, nullptr, b.ln1_g, b.ln1_b, norm, m.rows, H, 1e-5f, ln_opts()));
         gemm(norm, b.qkv, qkv, m.rows, false, nullptr, false, &kv, m.row_req, m.row_pos);   // Q -> qkv buffer, K/V -> their pages
       }
-      if (m.max_q == 1) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o, attn_early, attn_whole, attn_trigger));
-      else ck(tib::attention_paged(qkv, attn, m.row_start, m.qlens, m.kvlens, m.offsets, m.batch, m.max_q, m.max_kv, kv, o));
+      if (m.max_q == 1) {
+        ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o, attn_early, attn_whole, attn_trigger));
+      } else {
+        // Prompts and single tokens in one pass (the server folds admissions into a decode step): the single-token
+        // requests take the decode kernel -- the same arithmetic as in a pure decode step, so their tokens do not
+        // depend on what else is admitted -- and the tile kernel skips them.
+        const bool split = attn_whole && mixed_attention && m.singles > 0;
+        if (split) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o,
+                                                  false, true, false, m.row_start, m.qlens));
+        ck(tib::attention_paged(qkv, attn, m.row_start, m.qlens, m.kvlens, m.offsets, m.batch, m.max_q, m.max_kv, kv, o, split));
+      }
       gemm(attn, b.proj, res, m.rows, false, x, false);             // res = x + proj(attn)
       if (fused) gemm(res, b.fc, act, m.rows, false, nullptr, true, nullptr, nullptr, nullptr, b.ln2_g, b.ln2_b);
       else {
@@ -303,7 +314,7 @@ struct ti_llm_model {
   void transform(const std::vector<int32_t>& ss, const std::vector<int32_t>& packed, const std::vector<int32_t>& lens, bool all_rows) {
     const int batch = int(ss.size()), H = shape.hidden;
     Meta m{}; m.batch = batch;
-    for (int b = 0; b < batch; ++b) { m.rows += lens[size_t(b)]; m.max_q = std::max(m.max_q, lens[size_t(b)]); }
+    for (int b = 0; b < batch; ++b) { m.rows += lens[size_t(b)]; m.max_q = std::max(m.max_q, lens[size_t(b)]); m.singles += lens[size_t(b)] == 1; }
     const int rows = m.rows;
     int32_t* ids = h_meta; int32_t* row_req = ids + rows; int32_t* row_pos = row_req + rows; int32_t* per = row_pos + rows;
     int32_t *row_start = per, *qlens = per + batch, *offsets = per + 2 * batch, *kvlens = per + 3 * batch,
@@ -356,6 +367,7 @@ struct ti_llm_model {
   // may start at once; measured: a few microseconds per step at small batches.  After a LayerNorm it did not pay.
   bool ln_trigger = false, gemm_trigger = true;
   tib::LaunchOpts ln_opts() const { tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl; o.early_trigger = ln_trigger; return o; }
+  bool mixed_attention = true;                   // mixed passes: single-token requests through the decode kernel
   bool attn_trigger = true;                      // the projection GEMM after attention prefetches its weights meanwhile
   bool attn_early = true, attn_whole = true;     // decode attention: reads ahead of the dependency wait; one CTA per (request, head)
   int fuse_ln_rows = 128;            // largest row count whose LayerNorms run inside the consuming GEMM

@@ -410,22 +410,22 @@ void Worker::run() noexcept {
           if (a.generated.size() == a.job->wire.max_new) { replica_->reset(int(slot)); retire(slot, kOk); }
         }
       };
-      if (!new_slots.empty()) absorb(new_slots, replica_->step(new_slots, new_rows), Clock::now());
-      // ---- one decode step for every request that already has its first token
-      std::vector<int32_t> step_slots;
-      std::vector<const std::vector<int32_t>*> step_rows;
+      // ---- one pass: the prompts of the requests admitted above together with one decode step for every request
+      // that already has its first token (admissions do not cost the running requests a separate pass)
+      std::vector<int32_t> pass_slots = new_slots;
+      std::vector<const std::vector<int32_t>*> pass_rows = new_rows;
       std::vector<std::vector<int32_t>> last_tokens;
       last_tokens.reserve(slots);
       for (size_t slot = 0; slot < slots; ++slot) {
         if (!active[slot]) continue;
         Active& a = *active[slot];
+        if (std::find(new_slots.begin(), new_slots.end(), int32_t(slot)) != new_slots.end()) continue;   // admitted this round
         if (a.job->cancel.load() || server_.stopping()) { replica_->reset(int(slot)); retire(slot, kCancelled); continue; }
-        if (std::find(new_slots.begin(), new_slots.end(), int32_t(slot)) != new_slots.end()) continue;   // prefilled this round
         last_tokens.push_back({a.generated.back()});
-        step_slots.push_back(int32_t(slot));
+        pass_slots.push_back(int32_t(slot));
       }
-      for (auto& row : last_tokens) step_rows.push_back(&row);
-      if (!step_slots.empty()) absorb(step_slots, replica_->step(step_slots, step_rows), Clock::now());
+      for (auto& row : last_tokens) pass_rows.push_back(&row);
+      if (!pass_slots.empty()) absorb(pass_slots, replica_->step(pass_slots, pass_rows), Clock::now());
     } catch (const std::exception& error) {
       // A failed native call leaves the replica unusable: everything outstanding and everything that
       // arrives later on this worker is answered with an internal error; the process stays up.
