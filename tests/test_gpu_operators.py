@@ -85,6 +85,24 @@ def test_operator_sweep_against_oracle(ops, m):
     close(ops.gemm_int8(a, w, s, bias=bias), want)
 
 
+@pytest.mark.parametrize("k,n", [(768, 2304), (3072, 768)])
+def test_a_row_does_not_depend_on_the_row_count(ops, k, n):
+    """The tensor-core GEMM changes its shape with the row count -- 32-row tiles with the partial sums pushed to the
+    finishing CTA, 64-row tiles, one CTA per tile walking the whole K with an accumulator per K range, scalar or
+    8-column finishing -- but every form adds the same K ranges in the same order: the first rows of a large call are
+    bit-identical to a call with only those rows, with and without the fused GELU / residual epilogue."""
+    a, w, s, bias = int8_case(torch, 1500, n, k, seed=5)
+    res = torch.randn((1500, n), device="cuda").half()
+    small = ops.gemm_int8(a[:20], w, s, bias=bias)
+    small_fused = ops.gemm_int8_fused(a[:20], w, s, bias=bias, gelu=True, residual=res[:20])
+    for rows in (48, 200, 700, 1500):
+        assert torch.equal(ops.gemm_int8(a[:rows], w, s, bias=bias)[:20], small), f"{rows} rows"
+        got = ops.gemm_int8_fused(a[:rows], w, s, bias=bias, gelu=True, residual=res[:rows].contiguous())
+        assert torch.equal(got[:20], small_fused), f"{rows} rows, fused epilogue"
+    want = orc.gemm_int8(a.cpu().numpy(), w.cpu().numpy(), s.cpu().numpy(), bias.cpu().numpy(), out_fp32=True)
+    close(ops.gemm_int8(a, w, s, bias=bias), want)
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 3072, 768), (8, 768, 3072), (32, 3072, 768), (3, 100, 40)])
 def test_fused_bias_gelu_residual_equals_reference_sequence(ops, ref, m, n, k):
     a, w, s, bias = int8_case(torch, m, n, k, seed=1)
