@@ -156,7 +156,6 @@ attn_tile_kernel(const AttnArgs p, const KV kv) {
 
 // ------------------------------------------------------------------ decode kernel (Q == 1)
 constexpr int kDecodeWarps = 4;          // chunked launches: 128 keys per CTA pass
-constexpr int kDecodeWarpsWhole = 8;     // one CTA per (request, head): 256 keys per pass over the whole history
 
 struct DecodeArgs {
   const __half* q; long long q_sb, q_sh;            // one query row per request

@@ -166,9 +166,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   // LayerNorm prologue of more than 8 rows: the rows are shared out over the K-split cluster and the CTAs signal each
   // other's barriers, which must exist first.  (Written as PTX: with cooperative_groups' cluster sync in this place
   // every launch of the kernel, also those that skip it, measured half a microsecond slower.)
-  static_assert(LN <= 0 || NMMA <= 64, "LayerNorm prologue: tiles of 32 or 64 rows");
-  const bool fuse_ln = LN < 0 ? (NMMA <= 64 && p.ln_gamma != nullptr) : LN != 0;
-  const bool ln_shared = LN < 0 ? (fuse_ln && splits > 1 && p.m > 8) : LN == 2;
+  static_assert(LN == 0 || NMMA <= 64, "LayerNorm prologue: tiles of 32 or 64 rows");
+  constexpr bool fuse_ln = LN != 0, ln_shared = LN == 2;
   if (ln_shared) {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   } else {
@@ -312,7 +311,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     // The first stages' rows are requested together (one round trip instead of one per stage).  With the shared
     // LayerNorm prologue they go out before it (its barrier wait covers their latency); with the local one after
     // it (measured: ahead of it they delay the row loads the statistics wait for).
-    constexpr bool kFetchFirst = LN == 2 || LN < 0;
+    constexpr bool kFetchFirst = LN == 2;
     if constexpr (kAhead > 1 && kFetchFirst) {
 #pragma unroll
       for (int d = 0; d < kAhead; ++d) fetch_a(a_ring[d], d);

@@ -192,9 +192,6 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       static const int lean_ok = env_int("TINYINFER_B200_TC_LEAN", 1);           // measurement aid
       switch (nmma) {
         case 32:
-#ifdef TIB_LN_RUNTIME
-          return launch_tc<32, -1>(map, a, grid, o);
-#endif
           // no K split, many slabs (vocabulary projection): the lean layout runs three CTAs per SM
           if (!c.ln_gamma && splits == 1 && lean_ok && slabs > 2 * sm_count()) return launch_tc<32, 0, true>(map, a, grid, o);
           if (!c.ln_gamma) return launch_tc<32>(map, a, grid, o);
@@ -292,13 +289,9 @@ cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kl
     // One CTA of 8 warps walks the whole history of a (request, head) and merges in shared memory: no partials in
     // global memory, no second stage, and a grid small enough to be resident at once.
     p.chunk = 1 << 30; p.chunks = 1;
-    static const int staged = env_int("TINYINFER_B200_ATTN_STAGED", 1);          // measurement aid: 0 = register-resident variant
-    if (staged) {
-      const cudaError_t ready = allow_smem(attn_decode_staged_kernel<64, KvPaged>, staged_smem_bytes<64>());
-      if (ready != cudaSuccess) return ready;
-      return launch(attn_decode_staged_kernel<64, KvPaged>, dim3(kv.heads, batch), dim3(kStagedWarps * 32), staged_smem_bytes<64>(), o, 1, p, paged(kv));
-    }
-    return launch(attn_decode_kernel<64, KvPaged, kDecodeWarpsWhole>, dim3(1, kv.heads, batch), dim3(kDecodeWarpsWhole * 32), 0, o, 1, p, paged(kv));
+    const cudaError_t ready = allow_smem(attn_decode_staged_kernel<64, KvPaged>, staged_smem_bytes<64>());
+    if (ready != cudaSuccess) return ready;
+    return launch(attn_decode_staged_kernel<64, KvPaged>, dim3(kv.heads, batch), dim3(kStagedWarps * 32), staged_smem_bytes<64>(), o, 1, p, paged(kv));
   }
   p.chunk = chunk; p.chunks = decode_chunks(max_kv, chunk);
   cudaError_t st = launch(attn_decode_kernel<64, KvPaged>, dim3(p.chunks, kv.heads, batch), dim3(kDecodeWarps * 32), 0, o, 1, p, paged(kv));
