@@ -89,6 +89,10 @@ __device__ __forceinline__ uint32_t cluster_addr(const void* local, uint32_t ran
 __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+// one 64-bit scalar store (single-copy atomic): both halves become visible together
+__device__ __forceinline__ void st_cluster_b64(uint32_t addr, unsigned long long v) {
+  asm volatile("st.shared::cluster.b64 [%0], %1;" ::"r"(addr), "l"(v) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(addr) : "memory");
 }

@@ -134,9 +134,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   uint8_t* op_b = smem + L::kOpBOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
   uint64_t *raw_full = bars, *raw_empty = raw_full + kTcRawStages, *op_full = raw_empty + kTcRawStages, *op_empty = op_full + kOps,
-           *acc_ready = op_empty + kOps, *ln_bar = acc_ready + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(ln_bar + 1);
-  static_assert((2 * kTcRawStages + 2 * kOps + 3) * 8 <= 128, "barrier block");
+           *acc_ready = op_empty + kOps;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
+  static_assert((2 * kTcRawStages + 2 * kOps + 2) * 8 <= 128, "barrier block");
   static_assert(LN == 0 || kOps * L::kOpBBytes >= 8 * 768 * 2, "LayerNorm row strips live in the B-operand ring");
   __shared__ int s_failed;
 
@@ -158,17 +158,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     for (int s = 0; s < kTcRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kTcDequantThreads / 32); }
     for (int s = 0; s < kOps; ++s) { mbar_init(&op_full[s], kTcDequantThreads / 32); mbar_init(&op_empty[s], 1); }
     mbar_init(acc_ready, 1);
-    mbar_init(ln_bar, NMMA);                                  // one arrival per row of the tile (LayerNorm prologue)
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, tmem_cols);
   tc_fence_before();
-  // LayerNorm prologue of more than 8 rows: the rows are shared out over the K-split cluster and the CTAs signal each
-  // other's barriers, which must exist first.  (Written as PTX: with cooperative_groups' cluster sync in this place
-  // every launch of the kernel, also those that skip it, measured half a microsecond slower.)
+  // LayerNorm prologue of more than 8 rows: the rows are shared out over the K-split cluster and the CTAs write each
+  // other's statistics slots, which must be initialised first.  (Written as PTX: with cooperative_groups' cluster
+  // sync in this place every launch of the kernel, also those that skip it, measured half a microsecond slower.)
   static_assert(LN == 0 || NMMA <= 64, "LayerNorm prologue: tiles of 32 or 64 rows");
   constexpr bool fuse_ln = LN != 0, ln_shared = LN == 2;
+  // (mean, 1/sigma) of every row of the tile.  Shared mode: written by the CTA that prepares the row as one 8-byte store
+  // through distributed shared memory and awaited by polling 1/sigma, whose initial bit pattern (a NaN that rsqrtf never
+  // returns) means "not here yet": one remote store per row and CTA, no separate signal.
+  __shared__ __align__(8) float2 s_stats[LN != 0 ? 64 : 1];
+  constexpr uint32_t kStatPending = 0xffffffffu;
   if (ln_shared) {
+    if (tid < NMMA) s_stats[tid] = make_float2(0.f, __uint_as_float(kStatPending));
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   } else {
     __syncthreads();
@@ -268,7 +273,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     // Optional LayerNorm of the rows (decode: NMMA == 32, K <= 768): statistics per row are computed once per CTA
     // right after the dependency resolves, with the same summation order as layernorm_kernel, and applied here.
     __shared__ __half s_gamma[LN != 0 && NMMA <= 64 ? 768 : 1], s_beta[LN != 0 && NMMA <= 64 ? 768 : 1];
-    __shared__ float s_mean[64], s_inv[64];
     if (fuse_ln)
       for (int c = k_begin + t; c < k_end; c += kTcDequantThreads) { s_gamma[c - k_begin] = p.ln_gamma[c]; s_beta[c - k_begin] = p.ln_beta[c]; }
     auto store_a = [&](const uint4 (&src)[kPer], int oslot, int i) {
@@ -281,7 +285,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
           const int m = mg * 8 + m8, kk = i * kTcStageK + kc * 8;      // row of the tile, k offset inside this CTA's range
           if (k_begin + kk < k_end) {
             __half* h = reinterpret_cast<__half*>(&v);
-            const float mean = s_mean[m & 63], inv = s_inv[m & 63];
+            const float2 st = s_stats[m & 63];
+            const float mean = st.x, inv = st.y;
 #pragma unroll
             for (int e = 0; e < 8; ++e) h[e] = f2h((h2f(h[e]) - mean) * inv * h2f(s_gamma[kk + e]) + h2f(s_beta[kk + e]));
           }
@@ -340,19 +345,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
 #pragma unroll
             for (int u = 0; u < 3; ++u) { const int c = lane + 32 * u; if (c < chunks) *reinterpret_cast<uint4*>(strip + c * 8) = held[u]; }
             __syncwarp();
+            if (TIB_SLOT_GRID && t == 0) trace_slot(5);
             row_stats(strip, p.k, p.ln_eps, mean, inv);
             __syncwarp();
+            if (TIB_SLOT_GRID && t == 0) trace_slot(6);
           }
           if (!ln_shared) {
-            if (lane == 0) { s_mean[local] = mean; s_inv[local] = inv; }
+            if (lane == 0) s_stats[local] = make_float2(mean, inv);
           } else if (lane < splits) {
-            st_cluster_f32(cluster_addr(&s_mean[first + local], lane), mean);
-            st_cluster_f32(cluster_addr(&s_inv[first + local], lane), inv);
-            mbar_arrive_cluster(cluster_addr(ln_bar, lane));
+            st_cluster_b64(cluster_addr(&s_stats[first + local], lane),
+                           (unsigned long long)__float_as_uint(inv) << 32 | __float_as_uint(mean));
           }
         }
         if (!ln_shared) asm volatile("bar.sync 2, 256;" ::: "memory");      // the eight dequantising warps
-        else if (ok) ok = mbar_wait_cluster(ln_bar, 0, kStatusPipeTimeout);  // all 32 rows' statistics are here
+        else {
+          // every row of the tile is here once its 1/sigma has left the pending pattern (thread t polls rows t, t+256, ..)
+          for (int r = t; r < NMMA; r += kTcDequantThreads) {
+            bool here = false;
+            for (uint32_t spin = 0; spin < kSpinLimit && !here; ++spin)
+              here = uint32_t(reinterpret_cast<volatile unsigned long long*>(s_stats)[r] >> 32) != kStatPending;
+            if (!here) { report(kStatusPipeTimeout); ok = false; }
+          }
+          if (TIB_SLOT_GRID && t == 0) trace_slot(7);
+          asm volatile("bar.sync 2, 256;" ::: "memory");
+          if (TIB_SLOT_GRID && t == 0) trace_slot(8);
+        }
       }
     }
     if constexpr (kAhead > 1) {
