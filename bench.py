@@ -165,7 +165,8 @@ def graph_seconds(enqueue, launches, replays=10):
 
 # DRAM traffic over algorithmic bytes of one launch, from the ncu captures summarised under profiles/
 # (attn_decode_staged_kernel_batch32.md, gemm_tc_kernel_decode_batch32.md); None where no capture exists.
-TRAFFIC_RATIO = {"attention_decode": 27.12 / 26.6, "gemm_int8 qkv": 1.91 / 1.77, "gemm_int8 attn proj": 0.74 / 0.59, "gemm_int8 mlp fc": 2.50 / 2.36, "gemm_int8 mlp proj": 2.66 / 2.36}
+TRAFFIC_RATIO = {"attention_decode": 27.12 / 26.6, "gemm_int8 qkv": 1.91 / 1.77, "gemm_int8 attn proj": 0.74 / 0.59, "gemm_int8 mlp fc": 2.50 / 2.36, "gemm_int8 mlp proj": 2.66 / 2.36,
+                 "gemm_int8 projections": (0.74 + 2.66) / (0.59 + 2.36)}
 
 
 def kernel_rooflines(cached, peak):
@@ -376,7 +377,18 @@ def gpu_main(args, rank, world):
             "e2e": e2e, "gpu_launches": launches_per_step * K, "clocks": clocks.summary()}
     if rank == 0:
         kernels = kernel_rooflines(cached_at_start, peak)
-        top = max(kernels.items(), key=lambda kv: kv[1]["seconds"] * kv[1]["launches_per_step"])
+        # The dominant kernel is chosen the way the ncu launch list counts: by kernel instantiation and grid.  The two
+        # projection GEMMs of a layer (768x768 after attention, 3072x768 after the MLP) are the same kernel with the same
+        # grid (6 slabs x 8 K ranks) and form one entry there: 24 launches per step.
+        ranked = dict(kernels)
+        pa, pm = "gemm_int8 attn proj 768x768 (M=32)", "gemm_int8 mlp proj 3072x768 (M=32)"
+        if pa in ranked and pm in ranked:
+            a, m = ranked.pop(pa), ranked.pop(pm)
+            both = {"seconds": (a["seconds"] + m["seconds"]) / 2, "bytes": (a["bytes"] + m["bytes"]) // 2, "launches_per_step": 24}
+            both["gbs"] = both["bytes"] / both["seconds"] / 1e9
+            both["frac"] = both["gbs"] / peak
+            ranked["gemm_int8 projections: gemm_tc_kernel<32,0> grid (6,8,1), 768x768 and 3072x768 (M=32), mean per launch"] = both
+        top = max(ranked.items(), key=lambda kv: kv[1]["seconds"] * kv[1]["launches_per_step"])
         ratio = next((r for key, r in TRAFFIC_RATIO.items() if top[0].startswith(key)), None)
         line["roofline"] = {"kernel": top[0], "bound": "hbm", "achieved": top[1]["gbs"], "peak": peak, "unit": "GB/s", "frac": top[1]["frac"],
                             "traffic": None if ratio is None else int(top[1]["bytes"] * ratio), "algorithmic_bytes": top[1]["bytes"],
