@@ -1,13 +1,13 @@
 """Regenerates tests/golden/quant_golden.json from the reference itself.
 
-Needs the reference checkout (default /root/reference) and the reference host codec built
+Needs the reference checkout (see --reference) and the reference host codec built
 by `make -C oracle ref-host`; neither is available where the GPU tests run, which is why
 the outputs are committed.  Imports the reference's pure-Python quantiser spec
 (llm/quantization.py), its exporter twin (llm/export_weights.py:quantized_bytes) and its
 native codec wrapper (llm/host_codec.py), feeds them seeded inputs, and stores inputs as
 fp16 bit patterns with the outputs all three agree on.
 
-    python tests/golden/make_golden.py [--reference /root/reference]
+    python tests/golden/make_golden.py [--reference <checkout>]
 """
 import argparse
 import array
