@@ -492,8 +492,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   __half pre_bias[kPre], pre_res[kPre];
 #pragma unroll
   for (int s = 0; s < kPre; ++s) pre_bias[s] = pre_res[s] = f2h(0.f);
+  // 64-row tiles of a K split: a thread finishes four neighbouring columns of one row (their partial sums are read as
+  // float4, one per rank), so the 1024 elements of the tile take one round of 256 threads instead of four.
+  const bool quad = NMMA == 64 && push && cpr % 4 == 0 && p.n % 4 == 0 && p.ldo % 4 == 0 && !p.out_fp32 &&
+                    (!p.bias || reinterpret_cast<uintptr_t>(p.bias) % 8 == 0) && (!p.residual || reinterpret_cast<uintptr_t>(p.residual) % 8 == 0);
+  const int quads_per_row = cpr / 4, quads = NMMA * quads_per_row;
+  uint2 quad_bias = make_uint2(0, 0), quad_res = make_uint2(0, 0);
   if (NMMA >= 64 && vec8) request(tid, bias8, res8);
-  else {
+  else if (NMMA == 64 && quad) {
+    const int m = tid / quads_per_row, row = m0 + m, col = n0 + rank * cpr + (tid - m * quads_per_row) * 4;
+    if (tid < quads && row < p.m && col < p.n) {
+      if (p.bias) quad_bias = *reinterpret_cast<const uint2*>(p.bias + col);
+      if (p.residual && !(p.k_pool && col >= p.kv_hidden)) quad_res = *reinterpret_cast<const uint2*>(p.residual + size_t(row) * p.ldo + col);
+    }
+  } else {
 #pragma unroll
     for (int s = 0; s < kPre; ++s) {
       const int i = tid + s * kTcThreads, m = i / cpr, row = m0 + m, col = n0 + rank * cpr + (i - m * cpr);
@@ -575,6 +587,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         }
       }
       bias8 = next_b; res8 = next_r;
+    }
+  } else if (NMMA == 64 && quad) {
+#pragma unroll 1
+    for (int i = tid, round = 0; i < quads; i += kTcThreads, ++round) {
+      const int m = i / quads_per_row, c = (i - m * quads_per_row) * 4, row = m0 + m;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < splits; ++r) {
+        const float4 part4 = *reinterpret_cast<const float4*>(recv + (r * NMMA + m) * cpr + c);
+        acc.x += part4.x; acc.y += part4.y; acc.z += part4.z; acc.w += part4.w;
+      }
+#pragma unroll 1
+      for (int e = 0; e < 4; ++e) {
+        const int col = n0 + rank * cpr + c + e;
+        const float v = e == 0 ? acc.x : e == 1 ? acc.y : e == 2 ? acc.z : acc.w;
+        const uint32_t wb = e < 2 ? quad_bias.x : quad_bias.y, wr = e < 2 ? quad_res.x : quad_res.y;
+        const __half b = __ushort_as_half(static_cast<unsigned short>((e & 1) ? wb >> 16 : wb & 0xffffu));
+        const __half rr = __ushort_as_half(static_cast<unsigned short>((e & 1) ? wr >> 16 : wr & 0xffffu));
+        if (row < p.m && col < p.n && good) gemv_store(p, row, col, v, p.k_pool ? s_row_base[m] : -1, round == 0, b, rr);
+      }
     }
   } else {
 #pragma unroll 1
