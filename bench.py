@@ -274,8 +274,7 @@ def gpu_main(args, rank, world):
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"          # keep stdout to the one JSON line (NCCL prints its version there)
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line; NCCL's version banner goes to stderr
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     def barrier():
