@@ -274,8 +274,19 @@ def gpu_main(args, rank, world):
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line; NCCL's version banner goes to stderr
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # stdout carries the one JSON line: while the communicator comes up (NCCL prints a version banner on file
+        # descriptor 1 when NCCL_DEBUG is set) descriptor 1 points at stderr
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
 
     def barrier():
         torch.cuda.synchronize()
