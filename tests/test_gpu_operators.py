@@ -103,6 +103,24 @@ def test_a_row_does_not_depend_on_the_row_count(ops, k, n):
     close(ops.gemm_int8(a, w, s, bias=bias), want)
 
 
+def test_ragged_shapes_through_every_form_of_the_tensor_core_gemm(ops):
+    """N not a multiple of the 128-column slab, K not a multiple of the 64-row stage (so the last K ranges of the
+    split are short or empty), row counts that end inside a tile: 32-row, 64-row and whole-K forms against the oracle,
+    and the first rows of every call bit-identical."""
+    k, n = 520, 1008            # rows of W must stay 16-byte aligned for the tensor-core path (TMA)
+    a, w, s, bias = int8_case(torch, 1500, n, k, seed=9)
+    want = orc.gemm_int8(a.cpu().numpy(), w.cpu().numpy(), s.cpu().numpy(), bias.cpu().numpy(), out_fp32=True)
+    first = None
+    for rows in (7, 33, 100, 700, 1500):
+        got = ops.gemm_int8(a[:rows], w, s, bias=bias)
+        close(got, want[:rows])
+        close(ops.gemm_int8(a[:rows], w, s, bias=bias, output_dtype=torch.float32), want[:rows], atol=2e-3, rtol=1e-4)
+        if first is None:
+            first = got
+        else:
+            assert torch.equal(got[:7], first), f"{rows} rows"
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 3072, 768), (8, 768, 3072), (32, 3072, 768), (3, 100, 40)])
 def test_fused_bias_gelu_residual_equals_reference_sequence(ops, ref, m, n, k):
     a, w, s, bias = int8_case(torch, m, n, k, seed=1)
