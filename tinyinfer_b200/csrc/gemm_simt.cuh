@@ -219,15 +219,32 @@ gemv_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
           }
         }
       } else {
-        // Tiles filled by guarded loads (any alignment, any pitch); zero outside the matrix.
+        // Tiles filled by guarded loads (any alignment, any pitch); zero outside the matrix.  A 16-byte piece of a row
+        // that lies wholly inside the matrix is assembled from the five aligned 32-bit words that cover it (funnel
+        // shifts); pieces at the edges, and the last bytes of the buffer, go byte by byte.
         __syncthreads();
-        const WT* w = static_cast<const WT*>(p.w);
-        for (int i = tid; i < kGemvStageRows * BN; i += kGemvThreads) {
-          const int r = i / BN, c = i - r * BN;
-          const int kidx = kc0 + kk0 + r, col = n0 + c;
-          WT v = WT(0);
-          if (kidx < kc1 && col < p.n) v = w[size_t(kidx) * p.ldw + col];
-          reinterpret_cast<WT*>(stages)[r * BN + c] = v;
+        const uint8_t* wb = static_cast<const uint8_t*>(p.w);
+        const size_t w_bytes = (size_t(p.k - 1) * p.ldw + p.n) * sizeof(WT);      // one past the last byte of the matrix
+        for (int i = tid; i < kGemvStageRows * 8; i += kGemvThreads) {
+          const int r = i >> 3, piece = i & 7;
+          const int kidx = kc0 + kk0 + r, col = n0 + piece * (16 / int(sizeof(WT)));
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (kidx < kc1 && col < p.n) {
+            const size_t off = (size_t(kidx) * p.ldw + col) * sizeof(WT);
+            const uintptr_t addr = reinterpret_cast<uintptr_t>(wb) + off;
+            if (col + 16 / int(sizeof(WT)) <= p.n && off + 20 <= w_bytes && (off >= 3 || (addr & 3) == 0)) {
+              const uint32_t* words = reinterpret_cast<const uint32_t*>(addr & ~uintptr_t(3));
+              const uint32_t shift = uint32_t(addr & 3) * 8;
+              const uint32_t w0 = words[0], w1 = words[1], w2 = words[2], w3 = words[3], w4 = shift ? words[4] : 0u;
+              v.x = __funnelshift_r(w0, w1, shift); v.y = __funnelshift_r(w1, w2, shift);
+              v.z = __funnelshift_r(w2, w3, shift); v.w = __funnelshift_r(w3, w4, shift);
+            } else {
+              uint8_t* bytes = reinterpret_cast<uint8_t*>(&v);
+              const int valid = min(16, (p.n - col) * int(sizeof(WT)));
+              for (int e = 0; e < valid; ++e) bytes[e] = wb[off + e];
+            }
+          }
+          *reinterpret_cast<uint4*>(stages + r * 128 + piece * 16) = v;
         }
         __syncthreads();
         gemv_consume_stage<WT, MT>(stages, a_smem, kGemvAChunk, kk0, s, acc);
