@@ -119,7 +119,9 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
 // grid = (N / 128 slabs, k splits [cluster y], M / NMMA tiles), block = 320.
 // LN: LayerNorm prologue compiled in (0 = none, 1 = every CTA prepares the rows itself, 2 = rows shared out over the
 // K-split cluster); separate instantiations keep the plain GEMM free of that code.
-template <int NMMA, int LN = 0, bool LEAN = false>
+// DIRECT: the weight matrix cannot be described by a tensor map (row pitch not a multiple of 16 bytes); warp 0 then
+// fills the raw stages itself with realigned loads instead of issuing TMA copies.
+template <int NMMA, int LN = 0, bool LEAN = false, bool DIRECT = false>
 __global__ void __launch_bounds__(kTcThreads, LEAN ? 3 : NMMA <= 64 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   trace_event(kTrGemmTc, 0);
@@ -154,7 +156,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   if (p.early_trigger) pdl_launch_dependents();
   if (tid == 0) {
     s_failed = 0;
-    tma_prefetch_desc(&w_map);
+    if (!DIRECT) tma_prefetch_desc(&w_map);
     for (int s = 0; s < kTcRawStages; ++s) { mbar_init(&raw_full[s], 1); mbar_init(&raw_empty[s], kTcDequantThreads / 32); }
     for (int s = 0; s < kOps; ++s) { mbar_init(&op_full[s], kTcDequantThreads / 32); mbar_init(&op_empty[s], 1); }
     mbar_init(acc_ready, 1);
@@ -181,7 +183,56 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == 0 && DIRECT) {
+    // ------------------------------------------------------------ producer without TMA: the whole warp copies a stage
+    // (64 rows x 128 bytes = 512 pieces of 16 bytes, 16 per lane) from wherever the rows start; a piece wholly inside
+    // the matrix is assembled from the five aligned words that cover it, edge pieces go byte by byte; zero outside.
+    const uint8_t* wb = static_cast<const uint8_t*>(p.w);
+    const size_t w_bytes = size_t(p.k - 1) * p.ldw + p.n;       // one past the last byte of the matrix
+    bool ok = true;
+    for (int i = 0; i < stages && ok; ++i) {
+      const int slot = i % kTcRawStages;
+      const uint32_t phase = uint32_t(i / kTcRawStages) & 1u;
+      ok = mbar_wait(&raw_empty[slot], phase ^ 1u, kStatusPipeTimeout);
+      if (!ok) break;
+      uint8_t* tile = raw + slot * kTcRawBytes;
+#pragma unroll 1
+      for (int batch = 0; batch < 2; ++batch) {
+        uint4 v[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int piece = lane + 32 * (batch * 8 + q), r = piece >> 3, ch = piece & 7;
+          const int kidx = k_begin + i * kTcStageK + r, col = n0 + ch * 16;
+          v[q] = make_uint4(0, 0, 0, 0);
+          if (kidx < k_end && col < p.n) {
+            const size_t off = size_t(kidx) * p.ldw + col;
+            const uintptr_t addr = reinterpret_cast<uintptr_t>(wb) + off;
+            if (col + 16 <= p.n && off + 20 <= w_bytes && (off >= 3 || (addr & 3) == 0)) {
+              const uint32_t* words = reinterpret_cast<const uint32_t*>(addr & ~uintptr_t(3));
+              const uint32_t shift = uint32_t(addr & 3) * 8;
+              const uint32_t w0 = words[0], w1 = words[1], w2 = words[2], w3 = words[3], w4 = shift ? words[4] : 0u;
+              v[q].x = __funnelshift_r(w0, w1, shift); v[q].y = __funnelshift_r(w1, w2, shift);
+              v[q].z = __funnelshift_r(w2, w3, shift); v[q].w = __funnelshift_r(w3, w4, shift);
+            } else {
+              const int valid = min(16, p.n - col);
+              uint32_t wd[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+              for (int e = 0; e < 16; ++e) if (e < valid) wd[e >> 2] |= uint32_t(wb[off + e]) << ((e & 3) * 8);
+              v[q] = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+            }
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int piece = lane + 32 * (batch * 8 + q), r = piece >> 3, ch = piece & 7;
+          *reinterpret_cast<uint4*>(tile + r * 128 + ((ch ^ (r & 7)) << 4)) = v[q];      // the layout TMA's 128-byte swizzle gives
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&raw_full[slot]);
+    }
+    if (!ok && lane == 0) s_failed = 1;
+  } else if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (weights only: no dependency wait)
     if (lane == 0) {
       bool ok = true;

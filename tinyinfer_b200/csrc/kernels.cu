@@ -115,11 +115,11 @@ cudaError_t launch_gemv_mt(int mt, const CUtensorMap& map, const GemvArgs& args,
   }
 }
 
-template <int NMMA, int LN = 0, bool LEAN = false>
+template <int NMMA, int LN = 0, bool LEAN = false, bool DIRECT = false>
 cudaError_t launch_tc(const CUtensorMap& map, const GemvArgs& args, dim3 grid, const LaunchOpts& o) {
-  const cudaError_t ready = allow_smem(gemm_tc_kernel<NMMA, LN, LEAN>, TcSmem<NMMA, LEAN>::kBytes);
+  const cudaError_t ready = allow_smem(gemm_tc_kernel<NMMA, LN, LEAN, DIRECT>, TcSmem<NMMA, LEAN>::kBytes);
   if (ready != cudaSuccess) return ready;
-  return launch(gemm_tc_kernel<NMMA, LN, LEAN>, grid, dim3(kTcThreads), TcSmem<NMMA, LEAN>::kBytes, o, int(grid.y), map, args);
+  return launch(gemm_tc_kernel<NMMA, LN, LEAN, DIRECT>, grid, dim3(kTcThreads), TcSmem<NMMA, LEAN>::kBytes, o, int(grid.y), map, args);
 }
 
 int env_int(const char* name, int fallback) {
@@ -153,7 +153,11 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
     a.w_slab_rows = c.w_slab_rows;
     const bool mapped = c.w_slab_rows ? make_map_2d(&map, c.w, true, slab_count * uint64_t(c.w_slab_rows), 128, 128, 128, uint32_t(kTcStageK), true)
                                       : make_map_2d(&map, c.w, true, uint64_t(c.k), uint64_t(c.n), uint64_t(c.ldw), 128, uint32_t(kTcStageK), true);
-    if (mapped) {
+    // No tensor map (row pitch or base not 16-byte aligned, e.g. N = 50257): the same kernel with a producer warp that
+    // copies the weight tiles itself.
+    // (measured on 768x50257: faster than the SIMT kernel from about 16 rows on)
+    const bool direct = !mapped && !c.w_slab_rows && !c.ln_gamma && c.m >= 16;
+    if (mapped || direct) {
       const int slabs = (c.n + 127) / 128;
       // K split chosen from the matrix alone (never from M): the summation grouping of an output
       // element is then the same for every batch size and batch composition.
@@ -183,13 +187,21 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
         a.serial_chunks = splits;
         const dim3 grid(slabs, 1, (c.m + wide - 1) / wide);
         switch (wide) {
-          case 64: return launch_tc<64>(map, a, grid, o);
-          case 128: return launch_tc<128>(map, a, grid, o);
-          default: return launch_tc<256>(map, a, grid, o);
+          case 64: return direct ? launch_tc<64, 0, false, true>(map, a, grid, o) : launch_tc<64>(map, a, grid, o);
+          case 128: return direct ? launch_tc<128, 0, false, true>(map, a, grid, o) : launch_tc<128>(map, a, grid, o);
+          default: return direct ? launch_tc<256, 0, false, true>(map, a, grid, o) : launch_tc<256>(map, a, grid, o);
         }
       }
       const dim3 grid(slabs, splits, m_tiles);
       static const int lean_ok = env_int("TINYINFER_B200_TC_LEAN", 1);           // measurement aid
+      if (direct) {
+        switch (nmma) {
+          case 32: return launch_tc<32, 0, false, true>(map, a, grid, o);
+          case 64: return launch_tc<64, 0, false, true>(map, a, grid, o);
+          case 128: return launch_tc<128, 0, false, true>(map, a, grid, o);
+          default: return launch_tc<256, 0, false, true>(map, a, grid, o);
+        }
+      }
       switch (nmma) {
         case 32:
           // no K split, many slabs (vocabulary projection): the lean layout runs three CTAs per SM
