@@ -249,6 +249,43 @@ def test_admissions_folded_into_a_decode_step_change_nothing(model):
     model.reset_all()
 
 
+def test_step_by_step_decoding_with_speculative_continuation(model):
+    """A caller that feeds the model's outputs back through forward() gets, after a few steps, its next step launched
+    ahead of the call.  Tokens must equal greedy()'s, also when the caller stops continuing (another token, another
+    slot set, a reset) while a speculative step is in flight."""
+    rng = np.random.default_rng(44)
+    prompts = [rng.integers(0, 50257, int(n)).tolist() for n in (20, 75, 140)]
+    model.reset_all()
+    want = model.greedy(prompts, 40)["tokens"]
+    model.reset_all()
+    ids = model.forward([0, 1, 2], prompts, return_logits=False)["next_tokens"]
+    got = [[t] for t in ids]
+    for _ in range(39):
+        ids = model.forward([0, 1, 2], [[t] for t in ids], return_logits=False)["next_tokens"]
+        for row, t in zip(got, ids):
+            row.append(t)
+    assert got == want
+    assert model.lengths()[:3] == [len(p) + 39 for p in prompts]
+    # break the pattern: request 1 continues with another token than the one predicted; compare with a fresh context
+    forced = [ids[0], (ids[1] + 1) % 50257, ids[2]]
+    after = logits_of(model.forward([0, 1, 2], [[t] for t in forced]))
+    model.reset_all()
+    model.forward([5, 6, 7], [p + g[:39] for p, g in zip(prompts, want)], return_logits=False)
+    fresh = logits_of(model.forward([5, 6, 7], [[t] for t in forced]))
+    # (the fresh context was prefilled in one pass, the other grew token by token: same values up to summation order)
+    assert torch.allclose(after, fresh, atol=5e-3, rtol=0) and torch.equal(after.argmax(-1), fresh.argmax(-1))
+    # continue long enough to arm again, then reset one slot and reuse it while a speculative step may be in flight
+    ids = [int(t) for t in fresh.argmax(-1)]
+    for _ in range(12):
+        ids = model.forward([5, 6, 7], [[t] for t in ids], return_logits=False)["next_tokens"]
+    model.reset(6)
+    again = logits_of(model.forward([6], [prompts[0]]))
+    model.reset_all()
+    alone = logits_of(model.forward([0], [prompts[0]]))
+    assert torch.equal(again, alone)
+    model.reset_all()
+
+
 def test_medium_shape_matches_cpu_oracle(tmp_path_factory):
     """GPT-2 medium shape (24 layers, 16 heads, hidden 1024), seed 3: the reference runtime cannot load it
     (compile-time 12/12/768), so the operator-composed CPU oracle is the reference here."""

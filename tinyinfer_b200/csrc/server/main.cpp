@@ -590,6 +590,9 @@ void Server::run() {
 }  // namespace
 
 int main(int argc, char** argv) {
+  // The workers' batches change composition from pass to pass: the runtime's speculative continuation of
+  // step-by-step decoding (see llm_runtime.cpp) would mostly launch steps nobody asks for.
+  setenv("TINYINFER_B200_SPECULATE", "0", 0);
   std::signal(SIGINT, on_signal);
   std::signal(SIGTERM, on_signal);
   try {
