@@ -98,6 +98,7 @@ struct ti_llm_model {
     cudaSetDevice(opt.device);
     if (stream) cudaStreamSynchronize(stream);
     for (const StepGraph& g : graphs) cudaGraphExecDestroy(g.exec);
+    for (cudaEvent_t e : spec_done) if (e) cudaEventDestroy(e);
     for (void* p : owned) cudaFree(p);
     for (void* p : pinned) cudaFreeHost(p);
     if (stream) cudaStreamDestroy(stream);
@@ -194,7 +195,7 @@ struct ti_llm_model {
     d_next = dev<int32_t>(size_t(opt.max_batch)); h_next = host<int32_t>(size_t(opt.max_batch));
     d_seg = dev<int32_t>(size_t(5) * opt.max_batch); h_seg = host<int32_t>(size_t(5) * opt.max_batch);
     d_step = dev<int32_t>(1);
-    h_spec = host<int32_t>(size_t(opt.max_batch));
+    for (int i = 0; i < 2; ++i) { h_spec[i] = host<int32_t>(size_t(opt.max_batch) + 1); ck(cudaEventCreateWithFlags(&spec_done[i], cudaEventDisableTiming)); }
     if (const char* v = std::getenv("TINYINFER_B200_SPECULATE")) { spec_after = std::atoi(v); speculate = spec_after > 0; }
     d_argmax = dev<uint8_t>(size_t(12) * opt.max_batch + 8);
     ck(cudaMemsetAsync(d_argmax, 0, size_t(12) * opt.max_batch + 8, stream));
@@ -227,7 +228,7 @@ struct ti_llm_model {
     }
   }
   void release(int slot) {
-    spec.armed = false;
+    spec.armed = false; spec.inflight = 0;
     for (int i = page_count[size_t(slot)] - 1; i >= 0; --i) free_pages.push_back(table[size_t(slot) * pages_per_slot + i]);
     page_count[size_t(slot)] = 0; lengths[size_t(slot)] = 0;
   }
@@ -315,7 +316,7 @@ struct ti_llm_model {
   // packed request after request.  LayerNorm_f of each request's last row lands in `last`, or of
   // every row in `norm` when all_rows is set.
   void transform(const std::vector<int32_t>& ss, const std::vector<int32_t>& packed, const std::vector<int32_t>& lens, bool all_rows) {
-    spec.armed = false; spec.streak = 0;
+    spec.armed = false; spec.inflight = 0; spec.streak = 0;
     const int batch = int(ss.size()), H = shape.hidden;
     Meta m{}; m.batch = batch;
     for (int b = 0; b < batch; ++b) { m.rows += lens[size_t(b)]; m.max_q = std::max(m.max_q, lens[size_t(b)]); m.singles += lens[size_t(b)] == 1; }
@@ -370,14 +371,18 @@ struct ti_llm_model {
   // (same slots, the ids just returned, untouched lengths) and collects the result.  A call that asks for anything else
   // simply finds an extra step ahead of its work in the stream; that step's writes (a K/V row at a position the next
   // real step rewrites, device-side counters that every call re-uploads) are never read.
+  // Up to two such steps are in flight: when a call finds its step under way it first launches the one after it and
+  // only then waits (on an event, not on the stream) for its own ids, so the GPU never idles between steps.
   struct Speculation {
-    bool armed = false;
+    bool armed = false;                               // inflight > 0 and nothing but matching forward calls since
+    int inflight = 0, oldest = 0;                     // steps launched ahead, and which buffer the oldest one fills
     int streak = 0;                                   // consecutive calls that continued the previous one
     std::vector<int32_t> slots, last_out, lens_expected;
   } spec;
   bool speculate = true;
   int spec_after = 8, host_step = 0;                  // host_step mirrors the device step counter
-  int32_t* h_spec = nullptr;                          // pinned: the speculative step's ids
+  int32_t* h_spec[2] = {nullptr, nullptr};            // pinned: ids of a step launched ahead, then the device status word
+  cudaEvent_t spec_done[2] = {nullptr, nullptr};
   int32_t *d_seg = nullptr, *h_seg = nullptr, *d_step = nullptr, *d_log = nullptr, *h_log = nullptr;
   bool use_graph = true, use_pdl = true;
   // Early release of the next launch (see LaunchOpts::early_trigger).  After a GEMM comes a kernel whose reads ahead
@@ -429,7 +434,7 @@ struct ti_llm_model {
   void enqueue_segment(const std::vector<int32_t>& ss, const int32_t* first, int steps, cudaEvent_t before = nullptr,
                        cudaEvent_t after = nullptr) {
     const int batch = int(ss.size()), mb = opt.max_batch;
-    spec.armed = false; host_step = steps;
+    spec.armed = false; spec.inflight = 0; host_step = steps;
     int max_kv = 0;
     for (int b = 0; b < batch; ++b) {
       const int s = ss[size_t(b)], start = lengths[size_t(s)];
@@ -478,13 +483,41 @@ struct ti_llm_model {
     if (single && greedy) {
       // One token per request and the argmax wanted: one device-resident step -- already under way if this call
       // continues the previous one exactly (see Speculation).
-      bool hit = spec.armed && !out && ss == spec.slots && packed == spec.last_out;
+      bool hit = spec.armed && spec.inflight > 0 && !out && ss == spec.slots && packed == spec.last_out;
       for (int b = 0; hit && b < batch; ++b) hit = lengths[size_t(s[b])] == spec.lens_expected[size_t(b)];
       const bool continues = !out && ss == spec.slots && packed == spec.last_out;
+      // One more step ahead of the `spec.inflight` already launched, if there is room for the position it writes.
+      auto launch_ahead = [&]() -> bool {
+        if (!speculate || !use_graph || spec.inflight >= 2 || host_step + 1 >= opt.capacity) return false;
+        int max_kv = 0;
+        for (int b = 0; b < batch; ++b) {
+          const int rows = lengths[size_t(s[b])] + spec.inflight + 1;
+          if (rows > opt.capacity) return false;
+          max_kv = std::max(max_kv, rows);
+        }
+        for (int b = 0; b < batch; ++b) reserve(s[b], lengths[size_t(s[b])] + spec.inflight + 1);
+        upload_table();
+        int chunks = 1;
+        while (chunks * kDecodeChunk < max_kv) chunks *= 2;
+        const int buffer = (spec.oldest + spec.inflight) & 1;
+        ck(cudaGraphLaunch(step_graph(batch, chunks), stream));
+        ck(cudaMemcpyAsync(h_spec[buffer], d_log + size_t(host_step) * batch, size_t(batch) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+        ck(cudaMemcpyAsync(h_spec[buffer] + opt.max_batch, d_status_addr, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
+        ck(cudaEventRecord(spec_done[buffer], stream));
+        ++host_step; ++spec.inflight;
+        return true;
+      };
       if (hit) {
-        spec.armed = false;
-        finish();
-        std::memcpy(greedy, h_spec, size_t(batch) * sizeof(int32_t));
+        launch_ahead();                                                    // the step after the one this call collects
+        const int buffer = spec.oldest;
+        ck(cudaEventSynchronize(spec_done[buffer]));
+        if (h_spec[buffer][opt.max_batch]) {
+          const unsigned int code = unsigned(h_spec[buffer][opt.max_batch]);
+          unsigned int ignored = 0; tib::read_device_status(stream, &ignored);
+          throw GpuFailure("device wait timed out (status " + std::to_string(code) + ")");
+        }
+        std::memcpy(greedy, h_spec[buffer], size_t(batch) * sizeof(int32_t));
+        spec.oldest ^= 1; --spec.inflight;
         count_pass(); count_head(true);
       } else {
         enqueue_segment(ss, packed.data(), 1);
@@ -496,21 +529,12 @@ struct ti_llm_model {
       spec.streak = continues ? spec.streak + 1 : 0;
       spec.slots = ss; spec.last_out.assign(greedy, greedy + batch);
       for (int b = 0; b < batch; ++b) lengths[size_t(s[b])] += 1;
-      // Launch the step after this one now if the caller has been continuing long enough and there is room for it.
-      bool arm = speculate && use_graph && !out && spec.streak >= spec_after && host_step + 1 < opt.capacity;
-      for (int b = 0; arm && b < batch; ++b) arm = lengths[size_t(s[b])] + 1 <= opt.capacity;
-      if (arm) {
-        int max_kv = 0;
-        for (int b = 0; b < batch; ++b) { reserve(s[b], lengths[size_t(s[b])] + 1); max_kv = std::max(max_kv, lengths[size_t(s[b])] + 1); }
-        upload_table();
-        int chunks = 1;
-        while (chunks * kDecodeChunk < max_kv) chunks *= 2;
-        ck(cudaGraphLaunch(step_graph(batch, chunks), stream));
-        ck(cudaMemcpyAsync(h_spec, d_log + size_t(host_step) * batch, size_t(batch) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
-        ++host_step;
+      // Keep (or start) a step ahead if the caller has been continuing long enough.
+      if (!out && spec.streak >= spec_after && spec.inflight == 0) launch_ahead();
+      spec.armed = spec.inflight > 0;
+      if (spec.armed) {
         spec.lens_expected.resize(size_t(batch));
         for (int b = 0; b < batch; ++b) spec.lens_expected[size_t(b)] = lengths[size_t(s[b])];
-        spec.armed = true;
       }
       return;
     } else {
