@@ -139,7 +139,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
            *acc_ready = op_empty + kOps;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_ready + 1);
   static_assert((2 * kTcRawStages + 2 * kOps + 2) * 8 <= 128, "barrier block");
-  static_assert(LN == 0 || kOps * L::kOpBBytes >= 8 * 768 * 2, "LayerNorm row strips live in the B-operand ring");
+  static_assert(LN == 0 || LN == 3 || kOps * L::kOpBBytes >= 8 * 768 * 2, "LayerNorm row strips live in the B-operand ring");
   __shared__ int s_failed;
 
   cg::cluster_group cluster = cg::this_cluster();
@@ -168,7 +168,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   // other's statistics slots, which must be initialised first.  (Written as PTX: with cooperative_groups' cluster
   // sync in this place every launch of the kernel, also those that skip it, measured half a microsecond slower.)
   static_assert(LN == 0 || NMMA <= 64, "LayerNorm prologue: tiles of 32 or 64 rows");
-  constexpr bool fuse_ln = LN != 0, ln_shared = LN == 2;
+  // LN == 3: shared mode for rows of up to 1024 values (the dispatcher checks that the strips of the rows one CTA
+  // prepares fit the B-operand ring); a separate instantiation, so that the 768-wide kernels stay as they are.
+  constexpr bool fuse_ln = LN != 0, ln_shared = LN >= 2;
+  constexpr int kLnCols = LN == 3 ? 1024 : 768, kLnHeld = kLnCols / 256;
   // (mean, 1/sigma) of every row of the tile.  Shared mode: written by the CTA that prepares the row as one 8-byte store
   // through distributed shared memory and awaited by polling 1/sigma, whose initial bit pattern (a NaN that rsqrtf never
   // returns) means "not here yet": one remote store per row and CTA, no separate signal.
@@ -323,7 +326,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     };
     // Optional LayerNorm of the rows (decode: NMMA == 32, K <= 768): statistics per row are computed once per CTA
     // right after the dependency resolves, with the same summation order as layernorm_kernel, and applied here.
-    __shared__ __half s_gamma[LN != 0 && NMMA <= 64 ? 768 : 1], s_beta[LN != 0 && NMMA <= 64 ? 768 : 1];
+    __shared__ __half s_gamma[LN != 0 && NMMA <= 64 ? kLnCols : 1], s_beta[LN != 0 && NMMA <= 64 ? kLnCols : 1];
     if (fuse_ln)
       for (int c = k_begin + t; c < k_end; c += kTcDequantThreads) { s_gamma[c - k_begin] = p.ln_gamma[c]; s_beta[c - k_begin] = p.ln_beta[c]; }
     auto store_a = [&](const uint4 (&src)[kPer], int oslot, int i) {
@@ -367,7 +370,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     // The first stages' rows are requested together (one round trip instead of one per stage).  With the shared
     // LayerNorm prologue they go out before it (its barrier wait covers their latency); with the local one after
     // it (measured: ahead of it they delay the row loads the statistics wait for).
-    constexpr bool kFetchFirst = LN == 2;
+    constexpr bool kFetchFirst = LN >= 2;
     if constexpr (kAhead > 1 && kFetchFirst) {
 #pragma unroll
       for (int d = 0; d < kAhead; ++d) fetch_a(a_ring[d], d);
@@ -386,15 +389,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
           float mean = 0.f, inv = 0.f;
           const int row = m0 + first + local;
           if (row < p.m) {                                    // warp-uniform
-            uint4 held[3];
+            uint4 held[kLnHeld];
 #pragma unroll
-            for (int u = 0; u < 3; ++u) {
+            for (int u = 0; u < kLnHeld; ++u) {
               const int c = lane + 32 * u;
               held[u] = make_uint4(0, 0, 0, 0);
               if (c < chunks) held[u] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + c * 8);
             }
 #pragma unroll
-            for (int u = 0; u < 3; ++u) { const int c = lane + 32 * u; if (c < chunks) *reinterpret_cast<uint4*>(strip + c * 8) = held[u]; }
+            for (int u = 0; u < kLnHeld; ++u) { const int c = lane + 32 * u; if (c < chunks) *reinterpret_cast<uint4*>(strip + c * 8) = held[u]; }
             __syncwarp();
             if (TIB_SLOT_GRID && t == 0) trace_slot(5);
             row_stats(strip, p.k, p.ln_eps, mean, inv);

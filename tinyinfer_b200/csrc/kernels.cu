@@ -172,7 +172,10 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       static const int tile64_rows = env_int("TINYINFER_B200_TC_TILE64_ROWS", 1024);   // measurement aid
       const int nmma = c.m <= 32 ? 32 : (c.m <= 64 || (splits > 1 && c.m <= tile64_rows)) ? 64 : c.m <= 128 ? 128 : 256;
       if (c.ln_gamma) {
-        if (nmma > 64 || (nmma == 64 && splits == 1) || c.k > 768 || c.lda != c.k) return cudaErrorNotSupported;
+        if (nmma > 64 || (nmma == 64 && splits == 1) || c.k > 1024 || c.lda != c.k) return cudaErrorNotSupported;
+        // rows wider than 768: shared mode only, and the strips of the rows one CTA prepares must fit the B-operand ring
+        if (c.k > 768 && (splits == 1 || size_t(nmma / splits) * c.k * 2 > size_t(nmma == 64 ? 2 : kTcOpStages) * nmma * kTcStageK * 2))
+          return cudaErrorNotSupported;
         a.ln_gamma = static_cast<const __half*>(c.ln_gamma); a.ln_beta = static_cast<const __half*>(c.ln_beta); a.ln_eps = c.ln_eps;
       }
       const int m_tiles = (c.m + nmma - 1) / nmma;
@@ -208,8 +211,9 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
           if (!c.ln_gamma && splits == 1 && lean_ok && slabs > 2 * sm_count()) return launch_tc<32, 0, true>(map, a, grid, o);
           if (!c.ln_gamma) return launch_tc<32>(map, a, grid, o);
           // up to 8 rows every CTA prepares them itself; more are shared out over the K-split cluster
+          if (c.k > 768) return launch_tc<32, 3>(map, a, grid, o);
           return splits > 1 && c.m > 8 ? launch_tc<32, 2>(map, a, grid, o) : launch_tc<32, 1>(map, a, grid, o);
-        case 64: return c.ln_gamma ? launch_tc<64, 2>(map, a, grid, o) : launch_tc<64>(map, a, grid, o);
+        case 64: return !c.ln_gamma ? launch_tc<64>(map, a, grid, o) : c.k > 768 ? launch_tc<64, 3>(map, a, grid, o) : launch_tc<64, 2>(map, a, grid, o);
         case 128: return launch_tc<128>(map, a, grid, o);
         default: return launch_tc<256>(map, a, grid, o);
       }

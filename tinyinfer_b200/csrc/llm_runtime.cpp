@@ -208,7 +208,7 @@ struct ti_llm_model {
     if (const char* v = std::getenv("TINYINFER_B200_MIXED_ATTN")) mixed_attention = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_TRIGGER")) attn_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_WHOLE")) attn_whole = std::atoi(v) != 0;
-    fuse_ln = int8 && shape.hidden <= 768;
+    fuse_ln = int8 && shape.hidden <= 1024;
     if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) { fuse_ln_rows = std::min(1024, std::atoi(v)); fuse_ln = fuse_ln && fuse_ln_rows > 0; }
     h_status = host<unsigned int>(1); *h_status = 0;
     d_score_tokens = dev<int32_t>(size_t(opt.capacity)); d_score_mask = dev<uint8_t>(size_t(opt.capacity));
@@ -394,7 +394,7 @@ struct ti_llm_model {
   bool attn_trigger = true;                      // the projection GEMM after attention prefetches its weights meanwhile
   bool attn_early = true, attn_whole = true;     // decode attention: reads ahead of the dependency wait; one CTA per (request, head)
   int fuse_ln_rows = 128;            // largest row count whose LayerNorms run inside the consuming GEMM
-  bool fuse_ln = false;             // int8 weights and rows of at most 768 values: LayerNorm runs inside the consuming GEMM
+  bool fuse_ln = false;             // int8 weights and rows of at most 1024 values: LayerNorm runs inside the consuming GEMM
 
   int32_t* seg(int field) const { return d_seg + size_t(field) * opt.max_batch; }
 
@@ -404,7 +404,7 @@ struct ti_llm_model {
     m.rows = batch; m.batch = batch; m.max_q = 1; m.max_kv = max_kv;
     run_layers(m);
     tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
-    if (fuse_ln && batch <= std::min(fuse_ln_rows, 8)) gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b);
+    if (fuse_ln && shape.hidden <= 768 && batch <= std::min(fuse_ln_rows, 8)) gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b);
     else {
       ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, last, batch, shape.hidden, 1e-5f, ln_opts()));
       gemm(last, head, logits, batch, true, nullptr, false);
