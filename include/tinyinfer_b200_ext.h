@@ -22,6 +22,16 @@ int ti_b200_gemm_i8_fused(const uint16_t* a, const int8_t* b, const float* scale
                           const uint16_t* residual, void* y, int m, int n, int k, int output_dtype, int gelu,
                           uintptr_t stream, int device);
 
+/* Per-output-channel symmetric INT8 quantiser on the GPU: w[rows, columns] fp16 -> q[rows, columns] int8 and
+ * scales[columns] fp32, bit-identical to ti_host_quantize_f16 (backend/host_codec.cpp, specification
+ * llm/quantization.py): scale = float(double(max|w|) / 127.0) (1 for an all-zero column),
+ * q = clip(round_half_even(double(w) / double(scale)), -127, 127).  All pointers are device memory and must not
+ * overlap; nonfinite (device int32, required) is set to 1 when an input is NaN or infinite -- the host
+ * codec rejects such input, here q and scales are then unspecified.  Asynchronous on `stream`.  The reference has
+ * no device-side quantiser; its exporter quantises on the host. */
+int ti_b200_quantize_f16(const uint16_t* w, int64_t rows, int64_t columns, int8_t* q, float* scales,
+                         int32_t* nonfinite, uintptr_t stream, int device);
+
 /* Decode attention (one query per request) reading k/v[B,H,K,64] in place:
  * q[B,H,1,64] -> y[B,H,1,64], keys 0..kv_lengths[b]-1 visible.  Equals reference
  * ti_v2_attention_f16 (backend/runtime_v2.cu:82-90) with q_len 1 and

@@ -202,6 +202,15 @@ int ti_b200_gemm_i8_fused(const uint16_t* a, const int8_t* b, const float* scale
   return run_gemm(a, b, scales, bias, y, residual, gelu, m, n, k, dtype, true, stream);
 }
 
+int ti_b200_quantize_f16(const uint16_t* w, int64_t rows, int64_t columns, int8_t* q, float* scales, int32_t* nonfinite,
+                         uintptr_t stream, int device) {
+  int st = enter(device); if (st) return st;
+  if (rows < 1 || columns < 1 || columns > 0x7fffffff || rows > (int64_t(1) << 40) / columns || !aligned_to(w, 2) || !q ||
+      !aligned_to(scales, 4) || !aligned_to(nonfinite, 4))
+    return fail(TI_V2_INVALID_ARGUMENT, "invalid quantiser arguments (w FP16[rows,columns], q INT8, scales FP32[columns], flag INT32)");
+  return cuda_result(tib::quantize_i8(w, rows, int(columns), q, scales, nonfinite, reinterpret_cast<cudaStream_t>(stream)));
+}
+
 int64_t ti_b200_attention_decode_scratch_floats(int batch, int heads, int kv_len, int chunk) {
   if (batch <= 0 || heads <= 0 || kv_len <= 0 || chunk <= 0) return -1;
   return int64_t(batch) * heads * tib::decode_chunks(kv_len, chunk) * (64 + 2);

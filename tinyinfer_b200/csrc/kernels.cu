@@ -244,6 +244,24 @@ cudaError_t retile_i8(const int8_t* src, long long ld, int k, int n, int8_t* dst
   return cudaGetLastError();
 }
 
+cudaError_t quantize_i8(const void* w, long long rows, int cols, int8_t* q, float* scales, int* flag, cudaStream_t stream) {
+  if (!w || !q || !scales || !flag || rows < 1 || cols < 1) return cudaErrorInvalidValue;
+  cudaError_t st = cudaMemsetAsync(scales, 0, size_t(cols) * sizeof(float), stream);
+  if (st == cudaSuccess) st = cudaMemsetAsync(flag, 0, sizeof(int), stream);
+  if (st != cudaSuccess) return st;
+  const int col_blocks = (cols + 127) / 128;
+  // enough row groups to fill the device without more atomics than needed
+  const int groups = int(std::max<long long>(1, std::min<long long>(rows, (4LL * sm_count() + col_blocks - 1) / col_blocks)));
+  const int rows_per_block = int((rows + groups - 1) / groups);
+  const auto* half = static_cast<const __half*>(w);
+  auto* bits = reinterpret_cast<unsigned int*>(scales);
+  quant_absmax_kernel<<<dim3(col_blocks, unsigned((rows + rows_per_block - 1) / rows_per_block)), 128, 0, stream>>>(half, rows, cols, bits, flag, rows_per_block);
+  quant_scales_kernel<<<col_blocks, 128, 0, stream>>>(bits, scales, cols);
+  const long long elements = rows * cols;
+  quant_apply_kernel<<<unsigned((elements + 255) / 256), 256, 0, stream>>>(half, scales, q, elements, cols);
+  return cudaGetLastError();
+}
+
 cudaError_t sgemm(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
   sgemm_kernel<<<dim3((n + 15) / 16, (m + 15) / 16), 256, 0, stream>>>(a, b, c, m, n, k);
   return cudaGetLastError();

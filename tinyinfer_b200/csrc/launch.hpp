@@ -57,6 +57,10 @@ TIB_EXPORT cudaError_t gemm(const GemmCall& call, const LaunchOpts& opts);
 // dst[slab][row][c] = row < k && slab*128+c < n ? src[row*ld + slab*128+c] : 0, for ceil(n/128) slabs of slab_rows rows.
 TIB_EXPORT cudaError_t retile_i8(const int8_t* src, long long ld, int k, int n, int8_t* dst, int slab_rows, cudaStream_t stream);
 
+// Per-output-channel symmetric INT8 quantisation of w[rows][cols] (fp16) on the device, bit-identical to the host codec.
+// scales[cols] doubles as the scratch of the column maxima; flag (device int, zeroed here) becomes 1 for non-finite input.
+TIB_EXPORT cudaError_t quantize_i8(const void* w, long long rows, int cols, int8_t* q, float* scales, int* flag, cudaStream_t stream);
+
 TIB_EXPORT cudaError_t sgemm(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream);
 
 // Packed-tensor attention of the operator ABI: q[B,H,Q,D], k/v[B,H,K,D].

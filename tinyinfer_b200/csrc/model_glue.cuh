@@ -116,6 +116,37 @@ __global__ void retile_i8_kernel(const int8_t* src, long long ld, int k, int n, 
   *reinterpret_cast<uint4*>(dst + i * 16) = *reinterpret_cast<const uint4*>(v);
 }
 
+// ---- per-output-channel symmetric INT8 quantiser (reference specification: llm/quantization.py, backend/host_codec.cpp:
+// scale[c] = float(double(max_r |w[r][c]|) / 127.0), or 1 for an all-zero column; q = clip(round_half_even(double(w) /
+// double(scale)), -127, 127)).  Three launches: column maxima (bit patterns of non-negative floats order like unsigned
+// integers, so atomicMax on them is exact), scales, quantisation in fp64 exactly as the host codec computes it.
+// flag: set to 1 when an input is NaN or infinite (the host codec rejects such input; here the outputs are then unspecified).
+__global__ void quant_absmax_kernel(const __half* w, long long rows, int cols, unsigned int* max_bits, int* flag, int rows_per_block) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const long long r0 = (long long)blockIdx.y * rows_per_block, r1 = min(rows, r0 + rows_per_block);
+  if (c >= cols) return;
+  float best = 0.f; bool bad = false;
+  for (long long r = r0; r < r1; ++r) {
+    const float a = fabsf(h2f(w[r * cols + c]));
+    bad = bad || !(a <= 65504.f);                                // NaN or infinity
+    best = fmaxf(best, a);
+  }
+  atomicMax(max_bits + c, __float_as_uint(best));
+  if (bad) *flag = 1;
+}
+__global__ void quant_scales_kernel(const unsigned int* max_bits, float* scales, int cols) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= cols) return;
+  const float m = __uint_as_float(max_bits[c]);
+  scales[c] = m != 0.f ? float(double(m) / 127.0) : 1.0f;       // max_bits and scales may be the same buffer
+}
+__global__ void quant_apply_kernel(const __half* w, const float* scales, int8_t* q, long long elements, int cols) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= elements) return;
+  const double v = rint(double(h2f(w[i])) / double(scales[i % cols]));      // rint: to nearest, ties to even
+  q[i] = int8_t(v < -127.0 ? -127.0 : v > 127.0 ? 127.0 : v);
+}
+
 // End of a device-resident decode step: every request moves one position on.
 __global__ void advance_kernel(int32_t* row_pos, int32_t* kv_lengths, int32_t* step, int batch) {
   trace_event(kTrAdvance, 0);
