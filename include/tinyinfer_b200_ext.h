@@ -79,6 +79,14 @@ int ti_b200_artifact_check(const char* manifest_path, int32_t* layers, int32_t* 
 struct ti_llm_model;
 int ti_b200_llm_decode_steps(struct ti_llm_model* model, const int32_t* slots, const int32_t* first_tokens,
                              int32_t batch, int32_t steps, int32_t* out_tokens, double* device_ms);
+
+/* Exported by libtinyinfer_llm.so.  Selects how a greedy decode step of up to 32 requests runs: 1 = one persistent
+ * kernel per step (one CTA per SM, activations handed between CTAs as tagged words; the default wherever the model
+ * shape and the device allow it), 0 = one launch per operation replayed as a CUDA graph, -1 = leave as is.  Both plans
+ * produce the same bits.  active (nullable) receives the plan in force afterwards.  The reference has one plan only
+ * (a launch per operation, llm/src/runtime.cu:135-168).  Returns a ti_llm_status; TI_LLM_INVALID when plan 1 is
+ * asked for a shape it does not cover. */
+int ti_b200_llm_decode_plan(struct ti_llm_model* model, int32_t select, int32_t* active);
 #ifdef __cplusplus
 }
 #endif

@@ -49,17 +49,19 @@ def tensor_shapes(arch):
     return shapes
 
 
-def synthetic_tensors(arch, seed, std=0.02):
-    """Seeded random fp16 tensors: matrices N(0, std), biases 0, LayerNorm gamma 1 / beta 0."""
+def synthetic_tensors(arch, seed, std=0.02, dense=False):
+    """Seeded random fp16 tensors: matrices N(0, std), biases 0, LayerNorm gamma 1 / beta 0 (the benchmark
+    configurations' initialisation).  dense=True also randomises the vectors (biases N(0, 0.05), gamma 1 + N(0, 0.1),
+    beta N(0, 0.05)) so that a test sees every bias / LayerNorm parameter take part."""
     rng = np.random.default_rng(seed)
     out = {}
     for name, shape in tensor_shapes(arch).items():
         if len(shape) == 2:
             out[name] = rng.standard_normal(shape, dtype=np.float32).__mul__(np.float32(std)).astype(np.float16)
         elif ".ln_" in name and name.endswith(".weight"):
-            out[name] = np.ones(shape, np.float16)
+            out[name] = (1 + 0.1 * rng.standard_normal(shape, dtype=np.float32)).astype(np.float16) if dense else np.ones(shape, np.float16)
         else:
-            out[name] = np.zeros(shape, np.float16)
+            out[name] = (0.05 * rng.standard_normal(shape, dtype=np.float32)).astype(np.float16) if dense else np.zeros(shape, np.float16)
     return out
 
 
@@ -111,20 +113,22 @@ def write_artifact(directory, tensors, arch, precision="int8", codec=None):
     return manifest
 
 
-def write_synthetic(directory, arch=None, seed=0, precision="int8", std=0.02):
+def write_synthetic(directory, arch=None, seed=0, precision="int8", std=0.02, dense=False):
     """Seeded random model of `arch` (default GPT-2 small) -> artifact directory; returns the manifest path."""
     arch = dict(arch or GPT2_SMALL)
     directory = Path(directory)
     manifest_path = directory / "manifest.json"
     if manifest_path.exists() and (directory / "weights.bin").exists():
         existing = json.loads(manifest_path.read_text())
-        if existing.get("architecture") == arch and existing.get("precision") == precision and existing.get("synthetic_seed") == seed:
+        if existing.get("architecture") == arch and existing.get("precision") == precision and existing.get("synthetic_seed") == seed and \
+                bool(existing.get("synthetic_dense")) == dense:
             return manifest_path
         (directory / "weights.bin").unlink()
     elif (directory / "weights.bin").exists():
         (directory / "weights.bin").unlink()
-    manifest = write_artifact(directory, synthetic_tensors(arch, seed, std), arch, precision)
+    manifest = write_artifact(directory, synthetic_tensors(arch, seed, std, dense), arch, precision)
     manifest["synthetic_seed"] = seed
+    manifest["synthetic_dense"] = dense
     manifest_path.write_text(json.dumps(manifest, indent=1, allow_nan=False) + "\n", encoding="ascii")
     return manifest_path
 

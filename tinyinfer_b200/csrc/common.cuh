@@ -20,6 +20,8 @@ enum DeviceStatus : unsigned int {
   kStatusTmaTimeout = 1,       // a weight tile never arrived
   kStatusMmaTimeout = 2,       // a tcgen05.commit never arrived
   kStatusPipeTimeout = 3,      // a consumer never released a stage
+  kStatusFlagTimeout = 4,      // persistent decode step: a tagged word of another CTA never arrived
+  kStatusNoToken = 5,          // greedy argmax found no comparable logit in a row (all NaN)
 };
 
 // One status word per device for the library (defined in kernels.cu, the only device translation unit).

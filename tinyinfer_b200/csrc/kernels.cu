@@ -15,6 +15,7 @@ namespace tib { __device__ unsigned int g_device_status = 0; }
 #define TIB_STATUS_DEFINED
 #include "attention.cuh"
 #include "common.cuh"
+#include "decode_step.cuh"
 #include "elementwise.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
@@ -122,9 +123,32 @@ cudaError_t launch_tc(const CUtensorMap& map, const GemvArgs& args, dim3 grid, c
   return launch(gemm_tc_kernel<NMMA, LN, LEAN, DIRECT>, grid, dim3(kTcThreads), TcSmem<NMMA, LEAN>::kBytes, o, int(grid.y), map, args);
 }
 
+// Measurement aids of development builds (-DTIB_DEV_KNOBS): an environment variable may override a dispatch
+// threshold.  Release builds ignore the environment here.
 int env_int(const char* name, int fallback) {
+#ifdef TIB_DEV_KNOBS
   const char* v = std::getenv(name);
   return v ? std::atoi(v) : fallback;
+#else
+  (void)name;
+  return fallback;
+#endif
+}
+
+// K split of the tensor-core GEMM, chosen from the matrix alone (never from M): the summation grouping of an
+// output element is then the same for every batch size and batch composition.  Few stages per CTA matter more
+// than full tiles: a stage costs about a microsecond of serial latency.
+int tc_splits(int n, int k) {
+  const int slabs = (n + 127) / 128;
+  int splits = 1;
+  while (splits < 8 && slabs * splits < sm_count() && (k + splits * 2 - 1) / (splits * 2) >= kTcStageK) splits *= 2;
+  static const int forced_splits = env_int("TINYINFER_B200_TC_SPLITS", 0);
+  if (forced_splits > 0) splits = forced_splits;
+  return splits;
+}
+int tc_chunk(int k, int splits) {
+  const int chunk = (k + splits - 1) / splits;
+  return (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
 }
 
 }  // namespace
@@ -159,13 +183,7 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
     const bool direct = !mapped && !c.w_slab_rows && !c.ln_gamma && c.m >= 16;
     if (mapped || direct) {
       const int slabs = (c.n + 127) / 128;
-      // K split chosen from the matrix alone (never from M): the summation grouping of an output
-      // element is then the same for every batch size and batch composition.
-      int splits = 1;
-      // Few stages per CTA matter more than full tiles: a stage costs about a microsecond of serial latency.
-      while (splits < 8 && slabs * splits < sm_count() && (c.k + splits * 2 - 1) / (splits * 2) >= kTcStageK) splits *= 2;
-      static const int forced_splits = env_int("TINYINFER_B200_TC_SPLITS", 0);      // measurement aid
-      if (forced_splits > 0) splits = forced_splits;
+      const int splits = tc_splits(c.n, c.k);
       // 33..1024 rows of a K-split matrix: tiles of 64 rows in the decode kernel's form (push reduction, LayerNorm
       // prologue, two CTAs per SM): a 64-request step still runs every GEMM as one wave of clusters, and a single prompt's
       // prefill (measured at 150..900 rows) is faster than with 256-row tiles reduced by remote reads.
@@ -179,8 +197,7 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
         a.ln_gamma = static_cast<const __half*>(c.ln_gamma); a.ln_beta = static_cast<const __half*>(c.ln_beta); a.ln_eps = c.ln_eps;
       }
       const int m_tiles = (c.m + nmma - 1) / nmma;
-      int chunk = (c.k + splits - 1) / splits;
-      a.k_chunk = (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
+      a.k_chunk = tc_chunk(c.k, splits);
       // Many rows (prefill): a cluster reduction of 64..256-row partial tiles would cost more than the MMAs.  One CTA
       // then walks the whole K with one TMEM accumulator per K range and adds them in range order -- the very sums
       // of the split launch, so a row's result still does not depend on how many rows share the call.
@@ -403,6 +420,45 @@ cudaError_t nll_rows(const float* logits, long long pitch, int rows, int cols, c
 cudaError_t sum_f64(const double* values, double* out, int length, cudaStream_t stream) {
   sum_f64_kernel<<<1, 256, 0, stream>>>(values, out, length);
   return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------- persistent decode step
+int step_k_chunk(int n, int k) { return tc_chunk(k, tc_splits(n, k)); }
+
+const char* step_unsupported(const StepPlan& p) {
+  if (p.hidden < 128 || p.hidden % 128 || p.hidden > kStepMaxHidden) return "hidden size must be a multiple of 128 up to 1024";
+  if (p.heads * 64 != p.hidden) return "heads of 64 values";
+  if (p.ff % 128 || p.layers < 1 || p.layers > 60) return "layer shape";
+  const int chunks[4] = {p.chunk_qkv, p.chunk_proj, p.chunk_fc, p.chunk_head};
+  for (int c : chunks)
+    if (c < kTcStageK || c % kTcStageK || p.hidden % c || p.hidden / c > kStepMaxRanges) return "K split of a hidden-wide GEMM";
+  if (p.chunk_proj2 < kTcStageK || p.chunk_proj2 % kTcStageK || p.chunk_proj2 > kStepMaxHidden || p.ff % p.chunk_proj2 ||
+      p.ranks_proj2 != p.ff / p.chunk_proj2 || p.ranks_proj2 > kStepMaxRanges)
+    return "K split of the MLP projection";
+  if (step_role_ctas(p) > sm_count() || sm_count() < kStepRows) return "more GEMM items per layer than SMs";
+  if (p.first_helper != step_role_ctas(p) || p.head_slabs != (p.vocab + 127) / 128) return "inconsistent plan";
+  return nullptr;
+}
+
+cudaError_t make_tile_map(const void* arena, long long rows, TileMap* out) {
+  CUtensorMap map; std::memset(&map, 0, sizeof map);
+  static_assert(sizeof(CUtensorMap) == sizeof(TileMap), "tensor map size");
+  if (!make_map_2d(&map, arena, true, uint64_t(rows), 128, 128, 128, uint32_t(kTcStageK), true)) return cudaErrorInvalidValue;
+  std::memcpy(out, &map, sizeof map);
+  return cudaSuccess;
+}
+
+cudaError_t decode_step(const StepPlan& plan, const TileMap& tiles, cudaStream_t stream) {
+  if (plan.batch < 1 || plan.batch > kStepRows || step_unsupported(plan)) return cudaErrorInvalidValue;
+  const cudaError_t ready = allow_smem(decode_step_kernel, StepSmem::kBytes);
+  if (ready != cudaSuccess) return ready;
+  CUtensorMap map; std::memcpy(&map, &tiles, sizeof map);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(unsigned(sm_count())); cfg.blockDim = dim3(kStepThreads); cfg.dynamicSmemBytes = StepSmem::kBytes; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative; attr[0].val.cooperative = 1;      // every CTA resident, or the launch fails
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, decode_step_kernel, map, plan);
 }
 
 #ifdef TIB_TRACE

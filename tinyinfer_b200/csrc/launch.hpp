@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "step_plan.hpp"
+
 #if defined(__GNUC__)
 #define TIB_EXPORT __attribute__((visibility("default")))
 #else
@@ -116,6 +118,16 @@ TIB_EXPORT cudaError_t advance(int32_t* row_pos, int32_t* kv_lengths, int32_t* s
 TIB_EXPORT cudaError_t nll_rows(const float* logits, long long pitch, int rows, int cols, const int32_t* tokens,
                                 const uint8_t* mask, double* loss, int first_position, cudaStream_t stream);
 TIB_EXPORT cudaError_t sum_f64(const double* values, double* out, int length, cudaStream_t stream);
+
+// Persistent decode step (decode_step.cuh): one cooperative launch runs embedding .. argmax for plan.batch <= 32
+// requests and advances the device-resident state.  step_k_chunk: K rows per range of the K split a [K,N] matrix has
+// in gemm() (the plan must use the same ranges: results are then bit-identical to the launch-per-GEMM step).
+// step_unsupported: null, or why this shape / device cannot run the persistent step.
+struct alignas(64) TileMap { unsigned char bytes[128]; };      // tensor map over the tile arena ([rows][128] int8)
+TIB_EXPORT int step_k_chunk(int n, int k);
+TIB_EXPORT const char* step_unsupported(const StepPlan& plan);
+TIB_EXPORT cudaError_t make_tile_map(const void* arena, long long rows, TileMap* out);
+TIB_EXPORT cudaError_t decode_step(const StepPlan& plan, const TileMap& tiles, cudaStream_t stream);
 
 // Reads and clears the device status word set by a kernel whose bounded wait ran out
 // (0 = healthy).  Synchronises `stream` first.

@@ -55,6 +55,7 @@ struct Linear {
   const void* w = nullptr; const float* scales = nullptr; const void* bias = nullptr;
   int k = 0, n = 0; long long ldw = 0;
   int slab_rows = 0;                 // > 0: w holds slab-major tiles [ceil(n/128)][slab_rows][128] (int8 only)
+  long long tile_row0 = 0;           // first row of those tiles inside the model's tile arena ([rows][128] int8)
 };
 struct Block { const void *ln1_g, *ln1_b, *ln2_g, *ln2_b; Linear qkv, proj, fc, proj2; };
 
@@ -77,6 +78,7 @@ struct ti_llm_model {
   float* logits = nullptr;
   float *att_acc = nullptr, *att_ml = nullptr;
   int* att_counters = nullptr;                   // per (request, head) tickets of the decode attention, zero between launches
+  int8_t* tile_arena = nullptr; long long tile_rows = 0;   // slab-major tiles of every INT8 matrix
   // KV pool
   void *k_pool = nullptr, *v_pool = nullptr;
   int pages_per_slot = 0;
@@ -155,16 +157,23 @@ struct ti_llm_model {
     // one contiguous run of K x 128 bytes, so each TMA stage is a single 8 KB block of device memory
     // instead of 64 separate 128-byte pieces one matrix row apart.
     bool tiled = int8 && H % 8 == 0;
+#ifdef TIB_DEV_KNOBS
     if (const char* v = std::getenv("TINYINFER_B200_TILED")) tiled = tiled && std::atoi(v) != 0;
+#endif
     if (tiled) {
-      auto retile = [&](Linear& l) {
-        const int rows = (l.k + 63) / 64 * 64;
-        int8_t* tiles = dev<int8_t>(size_t((l.n + 127) / 128) * rows * 128);
-        ck(tib::retile_i8(static_cast<const int8_t*>(l.w), l.ldw, l.k, l.n, tiles, rows, stream));
-        l.w = tiles; l.slab_rows = rows;
-      };
-      for (Block& b : blocks) { retile(b.qkv); retile(b.proj); retile(b.fc); retile(b.proj2); }
-      retile(head);
+      // One arena holds the tiles of every matrix, so that a single tensor map (and a row offset per matrix) reaches
+      // all of them: the persistent decode step streams the weights of a whole step through it.
+      std::vector<Linear*> all;
+      for (Block& b : blocks) { all.push_back(&b.qkv); all.push_back(&b.proj); all.push_back(&b.fc); all.push_back(&b.proj2); }
+      all.push_back(&head);
+      long long rows_total = 0;
+      for (Linear* l : all) { l->slab_rows = (l->k + 63) / 64 * 64; l->tile_row0 = rows_total; rows_total += (long long)((l->n + 127) / 128) * l->slab_rows; }
+      tile_arena = dev<int8_t>(size_t(rows_total) * 128); tile_rows = rows_total;
+      for (Linear* l : all) {
+        int8_t* tiles = tile_arena + size_t(l->tile_row0) * 128;
+        ck(tib::retile_i8(static_cast<const int8_t*>(l->w), l->ldw, l->k, l->n, tiles, l->slab_rows, stream));
+        l->w = tiles;
+      }
     }
 
     max_rows = size_t(opt.max_batch) * opt.capacity;
@@ -202,18 +211,88 @@ struct ti_llm_model {
     d_log = dev<int32_t>(size_t(opt.capacity) * opt.max_batch); h_log = host<int32_t>(size_t(opt.capacity) * opt.max_batch);
     if (const char* v = std::getenv("TINYINFER_B200_GRAPH")) use_graph = std::atoi(v) != 0;   // debugging aids: 0 = plain launches
     if (const char* v = std::getenv("TINYINFER_B200_PDL")) use_pdl = std::atoi(v) != 0;
+#ifdef TIB_DEV_KNOBS                 // measurement aids of development builds
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_EARLY")) attn_early = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_LN_TRIGGER")) ln_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_GEMM_TRIGGER")) gemm_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_MIXED_ATTN")) mixed_attention = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_TRIGGER")) attn_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_WHOLE")) attn_whole = std::atoi(v) != 0;
-    fuse_ln = int8 && shape.hidden <= 1024;
-    if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) { fuse_ln_rows = std::min(1024, std::atoi(v)); fuse_ln = fuse_ln && fuse_ln_rows > 0; }
+    if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) fuse_ln_rows = std::min(1024, std::atoi(v));
+#endif
+    fuse_ln = int8 && shape.hidden <= 1024 && fuse_ln_rows > 0;
     h_status = host<unsigned int>(1); *h_status = 0;
     d_score_tokens = dev<int32_t>(size_t(opt.capacity)); d_score_mask = dev<uint8_t>(size_t(opt.capacity));
     d_loss = dev<double>(size_t(opt.capacity)); d_loss_sum = dev<double>(1);
+    build_step_plan();
     ck(cudaStreamSynchronize(stream));
+  }
+
+  // ------------------------------------------------------------ persistent decode step
+  // One launch per greedy step for up to 32 requests (decode_step.cuh) instead of the 65-kernel graph; same bits.
+  tib::StepPlan plan; tib::TileMap plan_tiles; bool plan_ready = false, use_persistent = true;
+  uint8_t* plan_words = nullptr; size_t plan_words_bytes = 0;     // the tagged exchange buffers, one allocation
+  uint64_t plan_epochs = 0;                                        // launches since the buffers were last cleared
+
+  void build_step_plan() {
+    if (!tile_arena || shape.hidden % 128 || shape.hidden > tib::kStepMaxHidden) return;
+    const int H = shape.hidden, F = 4 * H;
+    tib::StepPlan p;
+    p.hidden = H; p.heads = shape.heads; p.layers = shape.layers; p.ff = F; p.vocab = shape.vocab;
+    p.chunk_qkv = tib::step_k_chunk(3 * H, H); p.chunk_proj = tib::step_k_chunk(H, H); p.chunk_fc = tib::step_k_chunk(F, H);
+    p.chunk_proj2 = tib::step_k_chunk(H, F); p.chunk_head = tib::step_k_chunk(shape.vocab, H);
+    p.ranks_proj2 = p.chunk_proj2 > 0 ? F / p.chunk_proj2 : 0;
+    p.head_slabs = (shape.vocab + 127) / 128; p.first_helper = tib::step_role_ctas(p);
+    if (tib::step_unsupported(p)) return;
+    auto lin = [](const Linear& l) { tib::StepLinear s; s.tile_row0 = int(l.tile_row0); s.slab_rows = l.slab_rows; s.scales = l.scales; s.bias = static_cast<const __half*>(l.bias); return s; };
+    if (tile_rows > 0x7fffffffLL) return;
+    std::vector<tib::StepLayer> layers(blocks.size());
+    for (size_t l = 0; l < blocks.size(); ++l) {
+      const Block& b = blocks[l];
+      layers[l].qkv = lin(b.qkv); layers[l].proj = lin(b.proj); layers[l].fc = lin(b.fc); layers[l].proj2 = lin(b.proj2);
+      layers[l].ln1_g = static_cast<const __half*>(b.ln1_g); layers[l].ln1_b = static_cast<const __half*>(b.ln1_b);
+      layers[l].ln2_g = static_cast<const __half*>(b.ln2_g); layers[l].ln2_b = static_cast<const __half*>(b.ln2_b);
+    }
+    tib::StepLayer* d_layers = dev<tib::StepLayer>(layers.size());
+    ck(cudaMemcpyAsync(d_layers, layers.data(), layers.size() * sizeof(tib::StepLayer), cudaMemcpyHostToDevice, stream));
+    ck(cudaStreamSynchronize(stream));                             // `layers` is a local
+    p.layer = d_layers; p.head = lin(head);
+    p.lnf_g = static_cast<const __half*>(lnf_g); p.lnf_b = static_cast<const __half*>(lnf_b);
+    p.wte = static_cast<const __half*>(wte); p.wpe = static_cast<const __half*>(wpe);
+    p.ids = seg(0); p.row_pos = seg(2); p.kv_len = seg(3); p.slots = seg(4); p.step = d_step; p.log = d_log;
+    p.table = d_table; p.table_pitch = pages_per_slot;
+    p.k_pool = static_cast<__half*>(k_pool); p.v_pool = static_cast<__half*>(v_pool);
+    // tagged buffers: 8 bytes per pair of fp16 values (or per fp32 partial sum), 32 rows each
+    const size_t R = tib::kStepRows;
+    const size_t words_x = R * H / 2, words_qkv = R * 3 * H / 2, words_act = R * F / 2, words_part = size_t(H / 128) * p.ranks_proj2 * R * 128;
+    const size_t total = 3 * words_x + words_qkv + words_act + words_part;
+    plan_words_bytes = total * 8 + 16 + R * 8;
+    plan_words = dev<uint8_t>(plan_words_bytes);
+    ck(cudaMemsetAsync(plan_words, 0, plan_words_bytes, stream));
+    auto* w = reinterpret_cast<unsigned long long*>(plan_words);
+    p.xf = w; w += words_x; p.attnf = w; w += words_x; p.resf = w; w += words_x; p.qkvf = w; w += words_qkv; p.actf = w; w += words_act;
+    p.partf = w; w += words_part;
+    p.best = w; w += R;
+    p.sync = reinterpret_cast<unsigned int*>(w);
+    const unsigned int first_epoch[2] = {1u, 0u};
+    ck(cudaMemcpyAsync(p.sync, first_epoch, sizeof first_epoch, cudaMemcpyHostToDevice, stream));
+    ck(cudaStreamSynchronize(stream));
+    p.logits_pitch = vpitch;
+    ck(tib::make_tile_map(tile_arena, tile_rows, &plan_tiles));
+    plan = p; plan_ready = true; plan_epochs = 0;
+    if (const char* v = std::getenv("TINYINFER_B200_PERSISTENT")) use_persistent = std::atoi(v) != 0;
+  }
+  bool persistent_step(int batch) const { return plan_ready && use_persistent && int8 && batch <= tib::kStepRows; }
+  void launch_persistent(int batch, bool want_logits) {
+    if (++plan_epochs > (1ull << 25)) {                            // long before the 32-bit tags could repeat
+      ck(cudaMemsetAsync(plan_words, 0, plan_words_bytes, stream));
+      const unsigned int first_epoch[2] = {1u, 0u};
+      ck(cudaMemcpyAsync(plan.sync, first_epoch, sizeof first_epoch, cudaMemcpyHostToDevice, stream));   // pageable source: copied before the call returns
+      plan_epochs = 1;
+    }
+    tib::StepPlan p = plan;
+    p.batch = batch; p.logits = want_logits ? logits : nullptr;
+    ck(tib::decode_step(p, plan_tiles, stream));
   }
   static int tib_page_tokens() { return 32; }
 
@@ -432,7 +511,7 @@ struct ti_llm_model {
   // `lengths` (the caller advances them) but reserves the pages the steps will write.
   // before / after, when given, are recorded around the steps on the model's stream.
   void enqueue_segment(const std::vector<int32_t>& ss, const int32_t* first, int steps, cudaEvent_t before = nullptr,
-                       cudaEvent_t after = nullptr) {
+                       cudaEvent_t after = nullptr, bool want_logits = false) {
     const int batch = int(ss.size()), mb = opt.max_batch;
     spec.armed = false; spec.inflight = 0; host_step = steps;
     int max_kv = 0;
@@ -448,7 +527,9 @@ struct ti_llm_model {
     int chunks = 1;
     while (chunks * kDecodeChunk < max_kv) chunks *= 2;            // few distinct graphs: 1, 2, 4, 8 chunks
     if (before) ck(cudaEventRecord(before, stream));
-    if (use_graph) {
+    if (persistent_step(batch)) {
+      for (int i = 0; i < steps; ++i) launch_persistent(batch, want_logits);
+    } else if (use_graph) {
       cudaGraphExec_t exec = step_graph(batch, chunks);
       for (int i = 0; i < steps; ++i) ck(cudaGraphLaunch(exec, stream));
     } else {
@@ -488,7 +569,7 @@ struct ti_llm_model {
       const bool continues = !out && ss == spec.slots && packed == spec.last_out;
       // One more step ahead of the `spec.inflight` already launched, if there is room for the position it writes.
       auto launch_ahead = [&]() -> bool {
-        if (!speculate || !use_graph || spec.inflight >= 2 || host_step + 1 >= opt.capacity) return false;
+        if (!speculate || !(use_graph || persistent_step(batch)) || spec.inflight >= 2 || host_step + 1 >= opt.capacity) return false;
         int max_kv = 0;
         for (int b = 0; b < batch; ++b) {
           const int rows = lengths[size_t(s[b])] + spec.inflight + 1;
@@ -500,7 +581,8 @@ struct ti_llm_model {
         int chunks = 1;
         while (chunks * kDecodeChunk < max_kv) chunks *= 2;
         const int buffer = (spec.oldest + spec.inflight) & 1;
-        ck(cudaGraphLaunch(step_graph(batch, chunks), stream));
+        if (persistent_step(batch)) launch_persistent(batch, false);
+        else ck(cudaGraphLaunch(step_graph(batch, chunks), stream));
         ck(cudaMemcpyAsync(h_spec[buffer], d_log + size_t(host_step) * batch, size_t(batch) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
         ck(cudaMemcpyAsync(h_spec[buffer] + opt.max_batch, d_status_addr, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
         ck(cudaEventRecord(spec_done[buffer], stream));
@@ -520,7 +602,7 @@ struct ti_llm_model {
         spec.oldest ^= 1; --spec.inflight;
         count_pass(); count_head(true);
       } else {
-        enqueue_segment(ss, packed.data(), 1);
+        enqueue_segment(ss, packed.data(), 1, nullptr, nullptr, out != nullptr);
         if (out) ck(cudaMemcpy2DAsync(out, size_t(shape.vocab) * 4, logits, size_t(vpitch) * 4, size_t(shape.vocab) * 4, size_t(batch),
                                       cudaMemcpyDeviceToHost, stream));
         finish();
@@ -740,6 +822,20 @@ int ti_b200_llm_decode_steps(ti_llm_model* m, const int32_t* slots, const int32_
     cudaEventDestroy(before); cudaEventDestroy(after);
     if (out_tokens) std::memcpy(out_tokens, m->h_log, size_t(steps) * batch * sizeof(int32_t));
     for (int i = 0; i < batch; ++i) m->lengths[size_t(slots[i])] += steps;
+  });
+}
+
+// Declared in include/tinyinfer_b200_ext.h: which plan runs a greedy decode step of up to 32 requests.
+int ti_b200_llm_decode_plan(ti_llm_model* m, int32_t select, int32_t* active) {
+  return guarded(m, [&] {
+    if (select < -1 || select > 1) throw InvalidInput("decode plan: -1 (query), 0 (one launch per operation) or 1 (persistent step)");
+    if (select == 1 && !m->plan_ready) throw InvalidInput("the persistent decode step does not support this model shape or device");
+    if (select >= 0) {
+      ck(cudaStreamSynchronize(m->stream));
+      m->spec.armed = false; m->spec.inflight = 0; m->spec.streak = 0;
+      m->use_persistent = select == 1;
+    }
+    if (active) *active = m->plan_ready && m->use_persistent ? 1 : 0;
   });
 }
 
