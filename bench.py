@@ -17,12 +17,16 @@ Printed JSON (one line, rank 0):
   e2e        tokens/s through the per-step reference-facing call ti_llm_forward_batch: every step
              copies the step's ids + metadata from pinned host memory to the GPU and reads the
              step's next-token ids back to the host
-  roofline   achieved HBM GB/s of the dominant kernel (timed alone, same shapes, CUDA events) and of
-             the whole step against the measured copy bandwidth of this pool's B200s
+  roofline   the dominant kernel -- the persistent decode step, one launch per step: algorithmic weight + KV
+             bytes of a step over the mean launch duration (CUDA events over the timed region) against the
+             measured copy bandwidth of this pool's B200s
+  config0    the batch-1 configuration (32-token prompt, 63 decode steps) the HBM-roofline target is stated on
   cpu_baseline  the decode sequence composed from the reference's own CPU kernels, timed on the
              host cores for a bounded sample of the same workload
 
---impl reference prints the CPU arm alone in the same format.
+--impl reference times the reference's own runtime (its CUDA kernels compiled unmodified for sm_100a into
+oracle/_ref) on the same workload through the same per-step call; when that build is absent it falls back to the CPU
+composition.  The reference has no CPU GPT-2 runtime of its own.
 """
 from __future__ import annotations
 
@@ -125,18 +129,102 @@ def cpu_arm(steps, warmup, threads=None):
     return result, sample
 
 
-def reference_main(args, rank):
-    if rank != 0:
+def config_block(world):
+    return {"workload": WORKLOAD, "replicas": world, "l2": "inputs larger than L2 (about 0.5 GB of weights + KV per step)",
+            "weights": f"random N(0,0.02), seed {WEIGHT_SEED}"}
+
+
+def physical_cores():
+    """Cores this process may use (the launcher may have set OMP_NUM_THREADS=1, which is not a property of the machine)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def setup_ranks():
+    """(torch, dist or None, local rank): one process per GPU; NCCL only for the barrier and the max / sum of the timing."""
+    import torch
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        # stdout carries the one JSON line: while the communicator comes up (NCCL prints a version banner on file
+        # descriptor 1 when NCCL_DEBUG is set) descriptor 1 points at stderr
+        sys.stdout.flush()
+        saved_stdout = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_stdout, 1)
+            os.close(saved_stdout)
+    return torch, dist, local
+
+
+def reference_main(args, rank, world):
+    """The reference's own runtime on this box: oracle/_ref/libtinyinfer_llm.so is llm/src/runtime.cu and its WMMA
+    kernels compiled unmodified for sm_100a.  Same artifact, same prompts, same per-step call (ti_llm_forward_batch with
+    host ids in, host ids out), one replica per GPU like the other arm.  Without that build: the CPU composition."""
+    ref_lib = ROOT / "oracle" / "_ref" / "libtinyinfer_llm.so"
+    K, W = max(1, args.steps), max(3, args.warmup)
+    line = {"impl": "reference", "metric": "int8_gpt2_decode_tokens_per_s", "unit": "tokens/s", "n_gpus": args.gpus, "steps": K,
+            "warmup": W, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic", "config": config_block(world)}
+    if not ref_lib.exists():
+        if rank != 0:
+            return
+        result, sample = cpu_arm(min(K, 6), 1, threads=physical_cores())
+        line.update({"value": result["tokens_per_s"], "ms_per_step": result["seconds_per_step"] * 1e3, "dtype": "f32", "gpu_launches": 0,
+                     "reference_runs_on": "host CPU cores (oracle/_ref CUDA build absent)",
+                     "cpu_baseline": {"value": result["tokens_per_s"], "unit": "tokens/s", "cores": result["cores"], "kind": result["kind"], "sample": sample},
+                     "e2e": {"value": result["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+        print(json.dumps(line))
         return
-    result, sample = cpu_arm(max(1, args.steps), max(0, args.warmup))
-    line = {"impl": "reference", "metric": "int8_gpt2_decode_tokens_per_s", "value": result["tokens_per_s"], "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": result["seconds_per_step"] * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "runs_on": "host CPU cores"},
-            "cpu_baseline": {"value": result["tokens_per_s"], "unit": "tokens/s", "cores": result["cores"], "kind": result["kind"], "sample": sample},
-            "e2e": {"value": result["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}
-    print(json.dumps(line))
+    torch, dist, local = setup_ranks()
+    from tinyinfer_b200.runtime import NativeModel
+    from tinyinfer_b200 import replicas
+    if rank == 0:
+        artifact_path()
+    if dist:
+        dist.barrier()
+    prompts, slots = workload_prompts(), list(range(BATCH))
+    with NativeModel(ref_lib, artifact_path(), device=local, max_batch=BATCH, cache_slots=BATCH, capacity=1024) as model:
+        t0 = time.perf_counter()
+        ids = model.forward(slots, prompts, return_logits=False)["next_tokens"]
+        ttft_ms = (time.perf_counter() - t0) * 1e3
+        for _ in range(W):
+            ids = model.forward(slots, [[t] for t in ids], return_logits=False)["next_tokens"]
+        steps = min(K, 1024 - max(model.lengths()[:BATCH]) - 1)
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        with ClockSampler(local) as clocks:
+            t0 = time.perf_counter()
+            for _ in range(steps):
+                ids = model.forward(slots, [[t] for t in ids], return_logits=False)["next_tokens"]      # returns after its own stream sync
+            seconds = time.perf_counter() - t0
+        trace = model.trace()
+    _, slowest, value = replicas.job_throughput(BATCH * steps, seconds, dist, "cuda")
+    if rank == 0:
+        line.update({"value": value, "ms_per_step": slowest / steps * 1e3, "steps": steps, "dtype": "f16 activations x int8 weights, f32 accumulate",
+                     "reference_runs_on": "the same B200: reference CUDA runtime (WMMA kernels, about 161 launches per step) compiled for sm_100a",
+                     "prefill_ttft_ms": ttft_ms, "clocks": clocks.summary(), "gpu_launches": 0,
+                     "reference_trace": {k: trace[k] for k in ("forward_calls", "gemm_int8", "attention")},
+                     "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 5 * BATCH * 4, "d2h_bytes_per_step": BATCH * 4,
+                             "api": "ti_llm_forward_batch per step (the timed call itself)"}})
+        if world == 1 and not args.no_cpu:
+            result, sample = cpu_arm(steps=int(os.environ.get("TINYINFER_B200_CPU_STEPS", 4)), warmup=1, threads=physical_cores())
+            line["cpu_baseline"] = {"value": result["tokens_per_s"], "unit": "tokens/s", "cores": result["cores"], "kind": result["kind"], "sample": sample}
+        print(json.dumps(line))
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 # ---------------------------------------------------------------------------- GPU arm
@@ -161,12 +249,6 @@ def graph_seconds(enqueue, launches, replays=10):
     stop.record()
     torch.cuda.synchronize()
     return start.elapsed_time(stop) * 1e-3 / (replays * launches)
-
-
-# DRAM traffic over algorithmic bytes of one launch, from the ncu captures summarised under profiles/
-# (attn_decode_staged_kernel_batch32.md, gemm_tc_kernel_decode_batch32.md); None where no capture exists.
-TRAFFIC_RATIO = {"attention_decode": 27.12 / 26.6, "gemm_int8 qkv": 1.91 / 1.77, "gemm_int8 attn proj": 0.74 / 0.59, "gemm_int8 mlp fc": 2.50 / 2.36, "gemm_int8 mlp proj": 2.66 / 2.36,
-                 "gemm_int8 projections": (0.74 + 2.66) / (0.59 + 2.36)}
 
 
 def kernel_rooflines(cached, peak):
@@ -227,7 +309,7 @@ def kernel_rooflines(cached, peak):
     return out
 
 
-def operator_sweep():
+def operator_sweep(shapes=((768, 2304), (768, 768), (768, 3072), (3072, 768), (768, 50257)), rows_of=(1, 8, 32, 128, 512), gelu_too=True):
     """Standalone INT8-weight GEMV/GEMM sweep (activations fp16 N(0,1), weights uniform int8, fp16-representable
     scales in [1e-3, 2e-2], seed 1): device time per launch from a CUDA graph, achieved GB/s on the algorithmic
     bytes 2MK + KN + 6N + 2MN (4MN for the fp32 vocabulary projection) and TFLOP/s on 2MNK."""
@@ -238,16 +320,16 @@ def operator_sweep():
     peak, _ = peak_hbm()
     torch.manual_seed(1)
     rows = []
-    for k, n in ((768, 2304), (768, 768), (768, 3072), (3072, 768), (768, 50257)):
+    for k, n in shapes:
         sets = max(2, int(260e6 // (k * n)) + 1)                         # distinct weights > L2 per round
         ws = [torch.randint(-127, 128, (k, n), dtype=torch.int8, device="cuda") for _ in range(sets)]
         sc = (torch.rand(n, device="cuda") * 0.019 + 0.001).half().float()
         bias = (torch.randn(n, device="cuda") * 0.1).half()
-        for m in (1, 8, 32, 128, 512):
+        for m in rows_of:
             a = torch.randn((m, k), device="cuda").half()
             fp32 = n == 50257
             y = torch.empty((m, n), device="cuda", dtype=torch.float32 if fp32 else torch.float16)
-            for gelu in ((0,) if fp32 else (0, 1)):
+            for gelu in ((0,) if fp32 or not gelu_too else (0, 1)):
                 def run():
                     for w in ws:
                         if gelu:
@@ -266,27 +348,56 @@ def operator_sweep():
     return rows
 
 
+# DRAM bytes over algorithmic bytes of one launch of the persistent decode step, from the ncu capture summarised in
+# profiles/decode_step_kernel_batch32.md (dram__bytes_read.sum + dram__bytes_write.sum of one launch).
+STEP_TRAFFIC_SOURCE = "profiles/decode_step_kernel_batch32.md"
+STEP_TRAFFIC_RATIO = None
+
+
+def config0_record(model, weights, peak):
+    """Batch 1: 32-token prompt (seed 0), 63 decode steps with the cache at 32..94 positions."""
+    prompt = np.random.default_rng(0).integers(0, 50257, 32).tolist()
+    model.reset_all()
+    first = model.forward([0], [prompt], return_logits=False)["next_tokens"]
+    model.decode_steps([0], first, 63)                                   # warm: same steps, then again timed
+    model.reset_all()
+    first = model.forward([0], [prompt], return_logits=False)["next_tokens"]
+    out = model.decode_steps([0], first, 63)
+    nbytes = sum(step_bytes(weights, [32 + i]) for i in range(63))
+    seconds = out["device_ms"] * 1e-3
+    model.reset_all()
+    return {"workload": "GPT-2 small INT8, batch 1, 32-token prompt, 63 greedy decode steps (cache 32..94 positions), seed 0",
+            "us_per_step": seconds / 63 * 1e6, "tokens_per_s": 63 / seconds, "algorithmic_bytes_per_token": nbytes / 63,
+            "achieved_GBps": nbytes / seconds / 1e9, "frac": nbytes / seconds / 1e9 / peak, "gpu_launches_per_step": 1 if model.decode_plan() == 1 else 65}
+
+
+def config3_record(device):
+    """GPT-2 medium shape (24 layers, hidden 1024, 16 heads; seed 3), batch 8: prefill of 8 x 768 tokens (so that 256
+    generated tokens fit the 1024 learned positions), then 255 decode steps."""
+    from tinyinfer_b200 import artifact
+    from tinyinfer_b200.runtime import NativeModel
+    base = Path(os.environ.get("TINYINFER_B200_CACHE", Path(tempfile.gettempdir()) / "tinyinfer_b200_bench"))
+    manifest = artifact.write_synthetic(base / "gpt2_medium_int8_seed3", artifact.GPT2_MEDIUM, seed=3)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 50257, 768).tolist() for _ in range(8)]
+    with NativeModel(None, manifest, device=device, max_batch=8, cache_slots=8, capacity=1024) as m:
+        m.forward(list(range(8)), [p[:64] for p in prompts], return_logits=False)      # warm-up pass
+        m.reset_all()
+        t0 = time.perf_counter()
+        first = m.forward(list(range(8)), prompts, return_logits=False)["next_tokens"]
+        prefill_s = time.perf_counter() - t0
+        m.decode_steps(list(range(8)), first, 8)
+        out = m.decode_steps(list(range(8)), first, 247)
+        plan = m.decode_plan()
+    linear_flops = 2.0 * 8 * 768 * (24 * (1024 * 3072 + 1024 * 1024 + 2 * 1024 * 4096))
+    return {"workload": "GPT-2 medium shape INT8, batch 8, prefill 8 x 768 tokens then decode, seed 3", "prefill_ms": prefill_s * 1e3,
+            "prefill_tokens_per_s": 8 * 768 / prefill_s, "prefill_linear_TFLOPs": linear_flops / prefill_s / 1e12,
+            "decode_us_per_step": out["device_ms"] * 1e3 / 247, "decode_tokens_per_s": 8 * 247 / (out["device_ms"] * 1e-3),
+            "decode_plan": "persistent step" if plan == 1 else "launch per operation"}
+
+
 def gpu_main(args, rank, world):
-    import torch
-    local = int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        dist = dist_mod
-        # stdout carries the one JSON line: while the communicator comes up (NCCL prints a version banner on file
-        # descriptor 1 when NCCL_DEBUG is set) descriptor 1 points at stderr
-        sys.stdout.flush()
-        saved_stdout = os.dup(1)
-        os.dup2(2, 1)
-        try:
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-            dist.barrier()
-            torch.cuda.synchronize()
-        finally:
-            sys.stdout.flush()
-            os.dup2(saved_stdout, 1)
-            os.close(saved_stdout)
+    torch, dist, local = setup_ranks()
 
     def barrier():
         torch.cuda.synchronize()
@@ -301,7 +412,7 @@ def gpu_main(args, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    from tinyinfer_b200 import artifact
+    from tinyinfer_b200 import artifact, replicas
     from tinyinfer_b200.runtime import NativeModel
     if rank == 0:
         manifest_path = artifact_path()
@@ -315,7 +426,9 @@ def gpu_main(args, rank, world):
     peak, peak_source = peak_hbm()
 
     with NativeModel(None, manifest_path, device=local, max_batch=BATCH, cache_slots=BATCH, capacity=1024) as model:
-        room = 1024 - max(len(p) for p in prompts) - 1
+        if args.plan is not None:
+            model.decode_plan(args.plan)
+        persistent = model.decode_plan() == 1
 
         def prefill():
             model.reset_all()
@@ -323,34 +436,37 @@ def gpu_main(args, rank, world):
             first = model.forward(slots, prompts, return_logits=False)["next_tokens"]
             return first, (time.perf_counter() - t0) * 1e3
 
-        # ---- value: device-resident decode steps ------------------------------------------------
-        first, ttft_ms = prefill()
-        ids = first
-        if W:
-            ids = model.decode_steps(slots, ids, W)["tokens"][-1]
-        cached_at_start = model.lengths()[:BATCH]
-        barrier()
-        device_ms, done, total_bytes = 0.0, 0, 0
-        with ClockSampler(local) as clocks:
-            while done < K:
+        def timed_steps(count, warm):
+            """`count` device-resident steps after `warm` untimed ones: (device ms, algorithmic bytes)."""
+            ids, _ = prefill()
+            if warm:
+                ids = model.decode_steps(slots, ids, warm)["tokens"][-1]
+            barrier()
+            ms, done, nbytes = 0.0, 0, 0
+            while done < count:
                 lengths_now = model.lengths()[:BATCH]
-                n = min(K - done, 1024 - max(lengths_now))
+                n = min(count - done, 1024 - max(lengths_now))
                 if n <= 0:                                  # generation exhausted the context: start over (untimed prefill)
                     ids, _ = prefill()
                     continue
                 out = model.decode_steps(slots, ids, n)
-                device_ms += out["device_ms"]
+                ms += out["device_ms"]
                 ids = out["tokens"][-1]
-                total_bytes += sum(step_bytes(weights, [t + i for t in lengths_now]) for i in range(n))
+                nbytes += sum(step_bytes(weights, [t + i for t in lengths_now]) for i in range(n))
                 done += n
-        barrier()
-        from tinyinfer_b200 import replicas
+            barrier()
+            return ms, nbytes
+
+        # ---- value: device-resident decode steps ------------------------------------------------
+        _, ttft_ms = prefill()
+        with ClockSampler(local) as clocks:
+            device_ms, total_bytes = timed_steps(K, W)
         _, slowest_s, value = replicas.job_throughput(BATCH * K, device_ms * 1e-3, dist, "cuda")    # sum of tokens / slowest rank
         device_ms = slowest_s * 1e3
-        # kernels of one decode step: embed, 12 x (QKV GEMM with LayerNorm prologue and K/V placement, attention, projection
-        # GEMM, FC GEMM with LayerNorm prologue, projection GEMM), final LayerNorm (a prologue of the vocabulary GEMM up to
-        # 8 rows), vocabulary GEMM, argmax, advance
-        launches_per_step = 1 + 12 * 5 + (0 if BATCH <= 8 else 1) + 3
+        # kernels of one decode step.  Persistent plan: one.  Launch-per-operation plan: embed, 12 x (QKV GEMM with LayerNorm
+        # prologue and K/V placement, attention, projection GEMM, FC GEMM with LayerNorm prologue, projection GEMM), final
+        # LayerNorm, vocabulary GEMM, argmax, advance.
+        launches_per_step = 1 if persistent else 1 + 12 * 5 + (0 if BATCH <= 8 else 1) + 3
         step_gbs = total_bytes / (device_ms * 1e-3) / 1e9
 
         if args.quick:
@@ -380,37 +496,49 @@ def gpu_main(args, rank, world):
         e2e["greedy_batch_tokens_per_s"] = world * BATCH * (NEW_TOKENS - 1) / decode_s
         e2e["greedy_batch_ttft_ms"] = gen["ttft_ms"][0]
 
+        extras = {}
+        if rank == 0 and world == 1 and not args.no_extras:
+            extras["config0"] = config0_record(model, weights, peak)
+            if persistent:                                    # the plan this build replaces, same workload, for the record
+                model.decode_plan(0)
+                ms0, _ = timed_steps(min(K, 40), 3)
+                extras["launch_per_operation_plan"] = {"ms_per_step": ms0 / min(K, 40), "gpu_launches_per_step": 65,
+                                                       "config0": config0_record(model, weights, peak)}
+                model.decode_plan(1)
+
     line = {"metric": "int8_gpt2_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": device_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations x int8 weights, f32 accumulate",
-            "data": "synthetic", "config": {"workload": WORKLOAD, "replicas": world, "l2": "inputs larger than L2 (about 0.5 GB of weights + KV per step)",
-                                            "weights": f"random N(0,0.02), seed {WEIGHT_SEED}", "prefill_ttft_ms": ttft_ms},
+            "data": "synthetic", "config": config_block(world), "prefill_ttft_ms": ttft_ms,
             "e2e": e2e, "gpu_launches": launches_per_step * K, "clocks": clocks.summary()}
     if rank == 0:
-        kernels = kernel_rooflines(cached_at_start, peak)
-        # The dominant kernel is chosen the way the ncu launch list counts: by kernel instantiation and grid.  The two
-        # projection GEMMs of a layer (768x768 after attention, 3072x768 after the MLP) are the same kernel with the same
-        # grid (6 slabs x 8 K ranks) and form one entry there: 24 launches per step.
-        ranked = dict(kernels)
-        pa, pm = "gemm_int8 attn proj 768x768 (M=32)", "gemm_int8 mlp proj 3072x768 (M=32)"
-        if pa in ranked and pm in ranked:
-            a, m = ranked.pop(pa), ranked.pop(pm)
-            both = {"seconds": (a["seconds"] + m["seconds"]) / 2, "bytes": (a["bytes"] + m["bytes"]) // 2, "launches_per_step": 24}
-            both["gbs"] = both["bytes"] / both["seconds"] / 1e9
-            both["frac"] = both["gbs"] / peak
-            ranked["gemm_int8 projections: gemm_tc_kernel<32,0> grid (6,8,1), 768x768 and 3072x768 (M=32), mean per launch"] = both
-        top = max(ranked.items(), key=lambda kv: kv[1]["seconds"] * kv[1]["launches_per_step"])
-        ratio = next((r for key, r in TRAFFIC_RATIO.items() if top[0].startswith(key)), None)
-        line["roofline"] = {"kernel": top[0], "bound": "hbm", "achieved": top[1]["gbs"], "peak": peak, "unit": "GB/s", "frac": top[1]["frac"],
-                            "traffic": None if ratio is None else int(top[1]["bytes"] * ratio), "algorithmic_bytes": top[1]["bytes"],
-                            "peak_source": peak_source,
-                            "share_of_step": top[1]["seconds"] * top[1]["launches_per_step"] / (device_ms * 1e-3 / K)}
-        line["step_roofline"] = {"bound": "hbm", "achieved": step_gbs / world if world > 1 else step_gbs, "peak": peak, "unit": "GB/s",
-                                 "frac": (step_gbs / world if world > 1 else step_gbs) / peak,
+        per_gpu_gbs = step_gbs / world if world > 1 else step_gbs
+        if persistent:
+            traffic = None if STEP_TRAFFIC_RATIO is None else int(total_bytes / K * STEP_TRAFFIC_RATIO)
+            line["roofline"] = {"kernel": "decode_step_kernel: one persistent launch per decode step (embedding .. argmax), grid = SM count",
+                                "bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
+                                "traffic": traffic, "traffic_source": STEP_TRAFFIC_SOURCE if traffic is not None else None,
+                                "algorithmic_bytes": total_bytes / K, "launch_us": device_ms / K * 1e3, "peak_source": peak_source,
+                                "share_of_step": 1.0,
+                                "note": "algorithmic weight + KV bytes of a step / mean launch duration, CUDA events on the model's stream"}
+        line["step_roofline"] = {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
                                  "bytes_per_step": total_bytes / K, "note": "algorithmic weight+KV bytes per step / step time, per GPU"}
-        line["kernels"] = {k: {"us": v["seconds"] * 1e6, "GBps": v["gbs"], "frac": v["frac"], "launches_per_step": v["launches_per_step"]}
-                           for k, v in kernels.items()}
+        line.update(extras)
+        if world == 1 and not args.no_extras:
+            cached_at_start = [len(p) + W for p in prompts]
+            kernels = kernel_rooflines(cached_at_start, peak)
+            line["kernels"] = {k: {"us": v["seconds"] * 1e6, "GBps": v["gbs"], "frac": v["frac"], "launches_per_step": v["launches_per_step"]}
+                               for k, v in kernels.items()}
+            line["kernels_note"] = "operator kernels of the launch-per-operation plan, each timed alone (CUDA graph over > L2 buffers)"
+            if not persistent:
+                top = max(kernels.items(), key=lambda kv: kv[1]["seconds"] * kv[1]["launches_per_step"])
+                line["roofline"] = {"kernel": top[0], "bound": "hbm", "achieved": top[1]["gbs"], "peak": peak, "unit": "GB/s", "frac": top[1]["frac"],
+                                    "traffic": None, "algorithmic_bytes": top[1]["bytes"], "peak_source": peak_source,
+                                    "share_of_step": top[1]["seconds"] * top[1]["launches_per_step"] / (device_ms * 1e-3 / K)}
+            line["operator_sweep_768x3072"] = [{k: (round(v, 3) if isinstance(v, float) else v) for k, v in row.items()}
+                                               for row in operator_sweep(((768, 3072),), (1, 32, 128, 512), gelu_too=False)]
+            line["config3"] = config3_record(local)
         if world == 1 and not args.no_cpu:
-            result, sample = cpu_arm(steps=int(os.environ.get("TINYINFER_B200_CPU_STEPS", 6)), warmup=1)
+            result, sample = cpu_arm(steps=int(os.environ.get("TINYINFER_B200_CPU_STEPS", 6)), warmup=1, threads=physical_cores())
             line["cpu_baseline"] = {"value": result["tokens_per_s"], "unit": "tokens/s", "cores": result["cores"], "kind": result["kind"], "sample": sample}
         print(json.dumps(line))
     if dist:
@@ -425,6 +553,8 @@ def main():
     parser.add_argument("--warmup", type=int, default=7)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    parser.add_argument("--no-extras", action="store_true", help="skip config 0, config 3, the operator kernels and the sweep excerpt")
+    parser.add_argument("--plan", type=int, choices=[0, 1], default=None, help="decode plan: 1 persistent step (default where supported), 0 launch per operation")
     parser.add_argument("--quick", action="store_true", help="only the device-resident timed steps (for profilers)")
     parser.add_argument("--sweep", action="store_true", help="operator sweep of the INT8-weight GEMV/GEMM instead of the decode benchmark")
     args = parser.parse_args()
@@ -436,7 +566,7 @@ def main():
             for row in operator_sweep():
                 print(json.dumps(row))
     elif args.impl == "reference":
-        reference_main(args, rank)
+        reference_main(args, rank, world)
     else:
         gpu_main(args, rank, world)
 

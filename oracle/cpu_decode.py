@@ -87,6 +87,12 @@ class CpuDecoder:
         if threads:
             os.environ["OMP_NUM_THREADS"] = str(threads)
         self.k = CpuKernels()
+        if threads:
+            # an OpenMP runtime that is already loaded has read the environment; tell it directly as well
+            try:
+                C.CDLL("libgomp.so.1").omp_set_num_threads(int(threads))
+            except OSError:
+                pass
         self.arch = arch
         self.H, self.nh, self.L = arch["hidden"], arch["heads"], arch["layers"]
         self.d = self.H // self.nh

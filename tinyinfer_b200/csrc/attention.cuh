@@ -37,7 +37,7 @@ struct KvPacked {
   // each other at stride d from tile_offset(ref, b, h).
   __device__ __forceinline__ int tile_ref(int, int t0) const { return t0; }
   __device__ __forceinline__ size_t tile_offset(int ref, int b, int h) const { return offset(b, h, ref); }
-  __device__ __forceinline__ int tile_keys(int t0) const { return min(kPageTokens, kv_len - t0); }   // keys that exist in memory
+  __device__ __forceinline__ int tile_keys(int t0) const { return max(0, min(kPageTokens, kv_len - t0)); }   // keys that exist in memory
 };
 struct KvPaged {
   const __half* k; const __half* v;       // page pools
@@ -166,6 +166,7 @@ struct DecodeArgs {
   int* counters;                                     // optional int [batch][heads], all zero between launches: when given, the
                                                      // last chunk CTA of a (request, head) merges the partials itself
   int batch, heads, chunk, chunks;                   // keys per CTA; grid.x
+  int kv_len;                                        // keys that exist in memory per request: lengths are clamped to it
   // early: kv_lengths, the page table and every key but each request's newest one were written before the
   // kernel ahead of this one started, so they are read before the dependency wait (their latency then hides
   // behind that kernel); the newest key and the query are read after it.
@@ -212,7 +213,7 @@ attn_decode_kernel(const DecodeArgs p, const KV kv) {
 #pragma unroll
   for (int r = 0; r < kRefs; ++r) refs[r] = 0;
   if (p.early) {
-    len = p.kv_lengths[b];
+    len = max(0, min(p.kv_lengths[b], p.kv_len));
     const int end_early = min(len, begin + p.chunk);
 #pragma unroll
     for (int r = 0; r < kRefs; ++r) if (t_first + r * W * 32 < end_early) refs[r] = kv.tile_ref(b, t_first + r * W * 32);
@@ -221,7 +222,7 @@ attn_decode_kernel(const DecodeArgs p, const KV kv) {
   if (p.early_trigger) pdl_launch_dependents();
   pdl_wait();
   trace_event(kTrAttnDecode, 1);
-  if (!p.early) len = p.kv_lengths[b];
+  if (!p.early) len = max(0, min(p.kv_lengths[b], p.kv_len));
   const int end = min(len, begin + p.chunk);
   if (begin >= end && blockIdx.x != 0) return;        // nothing to do for this chunk (uniform per CTA)
 
@@ -388,7 +389,7 @@ attn_decode_staged_kernel(const DecodeArgs p, const KV kv) {
   const int t_first = warp * 32;
   bool requested = false;
   if (p.early) {
-    len = p.kv_lengths[b];
+    len = max(0, min(p.kv_lengths[b], p.kv_len));
     if (lane == 0) {
 #pragma unroll
       for (int r = 0; r < kRefs; ++r) if (t_first + r * W * 32 < len) refs[r] = kv.tile_ref(b, t_first + r * W * 32);
@@ -398,7 +399,7 @@ attn_decode_staged_kernel(const DecodeArgs p, const KV kv) {
   if (p.early_trigger) pdl_launch_dependents();
   pdl_wait();
   trace_event(kTrAttnDecode, 1);
-  if (!p.early) len = p.kv_lengths[b];
+  if (!p.early) len = max(0, min(p.kv_lengths[b], p.kv_len));
   if (p.q_lengths && p.q_lengths[b] != 1) return;      // uniform per CTA (never combined with `early`: nothing is in flight)
   const long long row = p.row_start ? p.row_start[b] : b;
 
@@ -505,7 +506,7 @@ __global__ void __launch_bounds__(D)
 attn_combine_kernel(const DecodeArgs p) {
   const int h = blockIdx.x, b = blockIdx.y, tid = threadIdx.x;
   pdl_wait();
-  const int len = p.kv_lengths[b];
+  const int len = max(0, min(p.kv_lengths[b], p.kv_len));
   const int used = max(1, min(p.chunks, (len + p.chunk - 1) / p.chunk));
   const size_t base = (size_t(b) * p.heads + h) * p.chunks;
   float mm = -CUDART_INF_F;

@@ -42,6 +42,21 @@ __device__ __forceinline__ __half2 dequant2(int q_lo, int q_hi, float s_lo, floa
   return __floats2half2_rn(float(q_lo) * s_lo, float(q_hi) * s_hi);
 }
 
+// Four int8 weights of one 32-bit word at once, same values as dequant2 without integer-to-float conversions (which
+// run on a narrow pipe and bound the tensor-core GEMM at decode sizes): byte b of (word ^ 0x80808080) is q + 128; placed
+// under the exponent of 2^23 it is the float 8388608 + 128 + q exactly, one subtraction leaves float(q), one
+// multiplication by the scale rounds once -- the product float(q) * scale of the reference -- and the pair is narrowed
+// by cvt.rn.f16x2.f32.
+__device__ __forceinline__ void dequant4(uint32_t word, float s0, float s1, float s2, float s3, __half2& lo, __half2& hi) {
+  const uint32_t u = word ^ 0x80808080u;
+  const float f0 = __uint_as_float(__byte_perm(u, 0x4b000000u, 0x7650)) - 8388736.f;
+  const float f1 = __uint_as_float(__byte_perm(u, 0x4b000000u, 0x7651)) - 8388736.f;
+  const float f2 = __uint_as_float(__byte_perm(u, 0x4b000000u, 0x7652)) - 8388736.f;
+  const float f3 = __uint_as_float(__byte_perm(u, 0x4b000000u, 0x7653)) - 8388736.f;
+  lo = __floats2half2_rn(f0 * s0, f1 * s1);
+  hi = __floats2half2_rn(f2 * s2, f3 * s3);
+}
+
 // acc += float(a) * float(b), one rounding (the product of two binary16 values is exact in
 // binary32).  Mixed-precision FMA of the sm_100 family.
 __device__ __forceinline__ float fma_f16(float acc, __half a, __half b) {

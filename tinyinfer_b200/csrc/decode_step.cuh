@@ -42,8 +42,8 @@ namespace tib {
 
 constexpr int kStepThreads = kTcThreads;        // warp 0 TMA producer, warp 1 MMA issuer, warps 2..9 workers
 constexpr int kStepWorkers = kTcDequantThreads;
-constexpr int kStepRaw = 8;                     // int8 weight stages in flight / resident ahead of use
-constexpr int kStepOps = 4;                     // fp16 operand stages
+constexpr int kStepRaw = 4;                     // int8 weight stages in flight / resident ahead of use
+constexpr int kStepOps = 6;                     // fp16 operand stages: this many stages of the next item are dequantised ahead of its input
 constexpr uint32_t kFlagSpinLimit = 1u << 20;   // polls of an L2 round trip each: about a second
 
 struct StepSmem {
@@ -278,6 +278,20 @@ decode_step_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
     int raw_i = 0, op_i = 0, att_i = 0;
     bool ok = true;
     float sc[16];
+#ifdef TIB_STEP_TIMELINE
+    int tl_n = 0;
+    auto step_mark = [&](int code) {
+      if (t == 0 && p.timeline && tl_n < 1024) {
+        unsigned long long tm;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm));
+        p.timeline[size_t(cta) * 1024 + tl_n++] = (unsigned long long)code << 48 | (tm & 0xffffffffffffull);
+      }
+    };
+#define STEP_MARK(layer, event) step_mark((layer) * 32 + (event))
+#else
+#define STEP_MARK(layer, event) ((void)0)
+#endif
+    STEP_MARK(63, 0);
 
     // Per-request constants of this step: visible keys and where the new K/V row goes.
     if (t < kStepRows) {
@@ -303,12 +317,7 @@ decode_step_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         const uint32_t words[4] = {q.x, q.y, q.z, q.w};
         __half2 h[8];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const int q0 = int(int8_t(words[w] & 0xffu)), q1 = int(int8_t((words[w] >> 8) & 0xffu));
-          const int q2 = int(int8_t((words[w] >> 16) & 0xffu)), q3 = int(int8_t(words[w] >> 24));
-          h[2 * w] = dequant2(q0, q1, sc[4 * w], sc[4 * w + 1]);
-          h[2 * w + 1] = dequant2(q2, q3, sc[4 * w + 2], sc[4 * w + 3]);
-        }
+        for (int w = 0; w < 4; ++w) dequant4(words[w], sc[4 * w], sc[4 * w + 1], sc[4 * w + 2], sc[4 * w + 3], h[2 * w], h[2 * w + 1]);
         uint8_t* core = dst + (kg * 16 + 2 * cc) * 128 + r8 * 16;
         *reinterpret_cast<uint4*>(core) = *reinterpret_cast<const uint4*>(&h[0]);
         *reinterpret_cast<uint4*>(core + 128) = *reinterpret_cast<const uint4*>(&h[4]);
@@ -617,16 +626,21 @@ decode_step_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
       const uint32_t tag_in = tag_base + 1u + uint32_t(layer), tag_out = tag_in, tag_next = tag_in + 1u;
       if (role.kind == kItemQkv) {
         // x -> LayerNorm -> c_attn + bias; Q, K, V to the tagged buffer, K and V also to their cache pages
+        STEP_MARK(layer, 1);
         gather(p.xf, hidden_words, 0, p.hidden, tag_in);
         asm volatile("bar.sync 2, 256;" ::: "memory");
+        STEP_MARK(layer, 2);
         row_statistics();
         asm volatile("bar.sync 2, 256;" ::: "memory");
+        STEP_MARK(layer, 3);
         run_stages(it, true);
+        STEP_MARK(layer, 4);
         if (warp < 6) {
           const int col = it.n0 + n_local;
           const __half bias = it.bias[col];
           float v[32];
           read_acc(v, it.stages / it.chunk_stages, item_index);
+          STEP_MARK(layer, 5);
           __half h[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) h[i] = f2h(v[i] + h2f(bias));
@@ -637,22 +651,28 @@ decode_step_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
 #pragma unroll
             for (int i = 0; i < 32; ++i) if (i < M && ok) pool[s_row_base[i]] = h[i];
           }
+          STEP_MARK(layer, 6);
         }
         next_item();
+        STEP_MARK(layer, 7);
       }
       // decode attention: items (request, head) dealt round robin, the helper CTAs first
-      for (int a = first_att; a < M * p.heads; a += grid) attention_item(a / p.heads, a % p.heads, layer);
+      for (int a = first_att; a < M * p.heads; a += grid) { STEP_MARK(layer, 8); attention_item(a / p.heads, a % p.heads, layer); STEP_MARK(layer, 9); }
       if (role.kind == kItemProj) {
         // attention output -> attn.c_proj + bias + x -> res
         if (warp < 6) request_residual(p.xf, hidden_words, it.n0 + n_local, tag_in);   // x has been complete since before c_attn
+        STEP_MARK(layer, 1);
         gather(p.attnf, hidden_words, 0, p.hidden, tag_in);
         asm volatile("bar.sync 2, 256;" ::: "memory");
+        STEP_MARK(layer, 2);
         run_stages(it, false);
+        STEP_MARK(layer, 4);
         if (warp < 6) {
           const int col = it.n0 + n_local;
           const __half bias = it.bias[col];
           float v[32];
           read_acc(v, it.stages / it.chunk_stages, item_index);
+          STEP_MARK(layer, 5);
           __half h[32];
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
@@ -662,41 +682,55 @@ decode_step_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
             h[2 * k + 1] = f2h(h2f(r1) + h2f(f2h(v[2 * k + 1] + h2f(bias))));
           }
           store_pairs(h, p.resf, hidden_words, col, tag_out);
+          STEP_MARK(layer, 6);
         }
         next_item();
+        STEP_MARK(layer, 7);
       }
       if (role.kind == kItemFc) {
         // res -> LayerNorm -> c_fc + bias -> tanh-GELU -> act
+        STEP_MARK(layer, 1);
         gather(p.resf, hidden_words, 0, p.hidden, tag_in);
         asm volatile("bar.sync 2, 256;" ::: "memory");
+        STEP_MARK(layer, 2);
         row_statistics();
         asm volatile("bar.sync 2, 256;" ::: "memory");
+        STEP_MARK(layer, 3);
         run_stages(it, true);
+        STEP_MARK(layer, 4);
         if (warp < 6) {
           const int col = it.n0 + n_local;
           const __half bias = it.bias[col];
           float v[32];
           read_acc(v, it.stages / it.chunk_stages, item_index);
+          STEP_MARK(layer, 5);
           __half h[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) h[i] = i < M ? f2h(gelu_tanh(h2f(f2h(v[i] + h2f(bias))))) : f2h(0.f);
           store_pairs(h, p.actf, p.ff / 2, col, tag_out);
+          STEP_MARK(layer, 6);
         }
         next_item();
+        STEP_MARK(layer, 7);
       }
       if (role.kind == kItemProj2) {
         // act[:, K range] -> partial sums of mlp.c_proj; then this CTA finishes its share of the slab's columns:
         // sum over the K ranges in range order + bias + res -> x of the next layer
         const int ranks = p.ranks_proj2;
+        STEP_MARK(layer, 1);
         gather(p.actf, p.ff / 2, it.rank * p.chunk_proj2, p.chunk_proj2, tag_in);
         asm volatile("bar.sync 2, 256;" ::: "memory");
+        STEP_MARK(layer, 2);
         run_stages(it, false);
+        STEP_MARK(layer, 4);
         if (warp < 6) {
           float v[32];
           read_acc(v, 1, item_index);
+          STEP_MARK(layer, 5);
           unsigned long long* dst = p.partf + (size_t(it.slab * ranks + it.rank) * kStepRows) * 128 + n_local;
 #pragma unroll
           for (int i = 0; i < 32; ++i) if (i < M && ok) st_flag(dst + size_t(i) * 128, __float_as_uint(v[i]), tag_out);
+          STEP_MARK(layer, 6);
         }
         const int pairs = (64 + ranks - 1) / ranks, pair0 = it.rank * pairs, my_pairs = max(0, min(64, pair0 + pairs) - pair0);
 #pragma unroll 1
@@ -720,19 +754,25 @@ decode_step_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           const __half h1 = f2h(h2f(high_half(uint32_t(rw))) + h2f(f2h(v1 + h2f(high_half(bias2)))));
           if (ok) st_flag(p.xf + size_t(mrow) * hidden_words + col / 2, pack_halves(h0, h1), tag_next);
         }
+        STEP_MARK(layer, 10);
         next_item();
+        STEP_MARK(layer, 7);
       }
     }
 
     // ---------------------------------------------------------------- final LayerNorm, vocabulary projection, argmax
     if (item_index < n_items) {
+      STEP_MARK(p.layers, 1);
       gather(p.xf, hidden_words, 0, p.hidden, tag_base + 1u + uint32_t(p.layers));
       asm volatile("bar.sync 2, 256;" ::: "memory");
+      STEP_MARK(p.layers, 2);
       row_statistics();
       asm volatile("bar.sync 2, 256;" ::: "memory");
+      STEP_MARK(p.layers, 3);
     }
     while (item_index < n_items) {
       run_stages(it, true);
+      STEP_MARK(p.layers, 4);
       if (warp < 6) {
         const int col = it.n0 + n_local;
         float v[32];
@@ -768,9 +808,11 @@ decode_step_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
         }
         asm volatile("bar.sync 3, 128;" ::: "memory");
       }
+      STEP_MARK(p.layers, 6);
       next_item();
     }
     if (warp == 2 && lane < M && s_best[lane] && ok) atomicMax(p.best + lane, s_best[lane]);
+    STEP_MARK(63, 1);
     if (t == 0) s_consumed = raw_i;
   }
 

@@ -334,6 +334,7 @@ cudaError_t attention_paged_decode(const void* qkv, void* out, const int32_t* kl
   p.out = static_cast<__half*>(out); p.o_sb = hidden; p.o_sh = kv.head_dim;
   p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml; p.counters = counters;
   p.batch = batch; p.heads = kv.heads; p.early = early && !q_lengths ? 1 : 0; p.early_trigger = early_trigger ? 1 : 0;
+  p.kv_len = kv.table_pitch * kPageTokens;              // positions a slot's page table can name
   p.row_start = row_start; p.q_lengths = q_lengths;
   if ((row_start || q_lengths) && !whole_history) return cudaErrorNotSupported;
   if (whole_history) {
@@ -357,7 +358,7 @@ cudaError_t attention_packed_decode(const void* q, const void* k, const void* v,
   p.q = static_cast<const __half*>(q); p.q_sb = 64LL * heads; p.q_sh = 64;
   p.out = static_cast<__half*>(y); p.o_sb = 64LL * heads; p.o_sh = 64;
   p.kv_lengths = kl; p.part_acc = scratch_acc; p.part_ml = scratch_ml;
-  p.batch = batch; p.heads = heads; p.chunk = chunk; p.chunks = decode_chunks(kv_len, chunk);
+  p.batch = batch; p.heads = heads; p.chunk = chunk; p.chunks = decode_chunks(kv_len, chunk); p.kv_len = kv_len;
   KvPacked kv{static_cast<const __half*>(k), static_cast<const __half*>(v), heads, kv_len, 64};
   // A chunk that spans the whole history: one CTA of 8 warps per (request, head), merged in shared memory.
   if (p.chunks == 1 && kv_len > kDecodeWarps * 32) {
@@ -393,11 +394,11 @@ cudaError_t softmax(const void* x, void* y, int rows, int cols, cudaStream_t str
   return cudaGetLastError();
 }
 cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const void* wte, const void* wpe, void* x, int rows,
-                  int hidden, const LaunchOpts& o) {
+                  int hidden, int vocab, const LaunchOpts& o) {
   const long long work = (long long)rows * (hidden / 8);
   const int blocks = int(std::min<long long>((work + 255) / 256, 148LL * 8));
   return launch(embed_kernel, dim3(std::max(blocks, 1)), dim3(256), 0, o, 1, ids, row_pos, static_cast<const __half*>(wte),
-                static_cast<const __half*>(wpe), static_cast<__half*>(x), rows, hidden);
+                static_cast<const __half*>(wpe), static_cast<__half*>(x), rows, hidden, vocab);
 }
 cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out, int32_t* feedback,
                    const int32_t* step, void* scratch, const LaunchOpts& o) {

@@ -106,7 +106,7 @@ TIB_EXPORT cudaError_t gelu(const void* x, void* y, long long count, cudaStream_
 TIB_EXPORT cudaError_t softmax(const void* x, void* y, int rows, int cols, cudaStream_t stream);
 
 TIB_EXPORT cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const void* wte, const void* wpe,
-                             void* x, int rows, int hidden, const LaunchOpts& opts);
+                             void* x, int rows, int hidden, int vocab, const LaunchOpts& opts);
 // out[(*step) * rows + r] = argmax of row r (step may be null = 0); feedback[r] too when non-null.
 // scratch: null, or 12 * rows bytes of device memory (8-byte aligned, zero before its first use, left zero
 // by every call) that lets several CTAs share a row.

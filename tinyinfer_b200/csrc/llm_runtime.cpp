@@ -279,6 +279,10 @@ struct ti_llm_model {
     ck(cudaStreamSynchronize(stream));
     p.logits_pitch = vpitch;
     ck(tib::make_tile_map(tile_arena, tile_rows, &plan_tiles));
+#ifdef TIB_STEP_TIMELINE
+    p.timeline = dev<unsigned long long>(size_t(256) * 1024);
+    ck(cudaMemsetAsync(p.timeline, 0, size_t(256) * 1024 * 8, stream));
+#endif
     plan = p; plan_ready = true; plan_epochs = 0;
     if (const char* v = std::getenv("TINYINFER_B200_PERSISTENT")) use_persistent = std::atoi(v) != 0;
   }
@@ -341,7 +345,7 @@ struct ti_llm_model {
   void run_layers(const Meta& m) {
     const int H = shape.hidden;
     tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
-    ck(tib::embed(m.ids, m.row_pos, wte, wpe, x, m.rows, H, o));
+    ck(tib::embed(m.ids, m.row_pos, wte, wpe, x, m.rows, H, shape.vocab, o));
     tib::PagedKv kv; kv.k_pool = k_pool; kv.v_pool = v_pool; kv.table = d_table; kv.slots = m.slots;
     kv.table_pitch = pages_per_slot; kv.layers = shape.layers; kv.heads = shape.heads; kv.head_dim = 64;
     for (int l = 0; l < shape.layers; ++l) {
@@ -838,6 +842,17 @@ int ti_b200_llm_decode_plan(ti_llm_model* m, int32_t select, int32_t* active) {
     if (active) *active = m->plan_ready && m->use_persistent ? 1 : 0;
   });
 }
+
+#ifdef TIB_STEP_TIMELINE
+// Development builds: copies the per-CTA event log of the last persistent step ([256][1024] words) and clears it.
+int ti_b200_step_timeline(ti_llm_model* m, unsigned long long* out) {
+  return guarded(m, [&] {
+    ck(cudaStreamSynchronize(m->stream));
+    ck(cudaMemcpy(out, m->plan.timeline, size_t(256) * 1024 * 8, cudaMemcpyDeviceToHost));
+    ck(cudaMemset(m->plan.timeline, 0, size_t(256) * 1024 * 8));
+  });
+}
+#endif
 
 int ti_llm_score_window(ti_llm_model* m, const int32_t* tokens, const uint8_t* mask, int32_t length, double* nll, uint64_t* count,
                         double* positions) {

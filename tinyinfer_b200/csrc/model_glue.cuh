@@ -11,14 +11,14 @@ namespace tib {
 // x[r,:] = fp16(float(wte[id]) + float(wpe[pos]))  (reference embed, llm/src/runtime.cu:25-30).
 __global__ void __launch_bounds__(256)
 embed_kernel(const int32_t* ids, const int32_t* row_pos, const __half* wte, const __half* wpe,
-             __half* x, int rows, int hidden) {
+             __half* x, int rows, int hidden, int vocab) {
   trace_event(kTrEmbed, 0);
   pdl_wait();
   const int chunks = hidden / 8;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * chunks;
        i += (long long)gridDim.x * blockDim.x) {
     const int r = int(i / chunks), c = int(i % chunks) * 8;
-    uint4 a = *reinterpret_cast<const uint4*>(wte + size_t(ids[r]) * hidden + c);
+    uint4 a = *reinterpret_cast<const uint4*>(wte + size_t(max(0, min(ids[r], vocab - 1))) * hidden + c);   // never an address outside the table
     const uint4 b = *reinterpret_cast<const uint4*>(wpe + size_t(row_pos[r]) * hidden + c);
     __half* ah = reinterpret_cast<__half*>(&a);
     const __half* bh = reinterpret_cast<const __half*>(&b);
@@ -95,7 +95,11 @@ argmax_kernel(const float* logits, long long pitch, int cols, int32_t* out, int3
     }
     if (write) {
       out[(step ? size_t(*step) * gridDim.x : 0) + r] = bi;
-      if (feedback) feedback[r] = bi;
+      // A row without any comparable logit (all NaN) yields INT_MAX as in the reference, whose host then rejects it as an
+      // invalid token.  Here the next step may read the id on the device, so it gets a valid one and the status word
+      // makes the host poison the model.
+      if (feedback) feedback[r] = bi < cols ? bi : 0;
+      if (bi >= cols) report(kStatusNoToken);
     }
   }
 }

@@ -50,6 +50,8 @@ struct StepPlan {
   unsigned int* sync = nullptr;        // [0] tag epoch, [1] finish tickets
   unsigned long long* best = nullptr;  // [kStepRows] argmax merge words, zero between steps
   float* logits = nullptr; int logits_pitch = 0;   // optional fp32 [batch][logits_pitch]
+  // development builds (-DTIB_STEP_TIMELINE): [CTA][1024] words (event code << 48 | %globaltimer) of worker thread 0
+  unsigned long long* timeline = nullptr;
 };
 
 // What CTA `cta` owns in every layer.  kind: 0 c_attn slab, 1 attn.c_proj slab, 2 c_fc slab, 3 (slab, K range) of
