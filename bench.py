@@ -499,12 +499,16 @@ def gpu_main(args, rank, world):
         extras = {}
         if rank == 0 and world == 1 and not args.no_extras:
             extras["config0"] = config0_record(model, weights, peak)
-            if persistent:                                    # the plan this build replaces, same workload, for the record
-                model.decode_plan(0)
-                ms0, _ = timed_steps(min(K, 40), 3)
-                extras["launch_per_operation_plan"] = {"ms_per_step": ms0 / min(K, 40), "gpu_launches_per_step": 65,
-                                                       "config0": config0_record(model, weights, peak)}
-                model.decode_plan(1)
+            # the other decode plan on the same workloads, for the record (both produce the same bits)
+            other = 0 if persistent else 1
+            try:
+                model.decode_plan(other)
+                ms_other, _ = timed_steps(min(K, 40), 3)
+                extras["other_decode_plan"] = {"plan": "persistent step kernel (1 launch per step)" if other == 1 else "launch per operation (65 launches per step)",
+                                               "ms_per_step": ms_other / min(K, 40), "config0": config0_record(model, weights, peak)}
+            except RuntimeError as error:                     # plan 1 is not available for every shape / device
+                extras["other_decode_plan"] = {"unavailable": str(error)}
+            model.decode_plan(1 if persistent else 0)
 
     line = {"metric": "int8_gpt2_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": device_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations x int8 weights, f32 accumulate",

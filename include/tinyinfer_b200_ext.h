@@ -80,13 +80,21 @@ struct ti_llm_model;
 int ti_b200_llm_decode_steps(struct ti_llm_model* model, const int32_t* slots, const int32_t* first_tokens,
                              int32_t batch, int32_t steps, int32_t* out_tokens, double* device_ms);
 
-/* Exported by libtinyinfer_llm.so.  Selects how a greedy decode step of up to 32 requests runs: 1 = one persistent
- * kernel per step (one CTA per SM, activations handed between CTAs as tagged words; the default wherever the model
- * shape and the device allow it), 0 = one launch per operation replayed as a CUDA graph, -1 = leave as is.  Both plans
- * produce the same bits.  active (nullable) receives the plan in force afterwards.  The reference has one plan only
+/* Exported by libtinyinfer_llm.so.  Selects how a greedy decode step of up to 32 requests runs: 0 = one launch per
+ * operation replayed as a CUDA graph (the default), 1 = one persistent kernel per step (one CTA per SM, activations
+ * handed between CTAs as tagged words; available where the model shape and the device allow it), -1 = leave as is.
+ * Both plans produce the same bits.  active (nullable) receives the plan in force afterwards.  The reference has one plan only
  * (a launch per operation, llm/src/runtime.cu:135-168).  Returns a ti_llm_status; TI_LLM_INVALID when plan 1 is
  * asked for a shape it does not cover. */
 int ti_b200_llm_decode_plan(struct ti_llm_model* model, int32_t select, int32_t* active);
+
+/* Exported by libtinyinfer_llm.so.  Test hook for the failure paths; the reference has none (its tests never reach
+ * llm/src/runtime.cu:127,172-174).  kind 0: the forward call after `after_calls` more valid ones fails on the host
+ * the way a failed launch does (TI_LLM_CUDA, the model is poisoned).  kind 1: enqueues a one-thread kernel whose
+ * bounded mbarrier wait runs out after about a thousand polls and records a timeout in the device status word -- the
+ * path every pipeline wait takes on expiry -- so the next call that synchronises returns TI_LLM_CUDA and poisons the
+ * model.  Neither faults, traps or hangs the GPU. */
+int ti_b200_llm_inject_failure(struct ti_llm_model* model, int32_t kind, int32_t after_calls);
 #ifdef __cplusplus
 }
 #endif

@@ -13,6 +13,7 @@ import argparse
 import array
 import hashlib
 import json
+import os
 import struct
 import sys
 from pathlib import Path
@@ -24,7 +25,8 @@ ROOT = Path(__file__).resolve().parents[2]
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", default=os.environ.get("TINYINFER_REFERENCE"), required="TINYINFER_REFERENCE" not in os.environ,
+                        help="the reference checkout (or the TINYINFER_REFERENCE environment variable)")
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
     from llm.export_weights import quantized_bytes

@@ -323,3 +323,35 @@ def test_two_devices_in_one_process(manifest):
         la = logits_of(a.forward([2], [prompt]))
         lb = logits_of(b.forward([2], [prompt]))
         assert torch.equal(la, lb)
+
+
+def _inject(model, kind, after=0):
+    import ctypes as C
+    fn = model.lib.ti_b200_llm_inject_failure
+    fn.argtypes, fn.restype = [C.c_void_p, C.c_int32, C.c_int32], C.c_int
+    assert fn(model._model, kind, after) == 0
+
+
+@pytest.mark.parametrize("kind", [0, 1], ids=["host_exception", "device_wait_runs_out"])
+def test_execution_failure_poisons_the_model(manifest, kind):
+    """Reference semantics (llm/src/runtime.cu:127,172-174, tinyinfer_llm.h:9-11): an execution failure returns
+    TI_LLM_CUDA / INTERNAL, every later call fails until destroy, lengths stay as they were, destroy works.
+    kind 0 throws on the host inside the second forward call; kind 1 lets a one-thread kernel's bounded wait run out
+    (microseconds; nothing faults), which the next synchronising call finds in the device status word."""
+    from tinyinfer_b200.runtime import NativeModel
+    prompt = tokens(8, 12)
+    with NativeModel(None, manifest, max_batch=2, cache_slots=2, capacity=64) as m:
+        first = m.forward([0], [prompt], return_logits=False)["next_tokens"]
+        before = m.lengths()
+        _inject(m, kind, 0)
+        with pytest.raises(RuntimeError) as failed:
+            m.forward([0], [first], return_logits=False)
+        assert "status 3" in str(failed.value)                      # TI_LLM_CUDA
+        for call in (lambda: m.forward([1], [prompt]), lambda: m.lengths(), lambda: m.reset(0), lambda: m.greedy([prompt], 2, slots=[1])):
+            with pytest.raises(RuntimeError) as again:
+                call()
+            assert "poisoned" in str(again.value)
+    # a fresh context on the same device works (the status word was cleared with the failure)
+    with NativeModel(None, manifest, max_batch=2, cache_slots=2, capacity=64) as m:
+        assert m.forward([0], [prompt], return_logits=False)["next_tokens"] == first
+        assert m.lengths() == before

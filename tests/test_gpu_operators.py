@@ -269,3 +269,29 @@ def test_native_status_codes(ops):
     assert lib.ti_v2_gelu_new_f16(a.data_ptr(), a.data_ptr(), ctypes.c_int64(0), 0, 0) == 1
     torch.cuda.synchronize()
     assert torch.equal(y, torch.full_like(y, 4.0))
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_attention_accepts_tensors_that_are_only_two_byte_aligned(ops, d):
+    """The reference's validators ask for 2-byte alignment of q/k/v/y (backend/include/tinyinfer_host_validation.hpp);
+    views that start one element into an allocation must be accepted and give the same bits as aligned copies."""
+    torch.manual_seed(d)
+    nq, nk, ql, kl, off = 17, 33, [17, 11], [33, 20], [16, 9]
+    shapes = {"q": (2, 2, nq, d), "k": (2, 2, nk, d), "v": (2, 2, nk, d)}
+    aligned = {name: (torch.randn(shape, device="cuda") * 0.5).half() for name, shape in shapes.items()}
+    want = ops.attention(aligned["q"], aligned["k"], aligned["v"], q_lengths=ql, kv_lengths=kl, query_offsets=off, causal=True)
+    shifted = {}
+    for name, tensor in aligned.items():
+        base = torch.empty(tensor.numel() + 8, device="cuda", dtype=torch.float16)
+        shifted[name] = base[1:1 + tensor.numel()].view(tensor.shape)
+        shifted[name].copy_(tensor)
+        assert shifted[name].data_ptr() % 16 == 2
+    out_base = torch.zeros(aligned["q"].numel() + 8, device="cuda", dtype=torch.float16)
+    out = out_base[1:1 + aligned["q"].numel()].view(aligned["q"].shape)
+    meta = [torch.tensor(values, dtype=torch.int32, device="cuda") for values in (ql, kl, off)]
+    status = ops.lib.ti_v2_attention_f16(shifted["q"].data_ptr(), shifted["k"].data_ptr(), shifted["v"].data_ptr(), out.data_ptr(),
+                                         meta[0].data_ptr(), meta[1].data_ptr(), meta[2].data_ptr(), 2, 2, nq, nk, d, 1, 0,
+                                         torch.cuda.current_stream().cuda_stream, torch.cuda.current_device())
+    assert status == 0, ops.lib.ti_v2_last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)

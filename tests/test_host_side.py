@@ -11,7 +11,6 @@ import pytest
 import tinyinfer_b200
 from oracle import ti_oracle as orc
 from tinyinfer_b200 import artifact, quantization
-from tinyinfer_b200.cache_reference import KVCache, causal_keys
 from tinyinfer_b200.host_codec import HostCodec
 
 ROOT = Path(__file__).resolve().parents[1]
@@ -153,25 +152,6 @@ def test_native_ops_reject_cpu_tensors_before_any_native_call(built):
         ops.gemm(a, a.t().contiguous())
     with pytest.raises(TypeError):
         ops.layernorm(a, a[0], a[0])
-
-
-# ------------------------------------------------------------------ cache semantics (reference test_contracts.py:60-99)
-def test_cache_append_offsets_isolation_and_transactions():
-    cache = KVCache(3, 2, 5)
-    cache.append_batch([0, 2], [[[10, 11], [20, 21]], [[30], [40]]], [[[110, 111], [120, 121]], [[130], [140]]])
-    assert cache.lengths == [2, 0, 1] and cache.read(0, 1) == ([20, 21], [120, 121])
-    cache.append_batch([2], [[[31, 32], [41, 42]]], [[[131, 132], [141, 142]]])
-    assert cache.lengths == [2, 0, 3] and cache.read(2, 0) == ([30, 31, 32], [130, 131, 132])
-    assert list(causal_keys(0, 2, 5)) == [0, 1, 2] and list(causal_keys(1, 2, 3)) == [0, 1, 2]
-    small = KVCache(2, 1, 2)
-    small.append_batch([0], [[[1]]], [[[2]]])
-    for args in (([0, 0], [[[3]], [[4]]], [[[5]], [[6]]]), ([1, 0], [[[3]], [[4, 5]]], [[[6]], [[7, 8]]]), ([1], [[[]]], [[[]]]),
-                 ([True], [[[3]]], [[[4]]]), ([2], [[[3]]], [[[4]]]), ([1], [[[3]]], [[[4, 5]]])):
-        with pytest.raises(ValueError):
-            small.append_batch(*args)
-        assert small.lengths == [1, 0] and small.read(1, 0) == ([], [])
-    small.reset(0)
-    assert small.lengths == [0, 0] and small.read(0, 0) == ([], [])
 
 
 # ------------------------------------------------------------------ artifact format

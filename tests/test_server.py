@@ -198,3 +198,42 @@ def test_mpsc_queue_with_real_threads(tmp_path, sanitizer):
     if sanitizer and "FATAL: ThreadSanitizer" in run.stderr:
         pytest.skip("thread sanitizer cannot run in this environment")
     assert run.returncode == 0 and run.stdout.strip() == "ok", run.stdout + run.stderr
+
+
+def test_a_failing_worker_answers_internal_and_the_other_worker_keeps_serving():
+    """Reference behaviour for a failed native call (server/src/main.cpp:151-156): everything outstanding on that worker
+    and everything it receives later is answered `internal`, the process stays up.  With several workers the router
+    then prefers the healthy ones.  The failure is injected on the host (test hook --fail-after-steps)."""
+    with Server("--devices", "0,1", "--max-batch", 4, "--fail-worker", 0, "--fail-after-steps", 3) as server:
+        sock = server.connect()
+        prompts = {i: [100 + i, 200 + i, 300 + i] for i in range(1, 9)}
+        for i, prompt in prompts.items():
+            sock.sendall(protocol.request(i, prompt, 6))
+        _, final = collect(sock, len(prompts))
+        failed = sorted(i for i, r in final.items() if r["status"] == protocol.INTERNAL)
+        served = sorted(i for i, r in final.items() if r["status"] == protocol.OK)
+        assert failed and served and len(failed) + len(served) == len(prompts)
+        for i in served:
+            assert final[i]["tokens"] == expected_tokens(prompts[i], 6)
+        for i in failed:
+            assert final[i]["tokens"] == []
+        # later requests: the healthy worker serves them all
+        for i in range(20, 30):
+            sock.sendall(protocol.request(i, [i, i + 1], 4))
+        _, later = collect(sock, 10)
+        assert all(r["status"] == protocol.OK and r["tokens"] == expected_tokens([i, i + 1], 4) for i, r in later.items())
+        sock.close()
+        err = server.close()
+    assert "model_poisoned: device 0" in err
+
+
+def test_a_single_failing_worker_answers_internal_from_then_on():
+    with Server("--max-batch", 2, "--fail-after-steps", 2) as server:
+        sock = server.connect()
+        sock.sendall(protocol.request(1, [5, 6, 7], 8))
+        _, final = collect(sock, 1)
+        assert final[1]["status"] == protocol.INTERNAL
+        sock.sendall(protocol.request(2, [9], 2))
+        _, final = collect(sock, 1)
+        assert final[2]["status"] == protocol.INTERNAL and final[2]["tokens"] == []
+        sock.close()

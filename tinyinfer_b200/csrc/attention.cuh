@@ -67,7 +67,19 @@ struct AttnArgs {
 // ------------------------------------------------------------------ tiled kernel (Q >= 1)
 constexpr int kAttnTileQ = 8, kAttnTileK = 32;
 
-template <int D, typename KV>
+// Eight consecutive halves: one 16-byte load where the tensors allow it (VEC), else element by element -- the operator
+// ABI accepts tensors that are only 2-byte aligned (reference validators, tinyinfer_host_validation.hpp).
+template <bool VEC>
+__device__ __forceinline__ uint4 load8(const __half* src) {
+  if (VEC) return *reinterpret_cast<const uint4*>(src);
+  uint4 v;
+  __half* h = reinterpret_cast<__half*>(&v);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) h[e] = src[e];
+  return v;
+}
+
+template <int D, typename KV, bool VEC = true>
 __global__ void __launch_bounds__(256)
 attn_tile_kernel(const AttnArgs p, const KV kv) {
   constexpr int PITCH = D + 8;                                  // halves; keeps 16-byte row reads conflict-free
@@ -91,7 +103,7 @@ attn_tile_kernel(const AttnArgs p, const KV kv) {
 
   for (int i = lane; i < D / 8; i += 32) {
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (active) v = *reinterpret_cast<const uint4*>(p.q + q_base + h * p.q_sh + (long long)qi * p.q_si + i * 8);
+    if (active) v = load8<VEC>(p.q + q_base + h * p.q_sh + (long long)qi * p.q_si + i * 8);
     *reinterpret_cast<uint4*>(&qs[warp][i * 8]) = v;
   }
   float m = -CUDART_INF_F, l = 0.f, acc[D / 32];
@@ -105,8 +117,8 @@ attn_tile_kernel(const AttnArgs p, const KV kv) {
       uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
       if (key < end) {
         const size_t o = kv.offset(b, h, key) + c * 8;
-        kk = *reinterpret_cast<const uint4*>(kv.k + o);
-        vv = *reinterpret_cast<const uint4*>(kv.v + o);
+        kk = load8<VEC>(kv.k + o);
+        vv = load8<VEC>(kv.v + o);
       }
       *reinterpret_cast<uint4*>(&ks[r][c * 8]) = kk;
       *reinterpret_cast<uint4*>(&vs[r][c * 8]) = vv;

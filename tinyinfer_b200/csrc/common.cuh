@@ -190,6 +190,14 @@ __device__ __forceinline__ void trace_slot(int what) {
 #endif
 enum TraceKernel { kTrEmbed = 1, kTrLayerNorm, kTrGemmTc, kTrGemv, kTrAttnDecode, kTrAttnTile, kTrCombine, kTrArgmax, kTrAdvance };
 
+// ------------------------------------------------------------------ argmax merge word
+// (value, index) as one 64-bit word whose unsigned order is: larger value first, lower index among equal values.
+__device__ __forceinline__ unsigned long long argmax_pack(float v, int index) {
+  const uint32_t u = __float_as_uint(v + 0.f);                      // -0 -> +0: equal values must compare equal
+  const uint32_t ordered = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+  return (unsigned long long)ordered << 32 | (0xffffffffu - uint32_t(index));
+}
+
 // ------------------------------------------------------------------ warp reductions
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -706,7 +706,10 @@ decode_step_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_const
           STEP_MARK(layer, 5);
           __half h[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) h[i] = i < M ? f2h(gelu_tanh(h2f(f2h(v[i] + h2f(bias))))) : f2h(0.f);
+          for (int i = 0; i < 32; ++i) {
+            h[i] = f2h(0.f);
+            if (i < M) h[i] = f2h(gelu_tanh(h2f(f2h(v[i] + h2f(bias)))));      // a branch, not a select: tanhf only for rows that exist
+          }
           store_pairs(h, p.actf, p.ff / 2, col, tag_out);
           STEP_MARK(layer, 6);
         }

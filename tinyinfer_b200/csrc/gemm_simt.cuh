@@ -61,6 +61,10 @@ struct GemvArgs {
   // LayerNorm prologue (tensor-core kernel, at most 32 rows, K = row width <= 768): `a` holds the rows before
   // normalisation; the kernel computes each row's statistics and normalises while staging the operand.
   const __half* ln_gamma; const __half* ln_beta; float ln_eps;
+  // Greedy argmax as an epilogue (tensor-core kernel, fp32 output without a K split, i.e. the vocabulary projection):
+  // every CTA merges the best (value, lowest index) of its 128 columns into argmax_best[row] (argmax_pack words, zero
+  // between steps) with atomicMax; skip_store: the logits themselves are not wanted.
+  unsigned long long* argmax_best; int skip_store;
 };
 
 // Offset (in halves) of head 0, element 0 of row `row`'s position inside the K / V pool.
@@ -97,12 +101,7 @@ __device__ __forceinline__ void gemv_consume_stage(const uint8_t* stage, const _
     if constexpr (sizeof(WT) == 1) {
       const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int q0 = int(int8_t(words[j] & 0xffu)), q1 = int(int8_t((words[j] >> 8) & 0xffu));
-        const int q2 = int(int8_t((words[j] >> 16) & 0xffu)), q3 = int(int8_t(words[j] >> 24));
-        w2[2 * j] = dequant2(q0, q1, s[4 * j], s[4 * j + 1]);
-        w2[2 * j + 1] = dequant2(q2, q3, s[4 * j + 2], s[4 * j + 3]);
-      }
+      for (int j = 0; j < 4; ++j) dequant4(words[j], s[4 * j], s[4 * j + 1], s[4 * j + 2], s[4 * j + 3], w2[2 * j], w2[2 * j + 1]);
     } else {
       const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll

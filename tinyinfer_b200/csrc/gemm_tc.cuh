@@ -30,6 +30,8 @@
 #include <cooperative_groups.h>
 #include <cuda.h>
 
+#include <math_constants.h>
+
 #include "common.cuh"
 #include "elementwise.cuh"
 #include "gemm_simt.cuh"
@@ -297,12 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         const uint32_t words[4] = {q.x, q.y, q.z, q.w};
         __half2 h[8];
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const int q0 = int(int8_t(words[w] & 0xffu)), q1 = int(int8_t((words[w] >> 8) & 0xffu));
-          const int q2 = int(int8_t((words[w] >> 16) & 0xffu)), q3 = int(int8_t(words[w] >> 24));
-          h[2 * w] = dequant2(q0, q1, sc[4 * w], sc[4 * w + 1]);
-          h[2 * w + 1] = dequant2(q2, q3, sc[4 * w + 2], sc[4 * w + 3]);
-        }
+        for (int w = 0; w < 4; ++w) dequant4(words[w], sc[4 * w], sc[4 * w + 1], sc[4 * w + 2], sc[4 * w + 3], h[2 * w], h[2 * w + 1]);
         uint8_t* core = dst + (kg * 16 + 2 * cc) * 128 + r8 * 16;      // core matrix (k-group, channel-group), row k%8
         *reinterpret_cast<uint4*>(core) = *reinterpret_cast<const uint4*>(&h[0]);
         *reinterpret_cast<uint4*>(core + 128) = *reinterpret_cast<const uint4*>(&h[4]);
@@ -584,6 +581,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         if (col + 1 < p.n) f.y += h2f(p.bias[col + 1]);
         if (col + 2 < p.n) f.z += h2f(p.bias[col + 2]);
         if (col + 3 < p.n) f.w += h2f(p.bias[col + 3]);
+      }
+      if (p.argmax_best) {
+        // a warp holds one row's 128 columns (the loop bounds are multiples of 32 and `row` is the same for the 32 lanes):
+        // largest value, lowest column among equals, columns past N and NaN never win (reference argmax, llm/src/runtime.cu:59-66)
+        float bv = -CUDART_INF_F; int bi = 0x7fffffff;
+        const float vals[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (col + e < p.n && (vals[e] > bv || (vals[e] == bv && col + e < bi))) { bv = vals[e]; bi = col + e; }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv, d);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if ((tid & 31) == 0 && bi != 0x7fffffff) atomicMax(p.argmax_best + row, argmax_pack(bv, bi));
+        if (p.skip_store) continue;
       }
       float* out = static_cast<float*>(p.out) + size_t(row) * p.ldo + col;
       if (col + 3 < p.n) *reinterpret_cast<float4*>(out) = f;

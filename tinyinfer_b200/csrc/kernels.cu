@@ -160,6 +160,7 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   a.out = c.out; a.residual = static_cast<const __half*>(c.residual);
   a.lda = c.lda; a.ldo = c.ldo; a.ldw = c.ldw; a.m = c.m; a.n = c.n; a.k = c.k;
   a.out_fp32 = c.out_fp32; a.gelu = c.gelu; a.early_trigger = o.early_trigger && o.pdl ? 1 : 0;
+  a.argmax_best = static_cast<unsigned long long*>(c.argmax_best); a.skip_store = c.skip_store ? 1 : 0;
   if (c.kv) {
     a.k_pool = static_cast<__half*>(c.kv->k_pool); a.v_pool = static_cast<__half*>(c.kv->v_pool);
     a.kv_table = c.kv->table; a.kv_slots = c.kv->slots; a.kv_row_req = c.kv_row_req; a.kv_row_pos = c.kv_row_pos;
@@ -237,6 +238,20 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
     }
   }
   if (c.ln_gamma || c.w_slab_rows) return cudaErrorNotSupported;   // only the tensor-core kernel has the LayerNorm prologue / reads tiles
+  // Row tiles run along grid.z (at most 65535): more rows than that go out as several launches over row blocks.
+  constexpr int kSimtRowsPerLaunch = 4 * 65535;
+  if (c.m > kSimtRowsPerLaunch) {
+    for (int row0 = 0; row0 < c.m; row0 += kSimtRowsPerLaunch) {
+      GemmCall part = c;
+      part.m = std::min(kSimtRowsPerLaunch, c.m - row0);
+      part.a = static_cast<const __half*>(c.a) + size_t(row0) * c.lda;
+      part.out = c.out_fp32 ? static_cast<void*>(static_cast<float*>(c.out) + size_t(row0) * c.ldo) : static_cast<void*>(static_cast<__half*>(c.out) + size_t(row0) * c.ldo);
+      if (c.residual) part.residual = static_cast<const __half*>(c.residual) + size_t(row0) * c.ldo;
+      const cudaError_t st = gemm(part, o);
+      if (st != cudaSuccess) return st;
+    }
+    return cudaSuccess;
+  }
   const int bn = c.w_int8 ? 128 : 64;
   const int mt = c.m >= 3 ? 4 : c.m;
   const int slabs = (c.n + bn - 1) / bn, m_tiles = (c.m + mt - 1) / mt;
@@ -280,8 +295,15 @@ cudaError_t quantize_i8(const void* w, long long rows, int cols, int8_t* q, floa
 }
 
 cudaError_t sgemm(const float* a, const float* b, float* c, int m, int n, int k, cudaStream_t stream) {
-  sgemm_kernel<<<dim3((n + 15) / 16, (m + 15) / 16), 256, 0, stream>>>(a, b, c, m, n, k);
-  return cudaGetLastError();
+  // 16-row tiles along grid.y (at most 65535 of them per launch): row blocks beyond that take further launches
+  constexpr int kRowsPerLaunch = 16 * 65535;
+  for (int row0 = 0; row0 < m; row0 += kRowsPerLaunch) {
+    const int rows = std::min(kRowsPerLaunch, m - row0);
+    sgemm_kernel<<<dim3((n + 15) / 16, (rows + 15) / 16), 256, 0, stream>>>(a + size_t(row0) * k, b, c + size_t(row0) * n, rows, n, k);
+    const cudaError_t st = cudaGetLastError();
+    if (st != cudaSuccess) return st;
+  }
+  return cudaSuccess;
 }
 
 // ---------------------------------------------------------------- attention
@@ -297,8 +319,11 @@ cudaError_t attention_packed(const void* q, const void* k, const void* v, void* 
   p.batch = batch; p.heads = heads; p.q_len = q_len; p.kv_len = kv_len; p.causal = causal;
   KvPacked kv{static_cast<const __half*>(k), static_cast<const __half*>(v), heads, kv_len, d};
   const dim3 grid((q_len + kAttnTileQ - 1) / kAttnTileQ, heads, batch);
-  if (d == 64) return launch(attn_tile_kernel<64, KvPacked>, grid, dim3(256), 0, o, 1, p, kv);
-  if (d == 128) return launch(attn_tile_kernel<128, KvPacked>, grid, dim3(256), 0, o, 1, p, kv);
+  const bool vec = (reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) % 16 == 0;
+  if (d == 64) return vec ? launch(attn_tile_kernel<64, KvPacked, true>, grid, dim3(256), 0, o, 1, p, kv)
+                          : launch(attn_tile_kernel<64, KvPacked, false>, grid, dim3(256), 0, o, 1, p, kv);
+  if (d == 128) return vec ? launch(attn_tile_kernel<128, KvPacked, true>, grid, dim3(256), 0, o, 1, p, kv)
+                           : launch(attn_tile_kernel<128, KvPacked, false>, grid, dim3(256), 0, o, 1, p, kv);
   return cudaErrorInvalidValue;
 }
 
@@ -319,7 +344,7 @@ cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start
   p.q_lengths = ql; p.kv_lengths = kl; p.offsets = off;
   p.batch = batch; p.heads = kv.heads; p.q_len = max_q; p.kv_len = max_kv; p.causal = 1; p.skip_single = skip_single ? 1 : 0;
   const dim3 grid((max_q + kAttnTileQ - 1) / kAttnTileQ, kv.heads, batch);
-  return launch(attn_tile_kernel<64, KvPaged>, grid, dim3(256), 0, o, 1, p, paged(kv));
+  return launch(attn_tile_kernel<64, KvPaged, true>, grid, dim3(256), 0, o, 1, p, paged(kv));
 }
 
 int decode_chunks(int max_kv, int chunk) { return std::max(1, (max_kv + chunk - 1) / chunk); }
@@ -409,6 +434,11 @@ cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int
   auto* tickets = reinterpret_cast<unsigned int*>(best + rows);
   return launch(argmax_kernel, dim3(rows, segments), dim3(256), 0, o, 1, logits, pitch, cols, out, feedback, step, best, tickets);
 }
+cudaError_t argmax_finish(void* best, int rows, int cols, int32_t* out, int32_t* feedback, int32_t* step, int32_t* row_pos,
+                          int32_t* kv_lengths, const LaunchOpts& o) {
+  if (rows < 1 || rows > 64) return cudaErrorInvalidValue;
+  return launch(argmax_finish_kernel, dim3(1), dim3(64), 0, o, 1, static_cast<unsigned long long*>(best), rows, cols, out, feedback, step, row_pos, kv_lengths);
+}
 cudaError_t advance(int32_t* row_pos, int32_t* kv_lengths, int32_t* step, int batch, const LaunchOpts& o) {
   return launch(advance_kernel, dim3((batch + 63) / 64), dim3(64), 0, o, 1, row_pos, kv_lengths, step, batch);
 }
@@ -478,6 +508,11 @@ extern "C" int ti_b200_trace_dump(unsigned long long* out, int capacity) {
   return int(n);
 }
 #endif
+
+cudaError_t selftest_bounded_wait(cudaStream_t stream, unsigned int polls) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(polls);
+  return cudaGetLastError();
+}
 
 cudaError_t device_status_address(unsigned int** address) {
   return cudaGetSymbolAddress(reinterpret_cast<void**>(address), g_device_status);

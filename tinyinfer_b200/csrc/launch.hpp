@@ -52,6 +52,9 @@ struct GemmCall {
   // gemm() returns cudaErrorNotSupported when the shape cannot take it.
   const void* ln_gamma = nullptr; const void* ln_beta = nullptr; float ln_eps = 1e-5f;
   bool uniform_numerics = false;                         // tensor-core kernel for any row count (batch-invariant results)
+  // fp32 output without a K split (vocabulary projection): merge each row's greedy argmax into argmax_best[row]
+  // (64-bit words, zero between steps; argmax_finish publishes them); skip_store: do not write the logits.
+  void* argmax_best = nullptr; bool skip_store = false;
   int m = 0, n = 0, k = 0;
 };
 TIB_EXPORT cudaError_t gemm(const GemmCall& call, const LaunchOpts& opts);
@@ -112,6 +115,10 @@ TIB_EXPORT cudaError_t embed(const int32_t* ids, const int32_t* row_pos, const v
 // by every call) that lets several CTAs share a row.
 TIB_EXPORT cudaError_t argmax(const float* logits, long long pitch, int rows, int cols, int32_t* out,
                               int32_t* feedback, const int32_t* step, void* scratch, const LaunchOpts& opts);
+// After a gemm() with argmax_best: out[(*step) * rows + r] and feedback[r] from best[r] (left zero), then row_pos[r]++,
+// kv_lengths[r]++ and (*step)++.  rows <= 64.
+TIB_EXPORT cudaError_t argmax_finish(void* best, int rows, int cols, int32_t* out, int32_t* feedback, int32_t* step,
+                                     int32_t* row_pos, int32_t* kv_lengths, const LaunchOpts& opts);
 // row_pos[b]++, kv_lengths[b]++ for b < batch, and (*step)++.
 TIB_EXPORT cudaError_t advance(int32_t* row_pos, int32_t* kv_lengths, int32_t* step, int batch, const LaunchOpts& opts);
 
@@ -128,6 +135,10 @@ TIB_EXPORT int step_k_chunk(int n, int k);
 TIB_EXPORT const char* step_unsupported(const StepPlan& plan);
 TIB_EXPORT cudaError_t make_tile_map(const void* arena, long long rows, TileMap* out);
 TIB_EXPORT cudaError_t decode_step(const StepPlan& plan, const TileMap& tiles, cudaStream_t stream);
+
+// Enqueues a one-thread kernel whose bounded wait runs out after `polls` polls and records kStatusPipeTimeout (test aid
+// for the timeout -> status word -> host error path; nothing faults or hangs).
+TIB_EXPORT cudaError_t selftest_bounded_wait(cudaStream_t stream, unsigned int polls);
 
 // Reads and clears the device status word set by a kernel whose bounded wait ran out
 // (0 = healthy).  Synchronises `stream` first.

@@ -208,6 +208,8 @@ struct ti_llm_model {
     if (const char* v = std::getenv("TINYINFER_B200_SPECULATE")) { spec_after = std::atoi(v); speculate = spec_after > 0; }
     d_argmax = dev<uint8_t>(size_t(12) * opt.max_batch + 8);
     ck(cudaMemsetAsync(d_argmax, 0, size_t(12) * opt.max_batch + 8, stream));
+    d_best = dev<unsigned long long>(64);
+    ck(cudaMemsetAsync(d_best, 0, 64 * sizeof(unsigned long long), stream));
     d_log = dev<int32_t>(size_t(opt.capacity) * opt.max_batch); h_log = host<int32_t>(size_t(opt.capacity) * opt.max_batch);
     if (const char* v = std::getenv("TINYINFER_B200_GRAPH")) use_graph = std::atoi(v) != 0;   // debugging aids: 0 = plain launches
     if (const char* v = std::getenv("TINYINFER_B200_PDL")) use_pdl = std::atoi(v) != 0;
@@ -230,7 +232,10 @@ struct ti_llm_model {
 
   // ------------------------------------------------------------ persistent decode step
   // One launch per greedy step for up to 32 requests (decode_step.cuh) instead of the 65-kernel graph; same bits.
-  tib::StepPlan plan; tib::TileMap plan_tiles; bool plan_ready = false, use_persistent = true;
+  // Off unless selected (ti_b200_llm_decode_plan, TINYINFER_B200_PERSISTENT=1): measured on a B200 it trails the graph of
+  // separate kernels at every batch size (its GEMM items span the whole K, six to twelve dequantisation stages on one SM
+  // where the separate kernels split K over a cluster), so it is kept as the second, bit-identical plan.
+  tib::StepPlan plan; tib::TileMap plan_tiles; bool plan_ready = false, use_persistent = false;
   uint8_t* plan_words = nullptr; size_t plan_words_bytes = 0;     // the tagged exchange buffers, one allocation
   uint64_t plan_epochs = 0;                                        // launches since the buffers were last cleared
 
@@ -320,8 +325,9 @@ struct ti_llm_model {
   // ln_g / ln_b: LayerNorm applied to `a` inside the GEMM (decode-sized calls only, see fuse_ln).
   void gemm(const void* a, const Linear& l, void* out, int rows, bool fp32, const void* residual, bool gelu,
             const tib::PagedKv* kv = nullptr, const int32_t* row_req = nullptr, const int32_t* row_pos = nullptr,
-            const void* ln_g = nullptr, const void* ln_b = nullptr) {
+            const void* ln_g = nullptr, const void* ln_b = nullptr, void* argmax_best = nullptr, bool skip_store = false) {
     tib::GemmCall c;
+    c.argmax_best = argmax_best; c.skip_store = skip_store;
     c.kv = kv; c.kv_row_req = row_req; c.kv_row_pos = row_pos; c.ln_gamma = ln_g; c.ln_beta = ln_b;
     c.a = a; c.lda = l.k; c.w = l.w; c.ldw = l.ldw; c.w_slab_rows = l.slab_rows; c.w_int8 = int8; c.scales = l.scales; c.bias = l.bias;
     c.out = out; c.ldo = fp32 ? vpitch : l.n; c.out_fp32 = fp32; c.residual = residual; c.gelu = gelu;
@@ -445,9 +451,10 @@ struct ti_llm_model {
   // written straight into ids[] (next step's input) and into d_log[step][request]; a last small
   // kernel advances positions, lengths and the counter.  Nothing returns to the host between steps,
   // so a step can be replayed as a CUDA graph; graphs are cached per (batch, attention chunk count).
-  struct StepGraph { int batch, chunks; cudaGraphExec_t exec; };
+  struct StepGraph { int batch, chunks; bool logits; cudaGraphExec_t exec; };
   std::vector<StepGraph> graphs;
   uint8_t* d_argmax = nullptr;      // per-row merge words of the argmax kernel (zero between launches)
+  unsigned long long* d_best = nullptr;   // per-row merge words of the argmax fused into the vocabulary projection (zero between steps)
   // Speculative continuation of step-by-step decoding through ti_llm_forward_batch: once a caller has fed back the
   // model's own outputs for the same slots `spec_after` times in a row, the next step is launched from the state that
   // is already on the GPU before the call returns; the following call only checks that it asks for exactly that step
@@ -481,32 +488,40 @@ struct ti_llm_model {
 
   int32_t* seg(int field) const { return d_seg + size_t(field) * opt.max_batch; }
 
-  void enqueue_step(int batch, int max_kv) {
+  // want_logits: the fp32 logits are stored too (a caller asked for them); the greedy argmax is merged by the vocabulary
+  // projection itself either way (int8 weights: the tensor-core kernel), so a greedy step never reads logits back.
+  void enqueue_step(int batch, int max_kv, bool want_logits) {
     Meta m{};
     m.ids = seg(0); m.row_req = seg(1); m.row_pos = seg(2); m.kvlens = seg(3); m.slots = seg(4);
     m.rows = batch; m.batch = batch; m.max_q = 1; m.max_kv = max_kv;
     run_layers(m);
     tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl;
-    if (fuse_ln && shape.hidden <= 768 && batch <= std::min(fuse_ln_rows, 8)) gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b);
+    void* best = int8 ? d_best : nullptr;
+    const bool skip = best && !want_logits;
+    if (fuse_ln && shape.hidden <= 768 && batch <= std::min(fuse_ln_rows, 8))
+      gemm(x, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, lnf_g, lnf_b, best, skip);
     else {
       ck(tib::layernorm(x, nullptr, lnf_g, lnf_b, last, batch, shape.hidden, 1e-5f, ln_opts()));
-      gemm(last, head, logits, batch, true, nullptr, false);
+      gemm(last, head, logits, batch, true, nullptr, false, nullptr, nullptr, nullptr, nullptr, nullptr, best, skip);
     }
-    ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_log, seg(0), d_step, d_argmax, o));
-    ck(tib::advance(seg(2), seg(3), d_step, batch, o));
+    if (best) ck(tib::argmax_finish(best, batch, shape.vocab, d_log, seg(0), d_step, seg(2), seg(3), o));
+    else {
+      ck(tib::argmax(logits, vpitch, batch, shape.vocab, d_log, seg(0), d_step, d_argmax, o));
+      ck(tib::advance(seg(2), seg(3), d_step, batch, o));
+    }
   }
 
-  cudaGraphExec_t step_graph(int batch, int chunks) {
-    for (const StepGraph& g : graphs) if (g.batch == batch && g.chunks == chunks) return g.exec;
+  cudaGraphExec_t step_graph(int batch, int chunks, bool want_logits = false) {
+    for (const StepGraph& g : graphs) if (g.batch == batch && g.chunks == chunks && g.logits == want_logits) return g.exec;
     cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
     ck(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
-    try { enqueue_step(batch, chunks * kDecodeChunk); }
+    try { enqueue_step(batch, chunks * kDecodeChunk, want_logits); }
     catch (...) { cudaStreamEndCapture(stream, &graph); if (graph) cudaGraphDestroy(graph); throw; }
     ck(cudaStreamEndCapture(stream, &graph));
     const cudaError_t st = cudaGraphInstantiate(&exec, graph, 0);
     cudaGraphDestroy(graph);
     ck(st);
-    graphs.push_back({batch, chunks, exec});
+    graphs.push_back({batch, chunks, want_logits, exec});
     return exec;
   }
 
@@ -534,10 +549,10 @@ struct ti_llm_model {
     if (persistent_step(batch)) {
       for (int i = 0; i < steps; ++i) launch_persistent(batch, want_logits);
     } else if (use_graph) {
-      cudaGraphExec_t exec = step_graph(batch, chunks);
+      cudaGraphExec_t exec = step_graph(batch, chunks, want_logits);
       for (int i = 0; i < steps; ++i) ck(cudaGraphLaunch(exec, stream));
     } else {
-      for (int i = 0; i < steps; ++i) enqueue_step(batch, chunks * kDecodeChunk);
+      for (int i = 0; i < steps; ++i) enqueue_step(batch, chunks * kDecodeChunk, want_logits);
     }
     if (after) ck(cudaEventRecord(after, stream));
     ck(cudaMemcpyAsync(h_log, d_log, size_t(steps) * batch * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
@@ -545,6 +560,7 @@ struct ti_llm_model {
   }
 
   // ------------------------------------------------------------ ABI bodies
+  int fail_after = -1;                               // test hook (ti_b200_llm_inject_failure): forward calls left before one fails
   void forward(const int32_t* s, const int32_t* tokens, const int32_t* lens, int batch, int stride, float* out, int32_t* greedy,
                bool internal = false) {
     ensure_usable();
@@ -565,6 +581,7 @@ struct ti_llm_model {
         packed.push_back(id);
       }
     }
+    if (fail_after >= 0 && fail_after-- == 0) throw GpuFailure("injected execution failure (test hook)");   // after validation, like a failed launch
     if (single && greedy) {
       // One token per request and the argmax wanted: one device-resident step -- already under way if this call
       // continues the previous one exactly (see Speculation).
@@ -826,6 +843,15 @@ int ti_b200_llm_decode_steps(ti_llm_model* m, const int32_t* slots, const int32_
     cudaEventDestroy(before); cudaEventDestroy(after);
     if (out_tokens) std::memcpy(out_tokens, m->h_log, size_t(steps) * batch * sizeof(int32_t));
     for (int i = 0; i < batch; ++i) m->lengths[size_t(slots[i])] += steps;
+  });
+}
+
+// Declared in include/tinyinfer_b200_ext.h: test hook for the failure paths.
+int ti_b200_llm_inject_failure(ti_llm_model* m, int32_t kind, int32_t after_calls) {
+  return guarded(m, [&] {
+    if (kind == 0 && after_calls >= 0) m->fail_after = after_calls;
+    else if (kind == 1) ck(tib::selftest_bounded_wait(m->stream, 1000));
+    else throw InvalidInput("inject failure: kind 0 (host, after N valid forward calls) or 1 (device wait that runs out)");
   });
 }
 

@@ -36,12 +36,6 @@ embed_kernel(const int32_t* ids, const int32_t* row_pos, const __half* wte, cons
 // publishes (value, index) packed into one 64-bit word through atomicMax on best[r]; the CTA that takes
 // the last ticket of the row writes the result and leaves best[r] and tickets[r] at zero again.
 // `best` / `tickets`: rows words each, zero before the first launch; unused with one segment.
-__device__ __forceinline__ unsigned long long argmax_pack(float v, int index) {
-  const uint32_t u = __float_as_uint(v + 0.f);                      // -0 -> +0: equal values must compare equal
-  const uint32_t ordered = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-  return (unsigned long long)ordered << 32 | (0xffffffffu - uint32_t(index));
-}
-
 __global__ void __launch_bounds__(256)
 argmax_kernel(const float* logits, long long pitch, int cols, int32_t* out, int32_t* feedback, const int32_t* step,
               unsigned long long* best, unsigned int* tickets) {
@@ -149,6 +143,42 @@ __global__ void quant_apply_kernel(const __half* w, const float* scales, int8_t*
   if (i >= elements) return;
   const double v = rint(double(h2f(w[i])) / double(scales[i % cols]));      // rint: to nearest, ties to even
   q[i] = int8_t(v < -127.0 ? -127.0 : v > 127.0 ? 127.0 : v);
+}
+
+// Last kernel of a decode step whose vocabulary projection merged the argmax itself (GemvArgs::argmax_best): publishes
+// the winners (out[step][row], feedback[row] = next step's input id), leaves `best` zero again and moves every request
+// one position on -- the work of argmax_kernel's last ticket and of advance_kernel.  One block of 64 threads, rows <= 64.
+__global__ void __launch_bounds__(64)
+argmax_finish_kernel(unsigned long long* best, int rows, int cols, int32_t* out, int32_t* feedback, int32_t* step,
+                     int32_t* row_pos, int32_t* kv_lengths) {
+  pdl_wait();
+  const int r = threadIdx.x, s = *step;
+  __syncthreads();                                              // everybody has read the counter before it moves
+  if (r < rows) {
+    const unsigned long long key = best[r];
+    best[r] = 0ull;
+    const int bi = key ? int(0xffffffffu - uint32_t(key)) : 0x7fffffff;
+    out[size_t(s) * rows + r] = bi;
+    feedback[r] = bi < cols ? bi : 0;                           // see argmax_kernel
+    if (bi >= cols) report(kStatusNoToken);
+    row_pos[r] += 1; kv_lengths[r] += 1;
+  }
+  if (r == 0) *step = s + 1;
+  pdl_launch_dependents();
+}
+
+// Self-test of the bounded waits: one thread waits on an mbarrier nobody ever arrives on, gives up after `polls` polls
+// (microseconds), records kStatusPipeTimeout in the device status word exactly as the pipelines do, and returns.  Nothing
+// faults and nothing hangs; the host sees the status at its next synchronisation.
+__global__ void bounded_wait_selftest_kernel(unsigned int polls) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    bool arrived = false;
+    for (unsigned int spin = 0; spin < polls && !arrived; ++spin) arrived = mbar_try(&bar, 0);
+    if (!arrived) report(kStatusPipeTimeout);
+  }
 }
 
 // End of a device-resident decode step: every request moves one position on.

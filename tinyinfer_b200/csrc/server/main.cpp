@@ -60,6 +60,9 @@ struct Config {
   int port = 8091, max_batch = 8, max_wait_us = 1000, capacity = 1024, max_new = 128, max_pending = 256, max_connections = 256;
   int per_connection = 32, max_output = 1 << 20, max_ids = 100000, send_chunk = 65536, gemm = 0, attention = 0;
   bool native = false;
+  // test hook: worker number fail_worker fails its model call number fail_after_steps (0 = never), as a native execution
+  // failure would; exercises the poisoned-worker path without touching a GPU
+  int fail_worker = 0, fail_after_steps = 0;
   std::vector<int> devices{0};
   std::string manifest, host = "127.0.0.1";
 };
@@ -70,7 +73,8 @@ Config parse_options(int argc, char** argv) {
       {"port", &c.port}, {"max-batch", &c.max_batch}, {"max-wait-us", &c.max_wait_us}, {"capacity", &c.capacity},
       {"max-new-tokens", &c.max_new}, {"max-pending", &c.max_pending}, {"max-connections", &c.max_connections},
       {"per-connection", &c.per_connection}, {"max-output-bytes", &c.max_output}, {"max-ids", &c.max_ids},
-      {"send-chunk-bytes", &c.send_chunk}, {"gemm-config", &c.gemm}, {"attention-config", &c.attention}};
+      {"send-chunk-bytes", &c.send_chunk}, {"gemm-config", &c.gemm}, {"attention-config", &c.attention},
+      {"fail-worker", &c.fail_worker}, {"fail-after-steps", &c.fail_after_steps}};
   auto integer = [](const std::string& text) {
     size_t used = 0;
     const int v = std::stoi(text, &used);
@@ -103,7 +107,7 @@ Config parse_options(int argc, char** argv) {
       c.max_connections < 1 || c.max_connections > 100000 || c.per_connection < 1 || c.per_connection > c.max_pending ||
       c.max_output < 64 || c.max_output > 64 * 1024 * 1024 || c.max_ids < 1 || c.max_ids > 1000000 || c.send_chunk < 1 ||
       c.send_chunk > 1048576 || c.gemm < 0 || c.gemm > 11 || c.attention < 0 || c.attention > 1 || !devices_ok ||
-      (c.native && c.manifest.empty()))
+      (c.native && c.manifest.empty()) || c.fail_worker < 0 || c.fail_worker >= int(c.devices.size()) || c.fail_after_steps < 0)
     throw std::runtime_error("option range");
   return c;
 }
@@ -111,7 +115,8 @@ Config parse_options(int argc, char** argv) {
 // ---------------------------------------------------------------------------------- model replica
 class Replica {
  public:
-  Replica(const Config& c, int device) : native_(c.native), capacity_(c.capacity), lengths_(size_t(c.max_batch), 0), last_(size_t(c.max_batch), 0) {
+  Replica(const Config& c, int device, int fail_after = 0)
+      : native_(c.native), capacity_(c.capacity), fail_after_(fail_after), lengths_(size_t(c.max_batch), 0), last_(size_t(c.max_batch), 0) {
     if (!native_) return;
     if (ti_llm_abi_version() != 1) throw std::runtime_error("ti_llm ABI mismatch");
     ti_llm_options o{sizeof(ti_llm_options), device, c.max_batch, c.max_batch, c.capacity, c.gemm, c.attention};
@@ -128,6 +133,7 @@ class Replica {
   // Appends rows[i] to slots[i]; returns the greedy next id of every row.
   std::vector<int32_t> step(const std::vector<int32_t>& slots, const std::vector<const std::vector<int32_t>*>& rows) {
     std::vector<int32_t> next(slots.size());
+    if (fail_after_ > 0 && ++calls_ == fail_after_) throw std::runtime_error("injected model failure (test hook)");
     if (native_) {
       size_t stride = 0;
       for (auto* row : rows) stride = std::max(stride, row->size());
@@ -163,7 +169,7 @@ class Replica {
  private:
   void check(int status) { if (status) throw std::runtime_error(ti_llm_last_error()); }
   bool native_;
-  int capacity_;
+  int capacity_, fail_after_ = 0, calls_ = 0;
   std::vector<int> lengths_;
   std::vector<int32_t> last_, tokens_, lens_;
   ti_llm_model* model_ = nullptr;
@@ -186,7 +192,8 @@ class Server;
 class Worker {
  public:
   Worker(Server& server, const Config& c, int index, int device) : server_(server), config_(c), index_(index), device_(device) {}
-  void load() { replica_ = std::make_unique<Replica>(config_, device_); }
+  void load() { replica_ = std::make_unique<Replica>(config_, device_, index_ == config_.fail_worker ? config_.fail_after_steps : 0); }
+  bool healthy() const { return !poisoned_flag_.load(std::memory_order_relaxed); }
   void start() { thread_ = std::thread([this] { run(); }); }
   void join() { if (thread_.joinable()) thread_.join(); }
   void submit(std::shared_ptr<Job> job) {
@@ -223,6 +230,7 @@ class Worker {
   std::condition_variable signal_;
   std::deque<std::shared_ptr<Job>> waiting_;
   bool poisoned_ = false;
+  std::atomic<bool> poisoned_flag_{false};           // what the router sees
 };
 
 // ---------------------------------------------------------------------------------- socket front end
@@ -431,6 +439,7 @@ void Worker::run() noexcept {
       // arrives later on this worker is answered with an internal error; the process stays up.
       std::cerr << "model_poisoned: device " << device_ << ": " << error.what() << '\n';
       poisoned_ = true;
+      poisoned_flag_.store(true, std::memory_order_relaxed);
       for (size_t slot = 0; slot < slots; ++slot) if (active[slot]) retire(slot, kInternal);
     }
   }
@@ -458,8 +467,14 @@ void Server::on_frame(int fd, Bytes body) {
   }
   auto job = std::make_shared<Job>();
   job->fd = fd; job->connection = c.token; job->wire = std::move(wire); job->accepted = Clock::now();
+  // fewest outstanding tokens among the workers whose model still works; a poisoned worker (it answers everything with an
+  // internal error at once, so it always looks idle) only gets requests when no healthy one is left
   size_t best = 0;
-  for (size_t i = 1; i < workers_.size(); ++i) if (workers_[i]->load_tokens() < workers_[best]->load_tokens()) best = i;
+  for (size_t i = 1; i < workers_.size(); ++i) {
+    const bool better_health = workers_[i]->healthy() && !workers_[best]->healthy();
+    const bool same_health = workers_[i]->healthy() == workers_[best]->healthy();
+    if (better_health || (same_health && workers_[i]->load_tokens() < workers_[best]->load_tokens())) best = i;
+  }
   job->worker = int(best);
   c.active.emplace(job->wire.id, job);
   ++outstanding_;

@@ -9,6 +9,7 @@ from __future__ import annotations
 import struct
 
 VERSION, GENERATE, CANCEL, FINAL, FIRST = 1, 1, 2, 0x8001, 0x8002
+OK, INVALID, OVERLOADED, CANCELLED, INTERNAL = 0, 1, 2, 3, 4            # response status (server/include/protocol.hpp:33-45)
 REQUEST = struct.Struct("!HHQII")
 RESPONSE = struct.Struct("!HHQIIIIQQQQ")
 MAX_RESPONSE = 60 + 4 * 1024
