@@ -396,6 +396,71 @@ def config3_record(device):
             "decode_plan": "persistent step" if plan == 1 else "launch per operation"}
 
 
+def server_record(torch, dist, rank, world, manifest_path, model_kind, requests, rate):
+    """The batching-server workload (4096 requests, Poisson arrivals, prompts log-uniform in [8, 900], outputs uniform in
+    [16, 256], seed 4) against ONE tinyinfer_server process that owns all `world` GPUs (one worker and one model replica
+    per GPU, requests routed to the worker with the fewest outstanding tokens).  Rank 0 starts the server; every rank
+    plays an equal share of the request stream through its own asyncio load generator; totals are summed, latency samples
+    merged.  `rate` is far above what the GPUs sustain, so the requests queue at the server: a saturating load.
+    model_kind "cpu" swaps the GPU model for the protocol stand-in (a token counter) and so measures the ceiling of the
+    host side alone: socket front end, router, load generators."""
+    import asyncio
+    import socket
+    from tinyinfer_b200 import replicas
+    from tinyinfer_b200.server import binary, loadgen
+    box, proc = [None], None
+    if rank == 0:
+        with socket.socket() as probe:
+            probe.bind(("127.0.0.1", 0))
+            port = probe.getsockname()[1]
+        cmd = [str(binary()), "--model", model_kind, "--port", str(port), "--devices", ",".join(map(str, range(world))),
+               "--max-batch", "64", "--max-wait-us", "2000", "--max-new-tokens", "256", "--max-pending", "8192",
+               "--max-connections", "8192", "--per-connection", "32"]
+        if model_kind == "native":
+            cmd += ["--manifest", str(manifest_path)]
+        proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+        ready = proc.stdout.readline()
+        box[0] = port if ready and json.loads(ready).get("ready") else -1
+    if dist:
+        dist.broadcast_object_list(box, src=0)
+    port = box[0]
+    result = None
+    if port > 0:
+        items = loadgen.workload(4, rate, requests)
+        mine = replicas.shard(items, rank, world)
+        if dist:
+            dist.barrier()
+        records, start = asyncio.run(loadgen.run_items("127.0.0.1", port, mine, outstanding=4096))
+        done = [r for r in records if r.get("status") == 0]
+        share = {"tokens": sum(r["tokens"] for r in done), "window": max((r["finished_at"] for r in done), default=start) - start,
+                 "completed": len(done), "offered": len(mine), "batch": sum(r["batch_size"] for r in done),
+                 "per_token_ms": [r["decode_s"] / (r["tokens"] - 1) * 1e3 for r in done if r["tokens"] > 1],
+                 "ttft_ms": [r["ttft_s"] * 1e3 for r in done]}
+        shares = [share]
+        if dist:
+            shares = [None] * world
+            dist.all_gather_object(shares, share)
+        if rank == 0:
+            tokens, window = sum(x["tokens"] for x in shares), max(x["window"] for x in shares)
+            completed = sum(x["completed"] for x in shares)
+            per_token = [v for x in shares for v in x["per_token_ms"]]
+            ttft = [v for x in shares for v in x["ttft_ms"]]
+            result = {"model": model_kind, "gpus": world, "requests": requests, "completed": completed, "offered_rate_per_s": rate,
+                      "generated_tokens": tokens, "tokens_per_s": tokens / window if window > 0 else 0.0, "drain_window_s": window,
+                      "mean_batch_size": sum(x["batch"] for x in shares) / max(1, completed),
+                      "per_output_token_ms": loadgen.summarise(per_token), "ttft_ms": loadgen.summarise(ttft),
+                      "load_generators": world, "max_batch_per_gpu": 64}
+    if dist:
+        dist.barrier()
+    if proc is not None:
+        proc.terminate()
+        try:
+            proc.communicate(timeout=20)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+    return result
+
+
 def gpu_main(args, rank, world):
     torch, dist, local = setup_ranks()
 
@@ -510,6 +575,12 @@ def gpu_main(args, rank, world):
                 extras["other_decode_plan"] = {"unavailable": str(error)}
             model.decode_plan(1 if persistent else 0)
 
+    # ---- the batching server on all N GPUs (after this process's own replica is gone), then its host side alone
+    server = {}
+    if not args.no_server:
+        server["native"] = server_record(torch, dist, rank, world, manifest_path, "native", 4096, 4000.0 * world)
+        server["host_side_ceiling"] = server_record(torch, dist, rank, world, manifest_path, "cpu", 4096, 4000.0 * world)
+
     line = {"metric": "int8_gpt2_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": device_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations x int8 weights, f32 accumulate",
             "data": "synthetic", "config": config_block(world), "prefill_ttft_ms": ttft_ms,
@@ -527,6 +598,9 @@ def gpu_main(args, rank, world):
         line["step_roofline"] = {"bound": "hbm", "achieved": per_gpu_gbs, "peak": peak, "unit": "GB/s", "frac": per_gpu_gbs / peak,
                                  "bytes_per_step": total_bytes / K, "note": "algorithmic weight+KV bytes per step / step time, per GPU"}
         line.update(extras)
+        if server:
+            line["server"] = server["native"]
+            line["server_host_side_ceiling"] = server["host_side_ceiling"]
         if world == 1 and not args.no_extras:
             cached_at_start = [len(p) + W for p in prompts]
             kernels = kernel_rooflines(cached_at_start, peak)
@@ -557,6 +631,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=7)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    parser.add_argument("--no-server", action="store_true", help="skip the batching-server workload")
     parser.add_argument("--no-extras", action="store_true", help="skip config 0, config 3, the operator kernels and the sweep excerpt")
     parser.add_argument("--plan", type=int, choices=[0, 1], default=None, help="decode plan: 1 persistent step (default where supported), 0 launch per operation")
     parser.add_argument("--quick", action="store_true", help="only the device-resident timed steps (for profilers)")

@@ -295,3 +295,34 @@ def test_attention_accepts_tensors_that_are_only_two_byte_aligned(ops, d):
     assert status == 0, ops.lib.ti_v2_last_error()
     torch.cuda.synchronize()
     assert torch.equal(out, want)
+
+
+TC_ATTN_CASES = [(200, 300, [200, 77], [300, 150], [100, 73], True), (1024, 1024, [1024, 1000], [1024, 1000], [0, 0], True),
+                 (130, 257, [130, 64], [257, 0], [0, 0], False), (64, 64, [64, 1], [64, 64], [0, 63], True),
+                 (300, 700, [300, 5], [650, 700], [350, 695], True)]
+
+
+@pytest.mark.parametrize("nq,nk,ql,kl,off,causal", TC_ATTN_CASES)
+def test_attention_with_many_query_rows_runs_on_tensor_cores_and_matches(ops, ref, nq, nk, ql, kl, off, causal):
+    """64 or more query rows of 64-wide heads take the tcgen05 attention kernel: against the reference's kernel and the
+    CPU oracle (same gate, atol = rtol = 0.02), all-masked and padding rows exact zeros, and a request's rows do not
+    depend on the other request in the call."""
+    torch.manual_seed(nq + nk)
+    q = (torch.randn((2, 3, nq, 64), device="cuda") * 0.5).half()
+    k = (torch.randn((2, 3, nk, 64), device="cuda") * 0.5).half()
+    v = torch.randn_like(k)
+    out = ops.attention(q, k, v, q_lengths=ql, kv_lengths=kl, query_offsets=off, causal=causal)
+    close(out, ref.attention(q, k, v, q_lengths=ql, kv_lengths=kl, query_offsets=off, causal=causal))
+    if nq * nk <= 300 * 700:
+        want = orc.attention(q.cpu().numpy(), k.cpu().numpy(), v.cpu().numpy(), ql, kl, off, causal)
+        close(out, want.astype(np.float32))
+    qi = torch.arange(nq, device="cuda")[None, :, None]
+    ki = torch.arange(nk, device="cuda")[None, None, :]
+    mask = (qi < torch.tensor(ql, device="cuda")[:, None, None]) & (ki < torch.tensor(kl, device="cuda")[:, None, None])
+    if causal:
+        mask = mask & (ki <= torch.tensor(off, device="cuda")[:, None, None] + qi)
+    dead = ~mask.any(dim=-1)[:, None, :, None].expand_as(out)
+    assert out[dead].count_nonzero().item() == 0
+    alone = ops.attention(q[:1].contiguous(), k[:1].contiguous(), v[:1].contiguous(), q_lengths=ql[:1], kv_lengths=kl[:1],
+                          query_offsets=off[:1], causal=causal)
+    assert torch.equal(alone[0], out[0])

@@ -62,6 +62,7 @@ struct AttnArgs {
   const int32_t* q_lengths; const int32_t* kv_lengths; const int32_t* offsets;
   int batch, heads, q_len, kv_len, causal;
   int skip_single;                                 // requests with exactly one query row are left to the decode kernel
+  int skip_min_q;                                  // > 0: requests with at least this many query rows are left to the tensor-core kernel
 };
 
 // ------------------------------------------------------------------ tiled kernel (Q >= 1)
@@ -91,6 +92,7 @@ attn_tile_kernel(const AttnArgs p, const KV kv) {
   pdl_wait();
   const int q_valid = max(0, min(p.q_len, p.q_lengths[b]));
   if (p.skip_single && p.q_lengths[b] == 1) return;               // uniform per CTA; nothing is written for this request here
+  if (p.skip_min_q && p.q_lengths[b] >= p.skip_min_q) return;
   const int kv_valid = max(0, min(p.kv_len, p.kv_lengths[b]));
   const long long off = p.offsets[b];
   const long long q_base = p.row_start ? p.row_start[b] * p.q_si : b * p.q_sb;

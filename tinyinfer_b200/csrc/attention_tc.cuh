@@ -1,0 +1,214 @@
+// Ragged causal attention for many query rows per request (prefill) on the sm_100a tensor cores.
+//
+// Same semantics as attn_tile_kernel / the reference's online_attention (kernels/src/cuda/tc/attention.cu:9-57): key j
+// is visible to query i of request b when j < min(kv_len, kv_lengths[b]) and (!causal || j <= offsets[b] + i); scores
+// q.k * rsqrt(64); fp32 online softmax; rows that see no key are exact zeros.  What changes is where the two
+// contractions run: one CTA owns 128 query rows of one (request, head) and walks the keys 64 at a time,
+//   S[128 x 64] = Q . K^T        tcgen05.mma kind::f16, both operands K-major in shared memory, accumulator in TMEM
+//   P = exp(S - max) (fp16)      one thread per query row: the row of S comes out of TMEM with tcgen05.ld, so the row
+//                                maximum and the row sum need no shuffles
+//   PV[128 x 64] = P . V         tcgen05.mma with P K-major and V as it is stored (head dimension contiguous = MN-major)
+//   O = O * alpha + PV           in registers (64 fp32 per thread)
+// The probabilities enter the second contraction rounded to fp16 (the reference multiplies fp32 p by fp16 v); the
+// difference is far inside the operator gate (atol = rtol = 0.02).  A row's result depends on its own keys only -- key
+// tiles start at key 0 whatever the query tile -- so it does not change with the batch or with the chunking of a prompt.
+// Head dimension 64 only; other shapes stay on the SIMT kernel.
+#pragma once
+#include <math_constants.h>
+
+#include "attention.cuh"
+#include "common.cuh"
+#include "gemm_tc.cuh"
+
+namespace tib {
+
+constexpr int kAttnTcRows = 128;      // query rows per CTA = TMEM lanes
+constexpr int kAttnTcKeys = 64;       // keys per step
+constexpr int kAttnTcMinRows = 64;    // requests with fewer query rows stay on the SIMT kernel (model runtime)
+
+struct AttnTcSmem {
+  static constexpr int kQOff = 0;                                   // Q  [128 x 64]  K-major core matrices, 16 KB
+  static constexpr int kKOff = kQOff + kAttnTcRows * 64 * 2;        // K  [64 keys x 64]  K-major, 8 KB
+  static constexpr int kVOff = kKOff + kAttnTcKeys * 64 * 2;        // V  [64 keys x 64]  MN-major (d contiguous), 8 KB
+  static constexpr int kPOff = kVOff + kAttnTcKeys * 64 * 2;        // P  [128 x 64 keys]  K-major, 16 KB
+  static constexpr int kBytes = kPOff + kAttnTcRows * kAttnTcKeys * 2;
+};
+
+// 32 lanes x 32 columns twice: one row of a 64-column accumulator
+__device__ __forceinline__ void tmem_load64(uint32_t taddr, float (&v)[64]) {
+  float lo[32], hi[32];
+  tmem_load32(taddr, lo);
+  tmem_load32(taddr + 32u, hi);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { v[i] = lo[i]; v[32 + i] = hi[i]; }
+}
+
+// grid = (ceil(max query rows / 128), heads, batch), block = 128.  min_q: requests with fewer rows are skipped (another
+// kernel serves them); 0 = serve every request.
+template <typename KV>
+__global__ void __launch_bounds__(kAttnTcRows, 2)
+attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
+  using L = AttnTcSmem;
+  extern __shared__ __align__(128) uint8_t attn_tc_smem[];
+  uint8_t* qs = attn_tc_smem + L::kQOff;
+  uint8_t* ks = attn_tc_smem + L::kKOff;
+  uint8_t* vs = attn_tc_smem + L::kVOff;
+  uint8_t* ps = attn_tc_smem + L::kPOff;
+  __shared__ __align__(8) uint64_t mma_done;
+  __shared__ uint32_t tmem_slot;
+  constexpr int D = 64;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int h = blockIdx.y, b = blockIdx.z, q0 = blockIdx.x * kAttnTcRows;
+  pdl_wait();
+  const int q_len_b = p.q_lengths[b];
+  const int q_valid = max(0, min(p.q_len, q_len_b));
+  if (q_len_b < min_q || q0 >= (p.row_start ? q_valid : p.q_len)) return;          // uniform per CTA
+  const int kv_valid = max(0, min(p.kv_len, p.kv_lengths[b]));
+  const long long off = p.offsets[b];
+  const long long q_base = p.row_start ? p.row_start[b] * p.q_si : b * p.q_sb;
+  const long long o_base = p.row_start ? p.row_start[b] * p.o_si : b * p.o_sb;
+  const int qi = q0 + tid;                                      // this thread's query row
+  const bool active = qi < q_valid;
+  const int last_query = min(q_valid, q0 + kAttnTcRows) - 1;
+  long long bound = p.causal ? off + last_query + 1 : (long long)kv_valid;
+  const int key_end = last_query < q0 || bound < 0 ? 0 : int(bound < (long long)kv_valid ? bound : (long long)kv_valid);
+  const long long my_last = p.causal ? off + qi : (long long)kv_valid - 1;
+
+  if (tid == 0) { mbar_init(&mma_done, 1); mbar_fence_init(); }
+  if (warp == 0) tmem_alloc(&tmem_slot, 128);
+  // Q rows -> K-major core matrices: (k chunk kc, row group mg) at (kc * 16 + mg) * 128, row m % 8 at 16 bytes each
+  {
+    const __half* src = p.q + q_base + h * p.q_sh + (long long)qi * p.q_si;
+#pragma unroll
+    for (int kc = 0; kc < D / 8; ++kc) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (active) v = load8<true>(src + kc * 8);
+      *reinterpret_cast<uint4*>(qs + (kc * (kAttnTcRows / 8) + (tid >> 3)) * 128 + (tid & 7) * 16) = v;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const uint32_t lane_addr = tmem_base + (uint32_t(32 * warp) << 16);
+  // instruction descriptors: fp32 accumulate, fp16 operands, M = 128, N = 64; S: both K-major; PV: B (= V) MN-major
+  constexpr uint32_t idesc_s = (1u << 4) | (uint32_t(kAttnTcKeys >> 3) << 17) | (uint32_t(kAttnTcRows >> 4) << 24);
+  constexpr uint32_t idesc_pv = idesc_s | (1u << 16);
+
+  float m = -CUDART_INF_F, l = 0.f, o[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) o[d] = 0.f;
+  uint32_t phase = 0;
+  bool ok = true;
+
+  for (int k0 = 0; k0 < key_end; k0 += kAttnTcKeys) {
+    // ---- K and V tile -> shared memory (zeros past key_end).  64 keys x 8 chunks of 8 values, 4 chunks per thread each.
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + kAttnTcRows * it, r = idx >> 3, c = idx & 7, key = k0 + r;
+      uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
+      if (key < key_end) {
+        const size_t at = kv.offset(b, h, key) + c * 8;
+        kk = load8<true>(kv.k + at);
+        vv = load8<true>(kv.v + at);
+      }
+      // K as the B operand of S, K-major: (d chunk c, key group r / 8) at (c * 8 + r / 8) * 128, key r % 8 at 16 bytes each
+      *reinterpret_cast<uint4*>(ks + (c * (kAttnTcKeys / 8) + (r >> 3)) * 128 + (r & 7) * 16) = kk;
+      // V as the B operand of PV, MN-major (d contiguous): (key group r / 8, d chunk c) at ((r / 8) * 8 + c) * 128, key r % 8
+      *reinterpret_cast<uint4*>(vs + ((r >> 3) * (D / 8) + c) * 128 + (r & 7) * 16) = vv;
+    }
+    fence_async_smem();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint64_t da = tc_desc(smem_u32(qs) + kk * 2 * (kAttnTcRows / 8) * 128, (kAttnTcRows / 8) * 128, 128);
+        const uint64_t db = tc_desc(smem_u32(ks) + kk * 2 * (kAttnTcKeys / 8) * 128, (kAttnTcKeys / 8) * 128, 128);
+        tc_mma_f16(tmem_base, da, db, idesc_s, kk > 0 ? 1u : 0u);
+      }
+      tc_commit(&mma_done);
+    }
+    if (ok) ok = mbar_wait(&mma_done, phase, kStatusMmaTimeout);
+    ok = __all_sync(0xffffffffu, ok);                         // tcgen05.ld is warp-collective
+    phase ^= 1u;
+    tc_fence_after();
+    float s[kAttnTcKeys];
+    if (ok) tmem_load64(lane_addr, s);
+    // ---- online softmax of this row
+    float tile_max = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < kAttnTcKeys; ++j) {
+      const int key = k0 + j;
+      const bool visible = ok && active && key < key_end && (long long)key <= my_last;
+      s[j] = visible ? s[j] * rsqrtf(float(D)) : -CUDART_INF_F;
+      tile_max = fmaxf(tile_max, s[j]);
+    }
+    const float next = fmaxf(m, tile_max);
+    const float alpha = next > -CUDART_INF_F ? expf(m - next) : 1.f;      // nothing seen yet: state stays empty
+    float tile_sum = 0.f;
+    uint32_t packed[kAttnTcKeys / 2];
+#pragma unroll
+    for (int j = 0; j < kAttnTcKeys; j += 2) {
+      const float p0 = s[j] > -CUDART_INF_F ? expf(s[j] - next) : 0.f;
+      const float p1 = s[j + 1] > -CUDART_INF_F ? expf(s[j + 1] - next) : 0.f;
+      tile_sum += p0 + p1;
+      const __half2 h2 = __floats2half2_rn(p0, p1);
+      packed[j / 2] = *reinterpret_cast<const uint32_t*>(&h2);
+    }
+    l = l * alpha + tile_sum;
+    m = next;
+    // P as the A operand of PV, K-major: (key chunk kc, row group) at (kc * 16 + tid / 8) * 128, row tid % 8
+#pragma unroll
+    for (int kc = 0; kc < kAttnTcKeys / 8; ++kc)
+      *reinterpret_cast<uint4*>(ps + (kc * (kAttnTcRows / 8) + (tid >> 3)) * 128 + (tid & 7) * 16) =
+          make_uint4(packed[4 * kc], packed[4 * kc + 1], packed[4 * kc + 2], packed[4 * kc + 3]);
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int kk = 0; kk < kAttnTcKeys / 16; ++kk) {
+        const uint64_t da = tc_desc(smem_u32(ps) + kk * 2 * (kAttnTcRows / 8) * 128, (kAttnTcRows / 8) * 128, 128);
+        const uint64_t db = tc_desc(smem_u32(vs) + kk * 2 * (D / 8) * 128, (D / 8) * 128, 128);
+        tc_mma_f16(tmem_base + 64u, da, db, idesc_pv, kk > 0 ? 1u : 0u);
+      }
+      tc_commit(&mma_done);
+    }
+    if (ok) ok = mbar_wait(&mma_done, phase, kStatusMmaTimeout);
+    ok = __all_sync(0xffffffffu, ok);
+    phase ^= 1u;
+    tc_fence_after();
+    float pv[D];
+    if (ok) {
+      tmem_load64(lane_addr + 64u, pv);
+#pragma unroll
+      for (int d = 0; d < D; ++d) o[d] = o[d] * alpha + pv[d];
+    }
+    tc_fence_before();
+    __syncthreads();                                          // the tiles and both accumulators are free again
+  }
+  pdl_launch_dependents();
+  // Padded layout (operator ABI): rows past the request's length are written as zeros.  Packed rows (row_start given): a
+  // row past the request's length belongs to another request and is left alone.
+  if (ok && (p.row_start ? active : qi < p.q_len)) {
+    __half* dst = p.out + o_base + h * p.o_sh + (long long)qi * p.o_si;
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+      uint4 packed8;
+      __half* hh = reinterpret_cast<__half*>(&packed8);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) hh[e] = f2h(l > 0.f && active ? o[c * 8 + e] / l : 0.f);
+      if ((reinterpret_cast<uintptr_t>(dst) & 15) == 0) *reinterpret_cast<uint4*>(dst + c * 8) = packed8;
+      else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) dst[c * 8 + e] = hh[e];
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, 128); }
+}
+
+}  // namespace tib

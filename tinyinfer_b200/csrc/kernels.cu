@@ -14,6 +14,7 @@
 namespace tib { __device__ unsigned int g_device_status = 0; }
 #define TIB_STATUS_DEFINED
 #include "attention.cuh"
+#include "attention_tc.cuh"
 #include "common.cuh"
 #include "decode_step.cuh"
 #include "elementwise.cuh"
@@ -318,8 +319,15 @@ cudaError_t attention_packed(const void* q, const void* k, const void* v, void* 
   p.q_lengths = ql; p.kv_lengths = kl; p.offsets = off;
   p.batch = batch; p.heads = heads; p.q_len = q_len; p.kv_len = kv_len; p.causal = causal;
   KvPacked kv{static_cast<const __half*>(k), static_cast<const __half*>(v), heads, kv_len, d};
-  const dim3 grid((q_len + kAttnTileQ - 1) / kAttnTileQ, heads, batch);
   const bool vec = (reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) % 16 == 0;
+  // Many query rows of 64-wide heads: both contractions on the tensor cores.
+  if (d == 64 && q_len >= kAttnTcMinRows && vec) {
+    const cudaError_t ready = allow_smem(attn_tc_kernel<KvPacked>, AttnTcSmem::kBytes);
+    if (ready != cudaSuccess) return ready;
+    const dim3 tc_grid((q_len + kAttnTcRows - 1) / kAttnTcRows, heads, batch);
+    return launch(attn_tc_kernel<KvPacked>, tc_grid, dim3(kAttnTcRows), AttnTcSmem::kBytes, o, 1, p, kv, 0);
+  }
+  const dim3 grid((q_len + kAttnTileQ - 1) / kAttnTileQ, heads, batch);
   if (d == 64) return vec ? launch(attn_tile_kernel<64, KvPacked, true>, grid, dim3(256), 0, o, 1, p, kv)
                           : launch(attn_tile_kernel<64, KvPacked, false>, grid, dim3(256), 0, o, 1, p, kv);
   if (d == 128) return vec ? launch(attn_tile_kernel<128, KvPacked, true>, grid, dim3(256), 0, o, 1, p, kv)
@@ -333,7 +341,8 @@ static KvPaged paged(const PagedKv& kv) {
 }
 
 cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start, const int32_t* ql, const int32_t* kl,
-                            const int32_t* off, int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& o, bool skip_single) {
+                            const int32_t* off, int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& o, bool skip_single,
+                            int long_requests, int short_requests) {
   if (kv.head_dim != 64) return cudaErrorInvalidValue;
   const int hidden = kv.heads * kv.head_dim;
   AttnArgs p{};
@@ -343,7 +352,20 @@ cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start
   p.row_start = row_start;
   p.q_lengths = ql; p.kv_lengths = kl; p.offsets = off;
   p.batch = batch; p.heads = kv.heads; p.q_len = max_q; p.kv_len = max_kv; p.causal = 1; p.skip_single = skip_single ? 1 : 0;
-  const dim3 grid((max_q + kAttnTileQ - 1) / kAttnTileQ, kv.heads, batch);
+  // Requests with at least kAttnTcMinRows rows in this pass take the tensor-core kernel, the others the SIMT tile kernel;
+  // the choice depends on the request's own row count only, never on what shares its pass.
+  if (long_requests > 0) {
+    const cudaError_t ready = allow_smem(attn_tc_kernel<KvPaged>, AttnTcSmem::kBytes);
+    if (ready != cudaSuccess) return ready;
+    const dim3 tc_grid((max_q + kAttnTcRows - 1) / kAttnTcRows, kv.heads, batch);
+    const cudaError_t st = launch(attn_tc_kernel<KvPaged>, tc_grid, dim3(kAttnTcRows), AttnTcSmem::kBytes, o, 1, p, paged(kv), kAttnTcMinRows);
+    if (st != cudaSuccess || short_requests == 0) return st;
+    p.skip_min_q = kAttnTcMinRows;
+  }
+  int short_q = max_q;
+  if (long_requests > 0) short_q = std::min(max_q, kAttnTcMinRows - 1);      // the SIMT grid only has to cover the short requests
+  p.q_len = max_q;
+  const dim3 grid((short_q + kAttnTileQ - 1) / kAttnTileQ, kv.heads, batch);
   return launch(attn_tile_kernel<64, KvPaged, true>, grid, dim3(256), 0, o, 1, p, paged(kv));
 }
 

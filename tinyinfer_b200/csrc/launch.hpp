@@ -79,7 +79,9 @@ TIB_EXPORT cudaError_t attention_packed(const void* q, const void* k, const void
 TIB_EXPORT cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start,
                                        const int32_t* q_lengths, const int32_t* kv_lengths, const int32_t* offsets,
                                        int batch, int max_q, int max_kv, const PagedKv& kv, const LaunchOpts& opts,
-                                       bool skip_single = false);
+                                       bool skip_single = false, int long_requests = 0, int short_requests = 1);
+// long_requests / short_requests: how many requests of the pass have at least / fewer than 64 query rows (the caller
+// knows the lengths on the host): the former run on the tensor-core kernel, the latter on the SIMT tile kernel.
 // Decode: one row per request.  scratch_acc: fp32 [batch*heads*chunks*D], scratch_ml: fp32
 // [batch*heads*chunks*2]; chunks = ceil(max_kv / chunk).
 // counters: optional int [batch*heads], zero between launches; when given the merge of the chunk

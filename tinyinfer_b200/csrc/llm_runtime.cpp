@@ -218,6 +218,7 @@ struct ti_llm_model {
     if (const char* v = std::getenv("TINYINFER_B200_LN_TRIGGER")) ln_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_GEMM_TRIGGER")) gemm_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_MIXED_ATTN")) mixed_attention = std::atoi(v) != 0;
+    if (const char* v = std::getenv("TINYINFER_B200_TC_ATTN")) tc_attention = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_TRIGGER")) attn_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_WHOLE")) attn_whole = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) fuse_ln_rows = std::min(1024, std::atoi(v));
@@ -345,6 +346,7 @@ struct ti_llm_model {
     const int32_t *row_start, *qlens, *offsets, *kvlens, *slots;   // per request
     int rows, batch, max_q, max_kv;
     int singles;                                                  // requests with exactly one row in this pass
+    int longs;                                                    // requests with at least 64 rows (tensor-core attention)
   };
 
   // Embedding and every transformer block; leaves the final hidden state in `x`.
@@ -374,7 +376,9 @@ struct ti_llm_model {
         const bool split = attn_whole && mixed_attention && m.singles > 0;
         if (split) ck(tib::attention_paged_decode(qkv, attn, m.kvlens, m.batch, m.max_kv, kDecodeChunk, att_acc, att_ml, att_counters, kv, o,
                                                   false, true, false, m.row_start, m.qlens));
-        ck(tib::attention_paged(qkv, attn, m.row_start, m.qlens, m.kvlens, m.offsets, m.batch, m.max_q, m.max_kv, kv, o, split));
+        const int shorts = m.batch - m.longs - (split ? m.singles : 0);
+        ck(tib::attention_paged(qkv, attn, m.row_start, m.qlens, m.kvlens, m.offsets, m.batch, m.max_q, m.max_kv, kv, o, split,
+                                tc_attention ? m.longs : 0, tc_attention ? shorts : 1));
       }
       gemm(attn, b.proj, res, m.rows, false, x, false);             // res = x + proj(attn)
       if (fused) gemm(res, b.fc, act, m.rows, false, nullptr, true, nullptr, nullptr, nullptr, b.ln2_g, b.ln2_b);
@@ -408,7 +412,9 @@ struct ti_llm_model {
     spec.armed = false; spec.inflight = 0; spec.streak = 0;
     const int batch = int(ss.size()), H = shape.hidden;
     Meta m{}; m.batch = batch;
-    for (int b = 0; b < batch; ++b) { m.rows += lens[size_t(b)]; m.max_q = std::max(m.max_q, lens[size_t(b)]); m.singles += lens[size_t(b)] == 1; }
+    for (int b = 0; b < batch; ++b) {
+      m.rows += lens[size_t(b)]; m.max_q = std::max(m.max_q, lens[size_t(b)]); m.singles += lens[size_t(b)] == 1; m.longs += lens[size_t(b)] >= 64;
+    }
     const int rows = m.rows;
     int32_t* ids = h_meta; int32_t* row_req = ids + rows; int32_t* row_pos = row_req + rows; int32_t* per = row_pos + rows;
     int32_t *row_start = per, *qlens = per + batch, *offsets = per + 2 * batch, *kvlens = per + 3 * batch,
@@ -480,6 +486,7 @@ struct ti_llm_model {
   // may start at once; measured: a few microseconds per step at small batches.  After a LayerNorm it did not pay.
   bool ln_trigger = false, gemm_trigger = true;
   tib::LaunchOpts ln_opts() const { tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl; o.early_trigger = ln_trigger; return o; }
+  bool tc_attention = true;                      // requests with 64 or more rows in a pass: attention on the tensor cores
   bool mixed_attention = true;                   // mixed passes: single-token requests through the decode kernel
   bool attn_trigger = true;                      // the projection GEMM after attention prefetches its weights meanwhile
   bool attn_early = true, attn_whole = true;     // decode attention: reads ahead of the dependency wait; one CTA per (request, head)

@@ -89,18 +89,23 @@ async def _one(host, port, item, start, gate, records, timeout):
     records.append(record)
 
 
-async def run(host, port, rate, count, seed, outstanding=2048, timeout=300.0):
-    items = workload(seed, rate, count)
+async def run_items(host, port, items, outstanding=2048, timeout=300.0):
+    """Sends `items` (a list from workload(), or a share of one) at their due times; returns the raw per-request records
+    and the clock value the due times are relative to."""
     gate = asyncio.Semaphore(outstanding)
     records = []
     start = time.perf_counter() + 0.05
     await asyncio.gather(*(_one(host, port, item, start, gate, records, timeout) for item in items))
+    return records, start
+
+
+def report(records, start, offered, offered_window_s, rate=None, seed=None):
     done = [r for r in records if r.get("status") == 0]
     last = max((r["finished_at"] for r in done), default=start)
     tokens = sum(r["tokens"] for r in done)
     per_token = [r["decode_s"] / (r["tokens"] - 1) for r in done if r["tokens"] > 1]
-    return {"rate": rate, "seed": seed, "offered": count, "completed": len(done), "failed": count - len(done),
-            "offered_window_s": items[-1][0], "drain_window_s": last - start, "generated_tokens": tokens,
+    return {"rate": rate, "seed": seed, "offered": offered, "completed": len(done), "failed": offered - len(done),
+            "offered_window_s": offered_window_s, "drain_window_s": last - start, "generated_tokens": tokens,
             "tokens_per_s": tokens / (last - start) if last > start else 0.0,
             "prompt_tokens": sum(r["prompt"] for r in done),
             "mean_batch_size": sum(r["batch_size"] for r in done) / len(done) if done else 0.0,
@@ -108,6 +113,12 @@ async def run(host, port, rate, count, seed, outstanding=2048, timeout=300.0):
             "per_output_token_ms": summarise([v * 1e3 for v in per_token]),
             "request_latency_ms": summarise([r["latency_s"] * 1e3 for r in done]),
             "statuses": {str(k): sum(1 for r in records if r.get("status") == k) for k in {r.get("status") for r in records}}}
+
+
+async def run(host, port, rate, count, seed, outstanding=2048, timeout=300.0):
+    items = workload(seed, rate, count)
+    records, start = await run_items(host, port, items, outstanding, timeout)
+    return report(records, start, count, items[-1][0], rate, seed)
 
 
 def main():
