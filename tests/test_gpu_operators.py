@@ -326,3 +326,19 @@ def test_attention_with_many_query_rows_runs_on_tensor_cores_and_matches(ops, re
     alone = ops.attention(q[:1].contiguous(), k[:1].contiguous(), v[:1].contiguous(), q_lengths=ql[:1], kv_lengths=kl[:1],
                           query_offsets=off[:1], causal=causal)
     assert torch.equal(alone[0], out[0])
+
+
+@pytest.mark.parametrize("k,n", [(768, 2304), (3072, 768), (768, 50304)])
+@pytest.mark.parametrize("m", [8, 32, 100, 512, 1500])
+def test_fp16_weights_run_the_tensor_core_kernel_with_the_bits_of_the_int8_path(ops, ref, m, k, n):
+    """ti_v2_gemm_ex_f16 (reference backend/runtime_v2.cu:62-68) from 5 rows on takes the same tcgen05 kernel as the
+    INT8 path, the weight tiles rearranged instead of dequantised: given the fp16 values an INT8 matrix dequantises to it
+    returns exactly the bits of the INT8 call, and it stays inside the gate of the reference's own kernel."""
+    a, w, s, bias = int8_case(torch, m, n, k, seed=7)
+    w16 = (w.float() * s[None, :]).half()                       # fp16_rn(float(q) * scale): the reference's dequantisation
+    got = ops.gemm(a, w16, bias=bias)
+    assert torch.equal(got, ops.gemm_int8(a, w, s, bias=bias))
+    got32 = ops.gemm(a, w16, bias=bias, output_dtype=torch.float32)
+    assert torch.equal(got32, ops.gemm_int8(a, w, s, bias=bias, output_dtype=torch.float32))
+    if n <= 4096:
+        close(got32, ref.gemm(a, w16, bias=bias, output_dtype=torch.float32), atol=2e-3, rtol=1e-4)

@@ -88,3 +88,27 @@ def test_static_scratch_rejects_oversized_problems_with_a_clear_error():
     assert "scratch" in message and str(capacity) in message
     torch.cuda.synchronize()
     assert torch.equal(out, torch.full_like(out, 7.0))           # nothing was launched
+
+
+def test_static_scratch_single_chunk_path_and_capacity_boundary():
+    lib = _library()
+    # a chunk that covers the whole history takes the kernel that merges in shared memory: the array is not touched
+    q, k, v, lengths = _case(3, 2, 3, 200, [200, 131])
+    regular, fixed = _both(lib, q, k, v, lengths, 256)
+    assert torch.equal(regular, fixed)
+    # the largest problem of this shape family that still fits the array (31 x 16 x 32 chunks x 66 floats = 1,047,552 of
+    # 1,048,576), bit for bit against the caller-scratch entry ...
+    capacity = lib.ti_b200_attention_decode_static_capacity_floats()
+    assert lib.ti_b200_attention_decode_scratch_floats(31, 16, 1024, 32) <= capacity
+    q, k, v, lengths = _case(4, 31, 16, 1024, [1024 - 7 * i for i in range(31)])
+    regular, fixed = _both(lib, q, k, v, lengths, 32)
+    assert torch.equal(regular, fixed)
+    # ... and the next larger one (71 x 7 x 32 x 66 = 1,049,664) is refused before anything is launched
+    assert lib.ti_b200_attention_decode_scratch_floats(71, 7, 1024, 32) > capacity
+    q, k, v, lengths = _case(5, 71, 7, 1024, [1024] * 71)
+    out = torch.full_like(q, 3.0)
+    status = lib.ti_b200_attention_decode_static_f16(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lengths.data_ptr(), 71, 7, 1024, 64, 32,
+                                                     torch.cuda.current_stream().cuda_stream, torch.cuda.current_device())
+    assert status == 1 and "scratch" in lib.ti_v2_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.equal(out, torch.full_like(out, 3.0))

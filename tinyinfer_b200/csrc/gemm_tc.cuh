@@ -60,11 +60,13 @@ constexpr int kTcOpABytes = 128 * kTcStageK * 2;      // fp16 weight tile
 
 // OPS: operand stages.  LEAN (one 32-row tile without K split or LayerNorm, i.e. the vocabulary projection): two operand
 // stages and no receive region -- 65 KB, so that three CTAs share an SM and 393 column slabs run as one wave.
-template <int NMMA, bool LEAN = false> struct TcSmem {
+// WB: bytes per weight element (1 = int8 with scales, 2 = fp16): a raw stage is 64 rows x 128 channels of them.
+template <int NMMA, bool LEAN = false, int WB = 1> struct TcSmem {
   static constexpr int kOps = LEAN || NMMA == 64 ? 2 : kTcOpStages;      // 64-row tiles: two stages keep two CTAs per SM
   static constexpr int kOpBBytes = NMMA * kTcStageK * 2;
+  static constexpr int kRawStage = kTcRawBytes * WB;
   static constexpr int kRawOff = 0;                                        // 1024-aligned (TMA swizzle)
-  static constexpr int kOpAOff = kRawOff + kTcRawStages * kTcRawBytes;
+  static constexpr int kOpAOff = kRawOff + kTcRawStages * kRawStage;
   static constexpr int kOpBOff = kOpAOff + kOps * kTcOpABytes;
   // NMMA == 32 (decode): 16 KB where the other CTAs of a K-split cluster deposit their partial sums of the 128 / splits
   // columns this CTA finishes, [source rank][32 rows][128 / splits] fp32.  It aliases nothing: peers write it while this
@@ -123,12 +125,17 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
 // K-split cluster); separate instantiations keep the plain GEMM free of that code.
 // DIRECT: the weight matrix cannot be described by a tensor map (row pitch not a multiple of 16 bytes); warp 0 then
 // fills the raw stages itself with realigned loads instead of issuing TMA copies.
-template <int NMMA, int LN = 0, bool LEAN = false, bool DIRECT = false>
-__global__ void __launch_bounds__(kTcThreads, LEAN ? 3 : NMMA <= 64 ? 2 : 1)
+// WT: int8_t (weights dequantised on the way into the operand stage) or __half (fp16 weights, [K,N] row-major: the tiles
+// arrive as two 64-channel boxes per stage and are only rearranged into the operand layout -- no arithmetic).
+template <int NMMA, int LN = 0, bool LEAN = false, bool DIRECT = false, typename WT = int8_t>
+__global__ void __launch_bounds__(kTcThreads, LEAN && sizeof(WT) == 1 ? 3 : NMMA <= 64 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
   trace_event(kTrGemmTc, 0);
   if (TIB_SLOT_GRID && threadIdx.x == 0) trace_slot(1);
-  using L = TcSmem<NMMA, LEAN>;
+  constexpr bool kHalfW = sizeof(WT) == 2;
+  static_assert(!kHalfW || (LN == 0 && !DIRECT), "fp16 weights: plain tensor-map path");
+  using L = TcSmem<NMMA, LEAN, int(sizeof(WT))>;
+  constexpr int kRawStage = L::kRawStage;
   constexpr int kOps = L::kOps;
   static_assert(!LEAN || (NMMA == 32 && LN == 0), "lean layout: plain 32-row tiles");
   extern __shared__ uint8_t smem_raw[];
@@ -200,7 +207,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
       const uint32_t phase = uint32_t(i / kTcRawStages) & 1u;
       ok = mbar_wait(&raw_empty[slot], phase ^ 1u, kStatusPipeTimeout);
       if (!ok) break;
-      uint8_t* tile = raw + slot * kTcRawBytes;
+      uint8_t* tile = raw + slot * kRawStage;
 #pragma unroll 1
       for (int batch = 0; batch < 2; ++batch) {
         uint4 v[8];
@@ -246,9 +253,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         const uint32_t phase = uint32_t(i / kTcRawStages) & 1u;
         ok = mbar_wait(&raw_empty[slot], phase ^ 1u, kStatusPipeTimeout);     // first round passes immediately
         if (!ok) break;
-        mbar_expect_tx(&raw_full[slot], kTcRawBytes);
-        if (p.w_slab_rows) tma_load_2d(raw + slot * kTcRawBytes, &w_map, 0, int(blockIdx.x) * p.w_slab_rows + k_begin + i * kTcStageK, &raw_full[slot]);
-        else tma_load_2d(raw + slot * kTcRawBytes, &w_map, n0, k_begin + i * kTcStageK, &raw_full[slot]);
+        mbar_expect_tx(&raw_full[slot], kRawStage);
+        if (kHalfW) {
+          // two boxes of 64 channels (128 bytes of fp16 per row, the widest a 128-byte swizzle takes)
+          tma_load_2d(raw + slot * kRawStage, &w_map, n0, k_begin + i * kTcStageK, &raw_full[slot]);
+          tma_load_2d(raw + slot * kRawStage + kTcRawBytes, &w_map, n0 + 64, k_begin + i * kTcStageK, &raw_full[slot]);
+        } else if (p.w_slab_rows) tma_load_2d(raw + slot * kRawStage, &w_map, 0, int(blockIdx.x) * p.w_slab_rows + k_begin + i * kTcStageK, &raw_full[slot]);
+        else tma_load_2d(raw + slot * kRawStage, &w_map, n0, k_begin + i * kTcStageK, &raw_full[slot]);
         if (TIB_SLOT_GRID) trace_slot(10 + i);
       }
       if (!ok) s_failed = 1;
@@ -286,12 +297,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
     const int t = tid - 64;                                   // 0..255
     const int r8 = t & 7, cc = (t >> 3) & 7, kg0 = t >> 6;     // k within 8-group, 16-byte chunk (16 channels), first k-group
     float sc[16];
+    if (!kHalfW) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j) { const int col = n0 + cc * 16 + j; sc[j] = col < p.n ? p.scales[col] : 1.f; }
+      for (int j = 0; j < 16; ++j) { const int col = n0 + cc * 16 + j; sc[j] = col < p.n ? p.scales[col] : 1.f; }
+    }
     // Weight tile of raw stage -> fp16 A-operand stage (independent of any earlier kernel).
     auto dequantise = [&](int rslot, int oslot) {
-      const uint8_t* src = raw + rslot * kTcRawBytes;
+      const uint8_t* src = raw + rslot * kRawStage;
       uint8_t* dst = op_a + oslot * kTcOpABytes;
+      if constexpr (kHalfW) {
+        // 64 rows x 16 chunks of 8 channels, four per thread: out of the swizzled box, into core matrix (k group, channel group)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int id = t + kTcDequantThreads * j, k8 = id & 7, ch = (id >> 3) & 15, kg = id >> 7, krow = kg * 8 + k8;
+          const uint4 w8 = *reinterpret_cast<const uint4*>(src + (ch >> 3) * kTcRawBytes + krow * 128 + (((ch & 7) ^ k8) << 4));
+          *reinterpret_cast<uint4*>(dst + (kg * 16 + ch) * 128 + k8 * 16) = w8;
+        }
+      } else {
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int kg = kg0 + 4 * j, krow = kg * 8 + r8;
@@ -303,6 +325,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap w_map, const GemvArgs p) {
         uint8_t* core = dst + (kg * 16 + 2 * cc) * 128 + r8 * 16;      // core matrix (k-group, channel-group), row k%8
         *reinterpret_cast<uint4*>(core) = *reinterpret_cast<const uint4*>(&h[0]);
         *reinterpret_cast<uint4*>(core + 128) = *reinterpret_cast<const uint4*>(&h[4]);
+      }
       }
     };
     // The matching 64 columns of A: NMMA rows x 8 chunks of 8 halves, as K-major core matrices.  The

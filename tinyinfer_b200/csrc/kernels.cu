@@ -117,11 +117,12 @@ cudaError_t launch_gemv_mt(int mt, const CUtensorMap& map, const GemvArgs& args,
   }
 }
 
-template <int NMMA, int LN = 0, bool LEAN = false, bool DIRECT = false>
+template <int NMMA, int LN = 0, bool LEAN = false, bool DIRECT = false, typename WT = int8_t>
 cudaError_t launch_tc(const CUtensorMap& map, const GemvArgs& args, dim3 grid, const LaunchOpts& o) {
-  const cudaError_t ready = allow_smem(gemm_tc_kernel<NMMA, LN, LEAN, DIRECT>, TcSmem<NMMA, LEAN>::kBytes);
+  constexpr int kBytes = TcSmem<NMMA, LEAN, int(sizeof(WT))>::kBytes;
+  const cudaError_t ready = allow_smem(gemm_tc_kernel<NMMA, LN, LEAN, DIRECT, WT>, kBytes);
   if (ready != cudaSuccess) return ready;
-  return launch(gemm_tc_kernel<NMMA, LN, LEAN, DIRECT>, grid, dim3(kTcThreads), TcSmem<NMMA, LEAN>::kBytes, o, int(grid.y), map, args);
+  return launch(gemm_tc_kernel<NMMA, LN, LEAN, DIRECT, WT>, grid, dim3(kTcThreads), kBytes, o, int(grid.y), map, args);
 }
 
 // Measurement aids of development builds (-DTIB_DEV_KNOBS): an environment variable may override a dispatch
@@ -238,6 +239,36 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
       }
     }
   }
+  // fp16 weights on the same tensor-core kernel: the tiles are rearranged instead of dequantised.  Same K split and the
+  // same tile forms as the int8 path, so a matrix gives the same bits whether it arrives as int8 + scales or as the fp16
+  // values those dequantise to.
+  if (!c.w_int8 && !c.ln_gamma && !c.w_slab_rows && (c.uniform_numerics || c.m >= tc_min_rows) && c.k % 8 == 0 && c.lda % 8 == 0 &&
+      reinterpret_cast<uintptr_t>(c.a) % 16 == 0) {
+    CUtensorMap map; std::memset(&map, 0, sizeof map);
+    if (make_map_2d(&map, c.w, false, uint64_t(c.k), uint64_t(c.n), uint64_t(c.ldw), 64, uint32_t(kTcStageK), true)) {
+      const int slabs = (c.n + 127) / 128, splits = tc_splits(c.n, c.k);
+      a.k_chunk = tc_chunk(c.k, splits);
+      const int wide = std::min(256, 512 / splits);
+      if (splits > 1 && c.m > 32 && slabs * ((c.m + wide - 1) / wide) >= sm_count()) {
+        a.serial_chunks = splits;
+        const dim3 grid(slabs, 1, (c.m + wide - 1) / wide);
+        switch (wide) {
+          case 64: return launch_tc<64, 0, false, false, __half>(map, a, grid, o);
+          case 128: return launch_tc<128, 0, false, false, __half>(map, a, grid, o);
+          default: return launch_tc<256, 0, false, false, __half>(map, a, grid, o);
+        }
+      }
+      const int nmma = c.m <= 32 ? 32 : (c.m <= 64 || (splits > 1 && c.m <= 1024)) ? 64 : c.m <= 128 ? 128 : 256;
+      const dim3 grid(slabs, splits, (c.m + nmma - 1) / nmma);
+      switch (nmma) {
+        case 32: return splits == 1 && slabs > 2 * sm_count() ? launch_tc<32, 0, true, false, __half>(map, a, grid, o)
+                                                              : launch_tc<32, 0, false, false, __half>(map, a, grid, o);
+        case 64: return launch_tc<64, 0, false, false, __half>(map, a, grid, o);
+        case 128: return launch_tc<128, 0, false, false, __half>(map, a, grid, o);
+        default: return launch_tc<256, 0, false, false, __half>(map, a, grid, o);
+      }
+    }
+  }
   if (c.ln_gamma || c.w_slab_rows) return cudaErrorNotSupported;   // only the tensor-core kernel has the LayerNorm prologue / reads tiles
   // Row tiles run along grid.z (at most 65535): more rows than that go out as several launches over row blocks.
   constexpr int kSimtRowsPerLaunch = 4 * 65535;
@@ -274,6 +305,13 @@ cudaError_t retile_i8(const int8_t* src, long long ld, int k, int n, int8_t* dst
   if (!src || !dst || k < 1 || n < 1 || slab_rows < k) return cudaErrorInvalidValue;
   const long long chunks = (long long)((n + 127) / 128) * slab_rows * 8;
   retile_i8_kernel<<<unsigned((chunks + 255) / 256), 256, 0, stream>>>(src, ld, k, n, dst, slab_rows, chunks);
+  return cudaGetLastError();
+}
+
+cudaError_t dequant_matrix(const int8_t* q, long long ldq, const float* scales, void* out, long long ldo, int k, int n, cudaStream_t stream) {
+  if (!q || !scales || !out || k < 1 || n < 1 || ldo < n) return cudaErrorInvalidValue;
+  const long long elements = (long long)k * ldo;
+  dequant_matrix_kernel<<<unsigned((elements + 255) / 256), 256, 0, stream>>>(q, ldq, scales, static_cast<__half*>(out), ldo, k, n);
   return cudaGetLastError();
 }
 

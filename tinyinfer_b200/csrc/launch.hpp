@@ -62,6 +62,9 @@ TIB_EXPORT cudaError_t gemm(const GemmCall& call, const LaunchOpts& opts);
 // dst[slab][row][c] = row < k && slab*128+c < n ? src[row*ld + slab*128+c] : 0, for ceil(n/128) slabs of slab_rows rows.
 TIB_EXPORT cudaError_t retile_i8(const int8_t* src, long long ld, int k, int n, int8_t* dst, int slab_rows, cudaStream_t stream);
 
+// out[k][ldo] (fp16) = the values q[k][ldq] (int8) with per-column `scales` dequantise to; columns n..ldo-1 are zero.
+TIB_EXPORT cudaError_t dequant_matrix(const int8_t* q, long long ldq, const float* scales, void* out, long long ldo, int k, int n, cudaStream_t stream);
+
 // Per-output-channel symmetric INT8 quantisation of w[rows][cols] (fp16) on the device, bit-identical to the host codec.
 // scales[cols] doubles as the scratch of the column maxima; flag (device int, zeroed here) becomes 1 for non-finite input.
 TIB_EXPORT cudaError_t quantize_i8(const void* w, long long rows, int cols, int8_t* q, float* scales, int* flag, cudaStream_t stream);
