@@ -1,0 +1,268 @@
+// Many-row GEMM (prefill) on the sm_100a tensor cores:  out[M,N] = A[M,K] . W[K,N] + bias  (+ GELU, + residual, K/V placement)
+//
+// For passes of hundreds to thousands of rows the decode-shaped kernel (gemm_tc.cuh) spends most of a CTA's life in its
+// prologue and epilogue: K is short (768 .. 4096), a 64-row tile is 12 .. 64 stages of work wrapped in fixed costs, and
+// every weight is dequantised again for every 64-row tile.  This kernel is built for that regime:
+//   * the weights are read from an "operand image": the fp16 values the INT8 matrix dequantises to (or the fp16 weights
+//     of an fp16 artifact), stored once at load time in exactly the shared-memory layout tcgen05.mma wants
+//     ([slab of 128 channels][64-row stage][16 KB of MN-major core matrices]).  A stage is one contiguous 16 KB block:
+//     warp 0 fetches it with a single bulk copy, no thread ever touches a weight;
+//   * tiles of 128 channels x 128 rows, four operand stages in flight, CTAs persistent over the tiles of the problem, so
+//     the epilogue of one tile overlaps the main loop of the next;
+//   * the K ranges of gemm()'s K split still get separate TMEM accumulators (two, alternating) and are added in range
+//     order -- by eight dedicated warps that keep the running sums in registers while the tensor cores work on the next
+//     range -- so a row's result carries the same bits as in the decode-shaped kernel, whatever the row count.
+// Warp roles (448 threads): 0 bulk-copy producer, 1 MMA issuer, 2-5 stage the rows of A (K-major core matrices),
+// 6-13 fold the K ranges and finish the tile (bias, GELU, residual, K/V placement, store).  Every wait is bounded.
+#pragma once
+#include <cuda.h>
+
+#include "attention.cuh"
+#include "common.cuh"
+#include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+
+namespace tib {
+
+constexpr int kWideRows = 128;                     // rows of A per tile = MMA N
+constexpr int kWideStages = 4;                     // operand stages (weights 16 KB + rows 16 KB each)
+constexpr int kWideStagers = 128;                  // warps 2..5
+constexpr int kWideFolders = 256;                  // warps 6..13
+constexpr int kWideThreads = 64 + kWideStagers + kWideFolders;
+constexpr int kWideImageStage = 128 * kTcStageK * 2;        // bytes of one weight stage in the operand image
+
+struct WideSmem {
+  static constexpr int kOpAOff = 0;
+  static constexpr int kOpBBytes = kWideRows * kTcStageK * 2;
+  static constexpr int kOpBOff = kOpAOff + kWideStages * kWideImageStage;
+  static constexpr int kBarOff = kOpBOff + kWideStages * kOpBBytes;
+  static constexpr int kBytes = kBarOff + 256 + 128;
+};
+
+// Byte offset of element (k, c) of a [K,N] matrix inside its operand image (stages_per_slab = ceil(K / 64)).
+__host__ __device__ __forceinline__ size_t wide_image_offset(int k, int c, int stages_per_slab) {
+  const int slab = c >> 7, stage = k >> 6, kg = (k & 63) >> 3, ng = (c & 127) >> 3;
+  return (size_t(slab) * stages_per_slab + stage) * kWideImageStage + size_t(kg * 16 + ng) * 128 + (k & 7) * 16 + (c & 7) * 2;
+}
+
+// Image of an INT8 matrix (its dequantised values) or of an fp16 matrix; channels >= n and rows >= k are zero.
+// One thread per 16 bytes of the image (8 channels of one k row).
+__global__ void wide_image_kernel(const int8_t* q, const __half* w16, long long ld, const float* scales, uint8_t* image, int k, int n,
+                                  int stages_per_slab, long long chunks) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= chunks) return;
+  // chunk i of the image: (slab, stage, kg, ng, k8)
+  const int k8 = int(i & 7), ng = int((i >> 3) & 15), kg = int((i >> 7) & 7);
+  const long long block = i >> 10;
+  const int stage = int(block % stages_per_slab), slab = int(block / stages_per_slab);
+  const int row = stage * 64 + kg * 8 + k8, col0 = slab * 128 + ng * 8;
+  __half h[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int col = col0 + e;
+    h[e] = f2h(0.f);
+    if (row < k && col < n) h[e] = q ? f2h(float(q[(long long)row * ld + col]) * scales[col]) : w16[(long long)row * ld + col];
+  }
+  *reinterpret_cast<uint4*>(image + i * 16) = *reinterpret_cast<const uint4*>(h);
+}
+
+// grid = min(tiles, SMs) persistent CTAs, block = kWideThreads.  p.w = operand image; p.k_chunk = rows per K range.
+__global__ void __launch_bounds__(kWideThreads, 1)
+gemm_wide_kernel(const GemvArgs p) {
+  using L = WideSmem;
+  extern __shared__ uint8_t wide_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(wide_smem_raw) + 127) & ~uintptr_t(127));
+  uint8_t* op_a = smem + L::kOpAOff;
+  uint8_t* op_b = smem + L::kOpBOff;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t *op_full = bars, *op_empty = op_full + kWideStages, *range_done = op_empty + kWideStages, *range_free = range_done + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(range_free + 2);
+  __shared__ int s_failed;
+  __shared__ long long s_row_base[2][kWideRows];               // K/V pool offset of each row of the tile (QKV projection), per tile parity
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int slabs = (p.n + 127) / 128, row_tiles = (p.m + kWideRows - 1) / kWideRows, tiles = slabs * row_tiles;
+  const int stages = (p.k + kTcStageK - 1) / kTcStageK;        // per tile
+  const int chunk_stages = p.k_chunk / kTcStageK;
+  const int ranges = (stages + chunk_stages - 1) / chunk_stages;
+
+  pdl_launch_dependents();
+  if (tid == 0) {
+    s_failed = 0;
+    for (int s = 0; s < kWideStages; ++s) { mbar_init(&op_full[s], 1 + kWideStagers / 32); mbar_init(&op_empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&range_done[b], 1); mbar_init(&range_free[b], kWideFolders / 32); }
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 2 * kWideRows);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  volatile int* failed = &s_failed;
+  auto wait = [&](uint64_t* bar, uint32_t parity, unsigned int code) {
+    for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+      if (mbar_try(bar, parity)) return true;
+      if ((spin & 1023u) == 1023u && *failed) return false;
+    }
+    report(code);
+    *failed = 1;
+    return false;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer: one 16 KB bulk copy per stage (weights only)
+    if (lane == 0) {
+      const uint8_t* image = static_cast<const uint8_t*>(p.w);
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int slab = tile % slabs;
+        for (int i = 0; i < stages && ok; ++i, ++it) {
+          const int slot = it % kWideStages;
+          ok = wait(&op_empty[slot], (uint32_t(it / kWideStages) & 1u) ^ 1u, kStatusPipeTimeout);
+          if (!ok) break;
+          mbar_expect_tx(&op_full[slot], kWideImageStage);
+          bulk_load(op_a + slot * kWideImageStage, image + (size_t(slab) * stages + i) * kWideImageStage, kWideImageStage, &op_full[slot]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 15) | (uint32_t(kWideRows >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+      int it = 0, g = 0;                                       // running stage / range numbers over all tiles of this CTA
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        for (int r = 0; r < ranges && ok; ++r, ++g) {
+          const int buffer = g & 1;
+          if (g >= 2) ok = wait(&range_free[buffer], uint32_t((g - 2) >> 1) & 1u, kStatusPipeTimeout);   // the folders have read it
+          if (!ok) break;
+          tc_fence_after();
+          const int first = r * chunk_stages, last = min(stages, first + chunk_stages);
+          for (int i = first; i < last && ok; ++i, ++it) {
+            const int slot = it % kWideStages;
+            ok = wait(&op_full[slot], uint32_t(it / kWideStages) & 1u, kStatusPipeTimeout);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t a_addr = smem_u32(op_a + slot * kWideImageStage), b_addr = smem_u32(op_b + slot * L::kOpBBytes);
+#pragma unroll
+            for (int kk = 0; kk < kTcStageK / 16; ++kk) {
+              const uint64_t da = tc_desc(a_addr + kk * 2 * 2048, 2048u, 128u);
+              const uint64_t db = tc_desc(b_addr + kk * 2 * (kWideRows / 8) * 128, (kWideRows / 8) * 128, 128);
+              tc_mma_f16(tmem_base + uint32_t(buffer * kWideRows), da, db, idesc, (i > first || kk > 0) ? 1u : 0u);
+            }
+            tc_commit(&op_empty[slot]);
+          }
+          if (ok) tc_commit(&range_done[buffer]);
+        }
+      }
+    }
+  } else if (warp < 2 + kWideStagers / 32) {
+    // ------------------------------------------------------------ rows of A -> K-major core matrices of the B operand
+    const int t = tid - 64;                                    // 0..127
+    constexpr int kPer = kWideRows * 8 / kWideStagers;         // 16-byte pieces per thread and stage
+    int it = 0;
+    bool ok = true;
+    uint4 ahead[kPer];
+    auto fetch = [&](uint4 (&dst)[kPer], int tile, int i) {
+      const int m0 = (tile / slabs) * kWideRows, k0 = i * kTcStageK;
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        const int id = t + kWideStagers * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
+        const int row = m0 + mg * 8 + m8, kcol = k0 + kc * 8;
+        dst[j] = make_uint4(0, 0, 0, 0);
+        if (tile < tiles && i < stages && row < p.m && kcol < p.k) dst[j] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + kcol);
+      }
+    };
+    pdl_wait();                                                // A comes from the previous kernel
+    int tile = blockIdx.x;
+    fetch(ahead, tile, 0);
+    for (; tile < tiles; tile += gridDim.x) {
+      for (int i = 0; i < stages; ++i, ++it) {
+        const int slot = it % kWideStages;
+        uint4 now[kPer];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) now[j] = ahead[j];
+        // request the next stage's rows (of this tile or the next) before waiting for the slot
+        if (i + 1 < stages) fetch(ahead, tile, i + 1); else fetch(ahead, tile + gridDim.x, 0);
+        if (ok) ok = wait(&op_empty[slot], (uint32_t(it / kWideStages) & 1u) ^ 1u, kStatusMmaTimeout);
+        if (ok) {
+          uint8_t* dst = op_b + slot * L::kOpBBytes;
+#pragma unroll
+          for (int j = 0; j < kPer; ++j) {
+            const int id = t + kWideStagers * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
+            *reinterpret_cast<uint4*>(dst + (kc * (kWideRows / 8) + mg) * 128 + m8 * 16) = now[j];
+          }
+          fence_async_smem();
+        }
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(&op_full[slot]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ fold the K ranges, finish the tile
+    const int f = warp - (2 + kWideStagers / 32);              // 0..7
+    const int quarter = warp & 3, half_rows = f >> 2;           // TMEM lanes 32 * quarter .., columns 64 * half_rows ..
+    const uint32_t taddr = tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(64 * half_rows);
+    const int ft = tid - (64 + kWideStagers);                  // 0..255
+    int g = 0, tile_no = 0;
+    bool ok = true;
+    pdl_wait();                                                // the residual comes from an earlier kernel
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++tile_no) {
+      const int slab = tile % slabs, m0 = (tile / slabs) * kWideRows, n0 = slab * 128;
+      const int col = n0 + 32 * quarter + lane;
+      long long* row_base = s_row_base[tile_no & 1];
+      if (p.k_pool) {
+        for (int i = ft; i < kWideRows; i += kWideFolders) row_base[i] = m0 + i < p.m ? kv_row_base(p, m0 + i) : 0;
+        asm volatile("bar.sync 4, 256;" ::: "memory");
+      }
+      float sum[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) sum[j] = 0.f;
+      for (int r = 0; r < ranges; ++r, ++g) {
+        const int buffer = g & 1;
+        if (ok) ok = wait(&range_done[buffer], uint32_t(g >> 1) & 1u, kStatusMmaTimeout);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        if (ok) {
+          float lo[32], hi[32];
+          tmem_load32(taddr + uint32_t(buffer * kWideRows), lo);
+          tmem_load32(taddr + uint32_t(buffer * kWideRows) + 32u, hi);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { sum[j] += lo[j]; sum[32 + j] += hi[j]; }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0 && ok) mbar_arrive(&range_free[buffer]);
+      }
+      // finish: the rounding points of gemv_store (bias -> fp16 -> GELU -> fp16 -> + residual -> fp16, or K/V to their pages)
+      if (ok && col < p.n) {
+        const float bias = p.bias ? h2f(p.bias[col]) : 0.f;
+        const bool to_cache = p.k_pool && col >= p.kv_hidden;
+        __half* pool = nullptr;
+        if (to_cache) {
+          const int cc = col - p.kv_hidden, which = cc >= p.kv_hidden, e = which ? cc - p.kv_hidden : cc;
+          pool = (which ? p.v_pool : p.k_pool) + (e >> 6) * 2048 + (e & 63);
+        }
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {                       // fully unrolled: sum[] stays in registers
+          const int row = m0 + 64 * half_rows + j;
+          if (row < p.m) {
+            __half h = f2h(sum[j] + bias);
+            if (to_cache) pool[row_base[64 * half_rows + j]] = h;
+            else {
+              if (p.gelu) h = f2h(gelu_tanh(h2f(h)));
+              if (p.residual) h = f2h(h2f(p.residual[size_t(row) * p.ldo + col]) + h2f(h));
+              static_cast<__half*>(p.out)[size_t(row) * p.ldo + col] = h;
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * kWideRows); }
+}
+
+}  // namespace tib

@@ -20,6 +20,7 @@ namespace tib { __device__ unsigned int g_device_status = 0; }
 #include "elementwise.cuh"
 #include "gemm_simt.cuh"
 #include "gemm_tc.cuh"
+#include "gemm_wide.cuh"
 #include "model_glue.cuh"
 
 namespace tib {
@@ -148,6 +149,7 @@ int tc_splits(int n, int k) {
   if (forced_splits > 0) splits = forced_splits;
   return splits;
 }
+constexpr int kWideMinRows = 129;       // fewer rows: one 32 / 64 / 128-row tile of the decode-shaped kernel (with its LayerNorm prologue)
 int tc_chunk(int k, int splits) {
   const int chunk = (k + splits - 1) / splits;
   return (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
@@ -168,6 +170,16 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
     a.kv_table = c.kv->table; a.kv_slots = c.kv->slots; a.kv_row_req = c.kv_row_req; a.kv_row_pos = c.kv_row_pos;
     a.kv_table_pitch = c.kv->table_pitch; a.kv_layers = c.kv->layers; a.kv_layer = c.kv->layer; a.kv_heads = c.kv->heads;
     a.kv_hidden = c.kv->heads * c.kv->head_dim;
+  }
+  // Many rows (prefill) of a matrix that has an operand image: the tile kernel built for that regime (gemm_wide.cuh), with
+  // the K ranges of the split below, so a row's result is the one the decode-shaped kernel gives.
+  if (c.w_image && c.m >= kWideMinRows && !c.out_fp32 && !c.ln_gamma && c.k % 8 == 0 && c.lda % 8 == 0 && reinterpret_cast<uintptr_t>(c.a) % 16 == 0) {
+    a.w = c.w_image;
+    a.k_chunk = tc_chunk(c.k, tc_splits(c.n, c.k));
+    const int tiles = ((c.n + 127) / 128) * ((c.m + kWideRows - 1) / kWideRows);
+    const cudaError_t ready = allow_smem(gemm_wide_kernel, WideSmem::kBytes);
+    if (ready != cudaSuccess) return ready;
+    return launch(gemm_wide_kernel, dim3(unsigned(std::min(tiles, sm_count()))), dim3(kWideThreads), WideSmem::kBytes, o, 1, a);
   }
   // Tensor-core path: int8 weights, 5 or more rows of A, operands addressable by TMA / 16-byte loads.
   static const int tc_min_rows = env_int("TINYINFER_B200_TC_MIN_ROWS", 5);      // measurement aid: where the SIMT kernel hands over
@@ -308,10 +320,13 @@ cudaError_t retile_i8(const int8_t* src, long long ld, int k, int n, int8_t* dst
   return cudaGetLastError();
 }
 
-cudaError_t dequant_matrix(const int8_t* q, long long ldq, const float* scales, void* out, long long ldo, int k, int n, cudaStream_t stream) {
-  if (!q || !scales || !out || k < 1 || n < 1 || ldo < n) return cudaErrorInvalidValue;
-  const long long elements = (long long)k * ldo;
-  dequant_matrix_kernel<<<unsigned((elements + 255) / 256), 256, 0, stream>>>(q, ldq, scales, static_cast<__half*>(out), ldo, k, n);
+size_t wide_image_bytes(int k, int n) { return size_t((n + 127) / 128) * size_t((k + kTcStageK - 1) / kTcStageK) * kWideImageStage; }
+
+cudaError_t wide_image(const int8_t* q, const void* w16, long long ld, const float* scales, void* image, int k, int n, cudaStream_t stream) {
+  if ((!q && !w16) || (q && !scales) || !image || k < 1 || n < 1) return cudaErrorInvalidValue;
+  const int stages = (k + kTcStageK - 1) / kTcStageK;
+  const long long chunks = (long long)(wide_image_bytes(k, n) / 16);
+  wide_image_kernel<<<unsigned((chunks + 255) / 256), 256, 0, stream>>>(q, static_cast<const __half*>(w16), ld, scales, static_cast<uint8_t*>(image), k, n, stages, chunks);
   return cudaGetLastError();
 }
 

@@ -55,6 +55,7 @@ struct GemmCall {
   // fp32 output without a K split (vocabulary projection): merge each row's greedy argmax into argmax_best[row]
   // (64-bit words, zero between steps; argmax_finish publishes them); skip_store: do not write the logits.
   void* argmax_best = nullptr; bool skip_store = false;
+  const void* w_image = nullptr;                         // optional operand image of the same matrix (wide_image): used from 129 rows on
   int m = 0, n = 0, k = 0;
 };
 TIB_EXPORT cudaError_t gemm(const GemmCall& call, const LaunchOpts& opts);
@@ -62,8 +63,11 @@ TIB_EXPORT cudaError_t gemm(const GemmCall& call, const LaunchOpts& opts);
 // dst[slab][row][c] = row < k && slab*128+c < n ? src[row*ld + slab*128+c] : 0, for ceil(n/128) slabs of slab_rows rows.
 TIB_EXPORT cudaError_t retile_i8(const int8_t* src, long long ld, int k, int n, int8_t* dst, int slab_rows, cudaStream_t stream);
 
-// out[k][ldo] (fp16) = the values q[k][ldq] (int8) with per-column `scales` dequantise to; columns n..ldo-1 are zero.
-TIB_EXPORT cudaError_t dequant_matrix(const int8_t* q, long long ldq, const float* scales, void* out, long long ldo, int k, int n, cudaStream_t stream);
+// Operand image of a [K,N] weight matrix for many-row passes (gemm_wide.cuh): the fp16 values an INT8 matrix `q` with
+// per-column `scales` dequantises to (or the fp16 matrix `w16`; exactly one of the two is given; `ld` = row pitch in
+// elements), laid out stage by stage in the shared-memory form of the tensor-core operand.  GemmCall::w_image takes it.
+TIB_EXPORT size_t wide_image_bytes(int k, int n);
+TIB_EXPORT cudaError_t wide_image(const int8_t* q, const void* w16, long long ld, const float* scales, void* image, int k, int n, cudaStream_t stream);
 
 // Per-output-channel symmetric INT8 quantisation of w[rows][cols] (fp16) on the device, bit-identical to the host codec.
 // scales[cols] doubles as the scratch of the column maxima; flag (device int, zeroed here) becomes 1 for non-finite input.

@@ -56,7 +56,7 @@ struct Linear {
   int k = 0, n = 0; long long ldw = 0;
   int slab_rows = 0;                 // > 0: w holds slab-major tiles [ceil(n/128)][slab_rows][128] (int8 only)
   long long tile_row0 = 0;           // first row of those tiles inside the model's tile arena ([rows][128] int8)
-  const void* w16 = nullptr; long long ld16 = 0;   // int8 models: the fp16 values the matrix dequantises to, [k][ld16], for many-row passes
+  const void* image = nullptr;       // operand image of the matrix for many-row passes (tib::wide_image)
 };
 struct Block { const void *ln1_g, *ln1_b, *ln2_g, *ln2_b; Linear qkv, proj, fc, proj2; };
 
@@ -161,18 +161,17 @@ struct ti_llm_model {
 #ifdef TIB_DEV_KNOBS
     if (const char* v = std::getenv("TINYINFER_B200_TILED")) tiled = tiled && std::atoi(v) != 0;
 #endif
-    if (int8) {
-      // Many-row passes (prefill) stream an fp16 copy of every matrix -- the very values the tiles dequantise to -- through the
-      // same tensor-core kernel instead of converting each weight once per 64-row tile; decode keeps the int8 tiles (half the
-      // bytes).  Built here, before the int8 pointers move to the tile arena.  247 MB for GPT-2 small.
+    {
+      // Many-row passes (prefill) read every matrix from its operand image -- the fp16 values the INT8 weights dequantise
+      // to, already in the layout the tensor cores read -- instead of converting each weight once per row tile; decode
+      // keeps the int8 tiles (half the bytes).  Built here, before the int8 pointers move to the tile arena.  About twice
+      // the bytes of the INT8 weights (247 MB for GPT-2 small).
       auto widen = [&](Linear& l) {
-        l.ld16 = (l.n + 127) / 128 * 128;
-        void* copy = dev<uint16_t>(size_t(l.k) * l.ld16);
-        ck(tib::dequant_matrix(static_cast<const int8_t*>(l.w), l.ldw, l.scales, copy, l.ld16, l.k, l.n, stream));
-        l.w16 = copy;
+        void* image = dev<uint8_t>(tib::wide_image_bytes(l.k, l.n));
+        ck(tib::wide_image(int8 ? static_cast<const int8_t*>(l.w) : nullptr, int8 ? nullptr : l.w, l.ldw, l.scales, image, l.k, l.n, stream));
+        l.image = image;
       };
       for (Block& b : blocks) { widen(b.qkv); widen(b.proj); widen(b.fc); widen(b.proj2); }
-      widen(head);
     }
     if (tiled) {
       // One arena holds the tiles of every matrix, so that a single tensor map (and a row offset per matrix) reaches
@@ -233,7 +232,7 @@ struct ti_llm_model {
     if (const char* v = std::getenv("TINYINFER_B200_GEMM_TRIGGER")) gemm_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_MIXED_ATTN")) mixed_attention = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_TC_ATTN")) tc_attention = std::atoi(v) != 0;
-    if (const char* v = std::getenv("TINYINFER_B200_WIDE_FP16")) wide_rows_fp16 = std::atoi(v);
+    if (const char* v = std::getenv("TINYINFER_B200_WIDE_GEMM")) wide_gemm = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_TRIGGER")) attn_trigger = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_ATTN_WHOLE")) attn_whole = std::atoi(v) != 0;
     if (const char* v = std::getenv("TINYINFER_B200_FUSE_LN")) fuse_ln_rows = std::min(1024, std::atoi(v));
@@ -346,9 +345,7 @@ struct ti_llm_model {
     c.argmax_best = argmax_best; c.skip_store = skip_store;
     c.kv = kv; c.kv_row_req = row_req; c.kv_row_pos = row_pos; c.ln_gamma = ln_g; c.ln_beta = ln_b;
     c.a = a; c.lda = l.k; c.w = l.w; c.ldw = l.ldw; c.w_slab_rows = l.slab_rows; c.w_int8 = int8; c.scales = l.scales; c.bias = l.bias;
-    if (int8 && l.w16 && rows >= wide_rows_fp16 && !ln_g) {       // same bits, no per-tile conversion
-      c.w = l.w16; c.ldw = l.ld16; c.w_slab_rows = 0; c.w_int8 = false; c.scales = nullptr;
-    }
+    if (wide_gemm) c.w_image = l.image;
     c.out = out; c.ldo = fp32 ? vpitch : l.n; c.out_fp32 = fp32; c.residual = residual; c.gelu = gelu;
     c.m = rows; c.n = l.n; c.k = l.k;
     // One kernel family for every batch size: logits of a request are bit-identical whatever it is
@@ -504,7 +501,7 @@ struct ti_llm_model {
   // may start at once; measured: a few microseconds per step at small batches.  After a LayerNorm it did not pay.
   bool ln_trigger = false, gemm_trigger = true;
   tib::LaunchOpts ln_opts() const { tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl; o.early_trigger = ln_trigger; return o; }
-  int wide_rows_fp16 = 129;                      // passes with at least this many rows run their GEMMs on the fp16 copies of the weights
+  bool wide_gemm = true;                         // passes of 129 rows and more run their GEMMs from the operand images
   bool tc_attention = true;                      // requests with 64 or more rows in a pass: attention on the tensor cores
   bool mixed_attention = true;                   // mixed passes: single-token requests through the decode kernel
   bool attn_trigger = true;                      // the projection GEMM after attention prefetches its weights meanwhile

@@ -114,15 +114,6 @@ __global__ void retile_i8_kernel(const int8_t* src, long long ld, int k, int n, 
   *reinterpret_cast<uint4*>(dst + i * 16) = *reinterpret_cast<const uint4*>(v);
 }
 
-// out[r][c] = fp16_rn(float(q[r][c]) * scales[c]) for c < n, 0 for n <= c < ldo: the fp16 values an INT8 matrix
-// dequantises to, written once so that many-row GEMMs (prefill) can stream them instead of converting every tile again.
-__global__ void dequant_matrix_kernel(const int8_t* q, long long ldq, const float* scales, __half* out, long long ldo, int k, int n) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= (long long)k * ldo) return;
-  const int r = int(i / ldo), c = int(i % ldo);
-  out[i] = c < n ? f2h(float(q[r * ldq + c]) * scales[c]) : f2h(0.f);
-}
-
 // ---- per-output-channel symmetric INT8 quantiser (reference specification: llm/quantization.py, backend/host_codec.cpp:
 // scale[c] = float(double(max_r |w[r][c]|) / 127.0), or 1 for an all-zero column; q = clip(round_half_even(double(w) /
 // double(scale)), -127, 127)).  Three launches: column maxima (bit patterns of non-negative floats order like unsigned
