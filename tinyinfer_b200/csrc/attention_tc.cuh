@@ -27,10 +27,11 @@ constexpr int kAttnTcKeys = 64;       // keys per step
 constexpr int kAttnTcMinRows = 64;    // requests with fewer query rows stay on the SIMT kernel (model runtime)
 
 struct AttnTcSmem {
+  static constexpr int kTile = kAttnTcKeys * 64 * 2;                // one K or V tile: 8 KB
   static constexpr int kQOff = 0;                                   // Q  [128 x 64]  K-major core matrices, 16 KB
-  static constexpr int kKOff = kQOff + kAttnTcRows * 64 * 2;        // K  [64 keys x 64]  K-major, 8 KB
-  static constexpr int kVOff = kKOff + kAttnTcKeys * 64 * 2;        // V  [64 keys x 64]  MN-major (d contiguous), 8 KB
-  static constexpr int kPOff = kVOff + kAttnTcKeys * 64 * 2;        // P  [128 x 64 keys]  K-major, 16 KB
+  static constexpr int kKOff = kQOff + kAttnTcRows * 64 * 2;        // K  2 x [64 keys x 64]  K-major (double buffer)
+  static constexpr int kVOff = kKOff + 2 * kTile;                   // V  2 x [64 keys x 64]  MN-major (d contiguous)
+  static constexpr int kPOff = kVOff + 2 * kTile;                   // P  [128 x 64 keys]  K-major, 16 KB
   static constexpr int kBytes = kPOff + kAttnTcRows * kAttnTcKeys * 2;
 };
 
@@ -101,21 +102,33 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   uint32_t phase = 0;
   bool ok = true;
 
-  for (int k0 = 0; k0 < key_end; k0 += kAttnTcKeys) {
-    // ---- K and V tile -> shared memory (zeros past key_end).  64 keys x 8 chunks of 8 values, 4 chunks per thread each.
+  // K and V tile at k0 -> buffer `buf`, asynchronously (16-byte copies straight into the operand layouts, zeros past
+  // key_end): 64 keys x 8 chunks of 8 values, 4 chunks per thread each.  The next tile travels while this one is used.
+  auto issue_tile = [&](int k0, int buf) {
+    const uint32_t kdst = smem_u32(ks + buf * L::kTile), vdst = smem_u32(vs + buf * L::kTile);
 #pragma unroll
     for (int it = 0; it < 4; ++it) {
       const int idx = tid + kAttnTcRows * it, r = idx >> 3, c = idx & 7, key = k0 + r;
-      uint4 kk = make_uint4(0, 0, 0, 0), vv = kk;
-      if (key < key_end) {
-        const size_t at = kv.offset(b, h, key) + c * 8;
-        kk = load8<true>(kv.k + at);
-        vv = load8<true>(kv.v + at);
-      }
+      const bool inside = key < key_end;
+      const size_t at = inside ? kv.offset(b, h, key) + c * 8 : 0;
       // K as the B operand of S, K-major: (d chunk c, key group r / 8) at (c * 8 + r / 8) * 128, key r % 8 at 16 bytes each
-      *reinterpret_cast<uint4*>(ks + (c * (kAttnTcKeys / 8) + (r >> 3)) * 128 + (r & 7) * 16) = kk;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                   ::"r"(kdst + uint32_t((c * (kAttnTcKeys / 8) + (r >> 3)) * 128 + (r & 7) * 16)), "l"(kv.k + at), "r"(inside ? 16 : 0) : "memory");
       // V as the B operand of PV, MN-major (d contiguous): (key group r / 8, d chunk c) at ((r / 8) * 8 + c) * 128, key r % 8
-      *reinterpret_cast<uint4*>(vs + ((r >> 3) * (D / 8) + c) * 128 + (r & 7) * 16) = vv;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                   ::"r"(vdst + uint32_t(((r >> 3) * (D / 8) + c) * 128 + (r & 7) * 16)), "l"(kv.v + at), "r"(inside ? 16 : 0) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  if (key_end > 0) issue_tile(0, 0);
+  int buf = 0;
+  for (int k0 = 0; k0 < key_end; k0 += kAttnTcKeys, buf ^= 1) {
+    // the buffer the next tile goes to was last read by the PV contraction of the previous step, which has completed
+    if (k0 + kAttnTcKeys < key_end) {
+      issue_tile(k0 + kAttnTcKeys, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     fence_async_smem();
     __syncthreads();
@@ -124,7 +137,7 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint64_t da = tc_desc(smem_u32(qs) + kk * 2 * (kAttnTcRows / 8) * 128, (kAttnTcRows / 8) * 128, 128);
-        const uint64_t db = tc_desc(smem_u32(ks) + kk * 2 * (kAttnTcKeys / 8) * 128, (kAttnTcKeys / 8) * 128, 128);
+        const uint64_t db = tc_desc(smem_u32(ks + buf * L::kTile) + kk * 2 * (kAttnTcKeys / 8) * 128, (kAttnTcKeys / 8) * 128, 128);
         tc_mma_f16(tmem_base, da, db, idesc_s, kk > 0 ? 1u : 0u);
       }
       tc_commit(&mma_done);
@@ -171,7 +184,7 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
 #pragma unroll
       for (int kk = 0; kk < kAttnTcKeys / 16; ++kk) {
         const uint64_t da = tc_desc(smem_u32(ps) + kk * 2 * (kAttnTcRows / 8) * 128, (kAttnTcRows / 8) * 128, 128);
-        const uint64_t db = tc_desc(smem_u32(vs) + kk * 2 * (D / 8) * 128, (D / 8) * 128, 128);
+        const uint64_t db = tc_desc(smem_u32(vs + buf * L::kTile) + kk * 2 * (D / 8) * 128, (D / 8) * 128, 128);
         tc_mma_f16(tmem_base + 64u, da, db, idesc_pv, kk > 0 ? 1u : 0u);
       }
       tc_commit(&mma_done);

@@ -12,7 +12,7 @@
 //   * the K ranges of gemm()'s K split still get separate TMEM accumulators (two, alternating) and are added in range
 //     order -- by eight dedicated warps that keep the running sums in registers while the tensor cores work on the next
 //     range -- so a row's result carries the same bits as in the decode-shaped kernel, whatever the row count.
-// Warp roles (448 threads): 0 bulk-copy producer, 1 MMA issuer, 2-5 stage the rows of A (K-major core matrices),
+// Warp roles (448 threads): 0 bulk-copy producer, 1 MMA issuer, 2-5 stage the rows of A (cp.async into K-major core matrices),
 // 6-13 fold the K ranges and finish the tile (bias, GELU, residual, K/V placement, store).  Every wait is bounded.
 #pragma once
 #include <cuda.h>
@@ -89,7 +89,7 @@ gemm_wide_kernel(const GemvArgs p) {
   pdl_launch_dependents();
   if (tid == 0) {
     s_failed = 0;
-    for (int s = 0; s < kWideStages; ++s) { mbar_init(&op_full[s], 1 + kWideStagers / 32); mbar_init(&op_empty[s], 1); }
+    for (int s = 0; s < kWideStages; ++s) { mbar_init(&op_full[s], 1 + kWideStagers); mbar_init(&op_empty[s], 1); }   // producer + every stager thread
     for (int b = 0; b < 2; ++b) { mbar_init(&range_done[b], 1); mbar_init(&range_free[b], kWideFolders / 32); }
     mbar_fence_init();
   }
@@ -143,6 +143,7 @@ gemm_wide_kernel(const GemvArgs p) {
             const int slot = it % kWideStages;
             ok = wait(&op_full[slot], uint32_t(it / kWideStages) & 1u, kStatusPipeTimeout);
             if (!ok) break;
+            fence_async_smem();                                // the rows arrived through the generic proxy (cp.async)
             tc_fence_after();
             const uint32_t a_addr = smem_u32(op_a + slot * kWideImageStage), b_addr = smem_u32(op_b + slot * L::kOpBBytes);
 #pragma unroll
@@ -159,44 +160,33 @@ gemm_wide_kernel(const GemvArgs p) {
     }
   } else if (warp < 2 + kWideStagers / 32) {
     // ------------------------------------------------------------ rows of A -> K-major core matrices of the B operand
+    // Asynchronous 16-byte copies straight from global to shared memory (zero fill past the last row / past K), each
+    // thread's share of a stage signalled on the stage's barrier when its copies have landed: up to kWideStages stages of
+    // rows are in flight per CTA without passing through registers.
     const int t = tid - 64;                                    // 0..127
     constexpr int kPer = kWideRows * 8 / kWideStagers;         // 16-byte pieces per thread and stage
     int it = 0;
     bool ok = true;
-    uint4 ahead[kPer];
-    auto fetch = [&](uint4 (&dst)[kPer], int tile, int i) {
-      const int m0 = (tile / slabs) * kWideRows, k0 = i * kTcStageK;
-#pragma unroll
-      for (int j = 0; j < kPer; ++j) {
-        const int id = t + kWideStagers * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
-        const int row = m0 + mg * 8 + m8, kcol = k0 + kc * 8;
-        dst[j] = make_uint4(0, 0, 0, 0);
-        if (tile < tiles && i < stages && row < p.m && kcol < p.k) dst[j] = *reinterpret_cast<const uint4*>(p.a + size_t(row) * p.lda + kcol);
-      }
-    };
     pdl_wait();                                                // A comes from the previous kernel
-    int tile = blockIdx.x;
-    fetch(ahead, tile, 0);
-    for (; tile < tiles; tile += gridDim.x) {
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+      const int m0 = (tile / slabs) * kWideRows;
       for (int i = 0; i < stages; ++i, ++it) {
-        const int slot = it % kWideStages;
-        uint4 now[kPer];
-#pragma unroll
-        for (int j = 0; j < kPer; ++j) now[j] = ahead[j];
-        // request the next stage's rows (of this tile or the next) before waiting for the slot
-        if (i + 1 < stages) fetch(ahead, tile, i + 1); else fetch(ahead, tile + gridDim.x, 0);
+        const int slot = it % kWideStages, k0 = i * kTcStageK;
         if (ok) ok = wait(&op_empty[slot], (uint32_t(it / kWideStages) & 1u) ^ 1u, kStatusMmaTimeout);
         if (ok) {
-          uint8_t* dst = op_b + slot * L::kOpBBytes;
+          const uint32_t dst = smem_u32(op_b + slot * L::kOpBBytes);
 #pragma unroll
           for (int j = 0; j < kPer; ++j) {
             const int id = t + kWideStagers * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
-            *reinterpret_cast<uint4*>(dst + (kc * (kWideRows / 8) + mg) * 128 + m8 * 16) = now[j];
+            const int row = m0 + mg * 8 + m8, kcol = k0 + kc * 8;
+            const bool inside = row < p.m && kcol < p.k;
+            const __half* src = inside ? p.a + size_t(row) * p.lda + kcol : p.a;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                         ::"r"(dst + uint32_t((kc * (kWideRows / 8) + mg) * 128 + m8 * 16)), "l"(src), "r"(inside ? 16 : 0) : "memory");
           }
-          fence_async_smem();
+          // arrives on the barrier once this thread's copies above are complete (counted in the barrier's expected arrivals)
+          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&op_full[slot])) : "memory");
         }
-        __syncwarp();
-        if (lane == 0 && ok) mbar_arrive(&op_full[slot]);
       }
     }
   } else {
