@@ -461,6 +461,23 @@ def server_record(torch, dist, rank, world, manifest_path, model_kind, requests,
     return result
 
 
+def prefill_main(args):
+    """Only the prefill of the 32 prompts of the workload (8,248 rows in one pass), `--steps` times: the command the
+    prefill profiles under profiles/ were captured with.  Prints the host-timed milliseconds per pass."""
+    import torch
+    from tinyinfer_b200.runtime import NativeModel
+    torch.cuda.set_device(0)
+    prompts, slots = workload_prompts(), list(range(BATCH))
+    with NativeModel(None, artifact_path(), device=0, max_batch=BATCH, cache_slots=BATCH, capacity=1024) as model:
+        times = []
+        for _ in range(max(1, args.steps)):
+            model.reset_all()
+            t0 = time.perf_counter()
+            model.forward(slots, prompts, return_logits=False)
+            times.append((time.perf_counter() - t0) * 1e3)
+    print(json.dumps({"prefill_ms": times, "rows": sum(len(p) for p in prompts)}))
+
+
 def gpu_main(args, rank, world):
     torch, dist, local = setup_ranks()
 
@@ -635,6 +652,7 @@ def main():
     parser.add_argument("--no-extras", action="store_true", help="skip config 0, config 3, the operator kernels and the sweep excerpt")
     parser.add_argument("--plan", type=int, choices=[0, 1], default=None, help="decode plan: 1 persistent step (default where supported), 0 launch per operation")
     parser.add_argument("--quick", action="store_true", help="only the device-resident timed steps (for profilers)")
+    parser.add_argument("--prefill", action="store_true", help="only the prefill pass of the workload's 32 prompts, --steps times (for profilers)")
     parser.add_argument("--sweep", action="store_true", help="operator sweep of the INT8-weight GEMV/GEMM instead of the decode benchmark")
     args = parser.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -644,6 +662,9 @@ def main():
             torch.cuda.set_device(0)
             for row in operator_sweep():
                 print(json.dumps(row))
+    elif args.prefill:
+        if rank == 0:
+            prefill_main(args)
     elif args.impl == "reference":
         reference_main(args, rank, world)
     else:
