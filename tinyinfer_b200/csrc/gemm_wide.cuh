@@ -7,13 +7,15 @@
 //     of an fp16 artifact), stored once at load time in exactly the shared-memory layout tcgen05.mma wants
 //     ([slab of 128 channels][64-row stage][16 KB of MN-major core matrices]).  A stage is one contiguous 16 KB block:
 //     warp 0 fetches it with a single bulk copy, no thread ever touches a weight;
-//   * tiles of 128 channels x 128 rows, four operand stages in flight, CTAs persistent over the tiles of the problem, so
+//   * tiles of 128 channels x 128 rows, six operand stages in flight, CTAs persistent over the tiles of the problem, so
 //     the epilogue of one tile overlaps the main loop of the next;
-//   * the K ranges of gemm()'s K split still get separate TMEM accumulators (two, alternating) and are added in range
+//   * the K ranges of gemm()'s K split still get separate TMEM accumulators (three, in rotation) and are added in range
 //     order -- by eight dedicated warps that keep the running sums in registers while the tensor cores work on the next
 //     range -- so a row's result carries the same bits as in the decode-shaped kernel, whatever the row count.
-// Warp roles (448 threads): 0 bulk-copy producer, 1 MMA issuer, 2-5 stage the rows of A (cp.async into K-major core matrices),
-// 6-13 fold the K ranges and finish the tile (bias, GELU, residual, K/V placement, store).  Every wait is bounded.
+// Warp roles (384 threads): 0 bulk-copy producer, 1 MMA issuer, 2-3 stage the rows of A (cp.async into K-major core
+// matrices), 4-11 fold the K ranges and finish the tile (bias, GELU, residual, K/V placement, store) -- the finishing of a
+// tile is cut into eight pieces that run between the folds of the next tile, so it never holds the tensor cores up.
+// Every wait is bounded.
 #pragma once
 #include <cuda.h>
 
@@ -25,9 +27,10 @@
 namespace tib {
 
 constexpr int kWideRows = 128;                     // rows of A per tile = MMA N
-constexpr int kWideStages = 4;                     // operand stages (weights 16 KB + rows 16 KB each)
-constexpr int kWideStagers = 128;                  // warps 2..5
-constexpr int kWideFolders = 256;                  // warps 6..13
+constexpr int kWideStages = 6;                     // operand stages (weights 16 KB + rows 16 KB each): 192 KB in flight per SM
+constexpr int kWideStagers = 64;                   // warps 2..3
+constexpr int kWideFolders = 256;                  // warps 4..11
+constexpr int kWideBuffers = 3;                    // TMEM accumulators of one K range each: the MMAs run up to two ranges ahead of the folders
 constexpr int kWideThreads = 64 + kWideStagers + kWideFolders;
 constexpr int kWideImageStage = 128 * kTcStageK * 2;        // bytes of one weight stage in the operand image
 
@@ -75,10 +78,11 @@ gemm_wide_kernel(const GemvArgs p) {
   uint8_t* op_a = smem + L::kOpAOff;
   uint8_t* op_b = smem + L::kOpBOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
-  uint64_t *op_full = bars, *op_empty = op_full + kWideStages, *range_done = op_empty + kWideStages, *range_free = range_done + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(range_free + 2);
+  uint64_t *op_full = bars, *op_empty = op_full + kWideStages, *range_done = op_empty + kWideStages, *range_free = range_done + kWideBuffers;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(range_free + kWideBuffers);
+  static_assert((2 * kWideStages + 2 * kWideBuffers) * 8 + 8 <= 256, "barrier block");
   __shared__ int s_failed;
-  __shared__ long long s_row_base[2][kWideRows];               // K/V pool offset of each row of the tile (QKV projection), per tile parity
+  __shared__ long long s_row_base[3][kWideRows];               // K/V pool offset of each row of a tile (QKV projection); three tiles in rotation
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int slabs = (p.n + 127) / 128, row_tiles = (p.m + kWideRows - 1) / kWideRows, tiles = slabs * row_tiles;
@@ -90,10 +94,11 @@ gemm_wide_kernel(const GemvArgs p) {
   if (tid == 0) {
     s_failed = 0;
     for (int s = 0; s < kWideStages; ++s) { mbar_init(&op_full[s], 1 + kWideStagers); mbar_init(&op_empty[s], 1); }   // producer + every stager thread
-    for (int b = 0; b < 2; ++b) { mbar_init(&range_done[b], 1); mbar_init(&range_free[b], kWideFolders / 32); }
+    for (int b = 0; b < kWideBuffers; ++b) { mbar_init(&range_done[b], 1); mbar_init(&range_free[b], kWideFolders / 32); }
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 2 * kWideRows);
+  constexpr uint32_t kTmemCols = 512;                           // three accumulators of 128 columns; allocations are powers of two
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -134,8 +139,8 @@ gemm_wide_kernel(const GemvArgs p) {
       bool ok = true;
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
         for (int r = 0; r < ranges && ok; ++r, ++g) {
-          const int buffer = g & 1;
-          if (g >= 2) ok = wait(&range_free[buffer], uint32_t((g - 2) >> 1) & 1u, kStatusPipeTimeout);   // the folders have read it
+          const int buffer = g % kWideBuffers;
+          if (g >= kWideBuffers) ok = wait(&range_free[buffer], uint32_t(g / kWideBuffers - 1) & 1u, kStatusPipeTimeout);   // the folders have read it
           if (!ok) break;
           tc_fence_after();
           const int first = r * chunk_stages, last = min(stages, first + chunk_stages);
@@ -163,7 +168,7 @@ gemm_wide_kernel(const GemvArgs p) {
     // Asynchronous 16-byte copies straight from global to shared memory (zero fill past the last row / past K), each
     // thread's share of a stage signalled on the stage's barrier when its copies have landed: up to kWideStages stages of
     // rows are in flight per CTA without passing through registers.
-    const int t = tid - 64;                                    // 0..127
+    const int t = tid - 64;                                    // 0..63
     constexpr int kPer = kWideRows * 8 / kWideStagers;         // 16-byte pieces per thread and stage
     int it = 0;
     bool ok = true;
@@ -197,62 +202,103 @@ gemm_wide_kernel(const GemvArgs p) {
     const int ft = tid - (64 + kWideStagers);                  // 0..255
     int g = 0, tile_no = 0;
     bool ok = true;
+    // The tile whose sums are complete and waiting to be finished (eight pieces of eight rows per thread).
+    __half2 done[32];                                          // already rounded to fp16 after the bias: rows 2i, 2i + 1
+    bool have_done = false;
+    int done_m0 = 0, done_col = 0;
+    const long long* done_base = nullptr;
+    // Piece `piece` (rows 8 * piece .. + 7 of this thread's 64) of the finished tile: the rounding points of gemv_store
+    // (bias -> fp16 -> GELU -> fp16 -> + residual -> fp16, or K/V to their cache pages).  `res` holds the residual values.
+    auto residual_of = [&](int piece, __half (&res)[8]) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int row = done_m0 + 64 * half_rows + piece * 8 + e;
+        res[e] = f2h(0.f);
+        if (have_done && p.residual && row < p.m && done_col < p.n && !(p.k_pool && done_col >= p.kv_hidden))
+          res[e] = p.residual[size_t(row) * p.ldo + done_col];
+      }
+    };
+    auto finish_piece = [&](int piece, const __half (&res)[8]) {
+      if (!have_done || !ok || done_col >= p.n) return;
+      const bool to_cache = p.k_pool && done_col >= p.kv_hidden;
+      __half* pool = nullptr;
+      if (to_cache) {
+        const int cc = done_col - p.kv_hidden, which = cc >= p.kv_hidden, e = which ? cc - p.kv_hidden : cc;
+        pool = (which ? p.v_pool : p.k_pool) + (e >> 6) * 2048 + (e & 63);
+      }
+      __half2 mine[4] = {};
+#pragma unroll
+      for (int c = 0; c < 8; ++c)                               // unrolled: done[] is only ever indexed by constants
+        if (c == piece) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) mine[e] = done[c * 4 + e];
+        }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int j = piece * 8 + e, row = done_m0 + 64 * half_rows + j;
+        if (row < p.m) {
+          __half h = (e & 1) ? __high2half(mine[e >> 1]) : __low2half(mine[e >> 1]);
+          if (to_cache) pool[done_base[64 * half_rows + j]] = h;
+          else {
+            if (p.gelu) h = f2h(gelu_tanh(h2f(h)));
+            if (p.residual) h = f2h(h2f(res[e]) + h2f(h));
+            static_cast<__half*>(p.out)[size_t(row) * p.ldo + done_col] = h;
+          }
+        }
+      }
+    };
     pdl_wait();                                                // the residual comes from an earlier kernel
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++tile_no) {
       const int slab = tile % slabs, m0 = (tile / slabs) * kWideRows, n0 = slab * 128;
-      const int col = n0 + 32 * quarter + lane;
-      long long* row_base = s_row_base[tile_no & 1];
+      long long* row_base = s_row_base[tile_no % 3];
       if (p.k_pool) {
         for (int i = ft; i < kWideRows; i += kWideFolders) row_base[i] = m0 + i < p.m ? kv_row_base(p, m0 + i) : 0;
         asm volatile("bar.sync 4, 256;" ::: "memory");
       }
+      const int col = n0 + 32 * quarter + lane;
+      const float bias = p.bias && col < p.n ? h2f(p.bias[col]) : 0.f;
       float sum[64];
 #pragma unroll
       for (int j = 0; j < 64; ++j) sum[j] = 0.f;
       for (int r = 0; r < ranges; ++r, ++g) {
-        const int buffer = g & 1;
-        if (ok) ok = wait(&range_done[buffer], uint32_t(g >> 1) & 1u, kStatusMmaTimeout);
+        const int buffer = g % kWideBuffers;
+        __half res[8];
+        if (r < 8) residual_of(r, res);                       // requested before the wait: in flight while the range completes
+        if (ok) ok = wait(&range_done[buffer], uint32_t(g / kWideBuffers) & 1u, kStatusMmaTimeout);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
         if (ok) {
-          float lo[32], hi[32];
-          tmem_load32(taddr + uint32_t(buffer * kWideRows), lo);
-          tmem_load32(taddr + uint32_t(buffer * kWideRows) + 32u, hi);
+          float part[32];
+          tmem_load32(taddr + uint32_t(buffer * kWideRows), part);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) { sum[j] += lo[j]; sum[32 + j] += hi[j]; }
+          for (int j = 0; j < 32; ++j) sum[j] += part[j];
+          tmem_load32(taddr + uint32_t(buffer * kWideRows) + 32u, part);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) sum[32 + j] += part[j];
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(&range_free[buffer]);
+        if (r < 8) finish_piece(r, res);                      // one piece of the previous tile between two folds
       }
-      // finish: the rounding points of gemv_store (bias -> fp16 -> GELU -> fp16 -> + residual -> fp16, or K/V to their pages)
-      if (ok && col < p.n) {
-        const float bias = p.bias ? h2f(p.bias[col]) : 0.f;
-        const bool to_cache = p.k_pool && col >= p.kv_hidden;
-        __half* pool = nullptr;
-        if (to_cache) {
-          const int cc = col - p.kv_hidden, which = cc >= p.kv_hidden, e = which ? cc - p.kv_hidden : cc;
-          pool = (which ? p.v_pool : p.k_pool) + (e >> 6) * 2048 + (e & 63);
-        }
+      for (int piece = ranges; piece < 8; ++piece) {          // fewer than eight ranges: the remaining pieces of the previous tile
+        __half res[8];
+        residual_of(piece, res);
+        finish_piece(piece, res);
+      }
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {                       // fully unrolled: sum[] stays in registers
-          const int row = m0 + 64 * half_rows + j;
-          if (row < p.m) {
-            __half h = f2h(sum[j] + bias);
-            if (to_cache) pool[row_base[64 * half_rows + j]] = h;
-            else {
-              if (p.gelu) h = f2h(gelu_tanh(h2f(h)));
-              if (p.residual) h = f2h(h2f(p.residual[size_t(row) * p.ldo + col]) + h2f(h));
-              static_cast<__half*>(p.out)[size_t(row) * p.ldo + col] = h;
-            }
-          }
-        }
-      }
+      for (int j = 0; j < 32; ++j) done[j] = __halves2half2(f2h(sum[2 * j] + bias), f2h(sum[2 * j + 1] + bias));
+      have_done = true; done_m0 = m0; done_col = col; done_base = row_base;
+    }
+    for (int piece = 0; piece < 8; ++piece) {                  // the last tile of this CTA
+      __half res[8];
+      residual_of(piece, res);
+      finish_piece(piece, res);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 2 * kWideRows); }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
 }  // namespace tib
