@@ -9,6 +9,10 @@
 //                                maximum and the row sum need no shuffles
 //   PV[128 x 64] = P . V         tcgen05.mma with P K-major and V as it is stored (head dimension contiguous = MN-major)
 //   O = O * alpha + PV           in registers (64 fp32 per thread)
+// The two contractions of neighbouring key tiles overlap the softmax: S of tile i+1 is issued before the softmax of tile
+// i starts (two S accumulators in TMEM, K/V tiles in a ring of three filled by cp.async one tile ahead), and PV of tile
+// i is folded into O only when tile i+1 needs the P buffer -- the additions happen in the same order as if every step
+// were waited for at once, so the pipelining does not change a bit of the result.
 // The probabilities enter the second contraction rounded to fp16 (the reference multiplies fp32 p by fp16 v); the
 // difference is far inside the operator gate (atol = rtol = 0.02).  A row's result depends on its own keys only -- key
 // tiles start at key 0 whatever the query tile -- so it does not change with the batch or with the chunking of a prompt.
@@ -29,9 +33,10 @@ constexpr int kAttnTcMinRows = 64;    // requests with fewer query rows stay on 
 struct AttnTcSmem {
   static constexpr int kTile = kAttnTcKeys * 64 * 2;                // one K or V tile: 8 KB
   static constexpr int kQOff = 0;                                   // Q  [128 x 64]  K-major core matrices, 16 KB
-  static constexpr int kKOff = kQOff + kAttnTcRows * 64 * 2;        // K  2 x [64 keys x 64]  K-major (double buffer)
-  static constexpr int kVOff = kKOff + 2 * kTile;                   // V  2 x [64 keys x 64]  MN-major (d contiguous)
-  static constexpr int kPOff = kVOff + 2 * kTile;                   // P  [128 x 64 keys]  K-major, 16 KB
+  static constexpr int kRing = 3;                                   // K/V tiles in rotation
+  static constexpr int kKOff = kQOff + kAttnTcRows * 64 * 2;        // K  3 x [64 keys x 64]  K-major
+  static constexpr int kVOff = kKOff + kRing * kTile;               // V  3 x [64 keys x 64]  MN-major (d contiguous)
+  static constexpr int kPOff = kVOff + kRing * kTile;               // P  [128 x 64 keys]  K-major, 16 KB
   static constexpr int kBytes = kPOff + kAttnTcRows * kAttnTcKeys * 2;
 };
 
@@ -55,7 +60,7 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   uint8_t* ks = attn_tc_smem + L::kKOff;
   uint8_t* vs = attn_tc_smem + L::kVOff;
   uint8_t* ps = attn_tc_smem + L::kPOff;
-  __shared__ __align__(8) uint64_t mma_done;
+  __shared__ __align__(8) uint64_t s_done, pv_done;
   __shared__ uint32_t tmem_slot;
   constexpr int D = 64;
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -75,8 +80,9 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   const int key_end = last_query < q0 || bound < 0 ? 0 : int(bound < (long long)kv_valid ? bound : (long long)kv_valid);
   const long long my_last = p.causal ? off + qi : (long long)kv_valid - 1;
 
-  if (tid == 0) { mbar_init(&mma_done, 1); mbar_fence_init(); }
-  if (warp == 0) tmem_alloc(&tmem_slot, 128);
+  if (tid == 0) { mbar_init(&s_done, 1); mbar_init(&pv_done, 1); mbar_fence_init(); }
+  constexpr uint32_t kTmemCols = 256;                           // S (2 x 64 columns, alternating) at 0 and 64, PV at 128
+  if (warp == 0) tmem_alloc(&tmem_slot, kTmemCols);
   // Q rows -> K-major core matrices: (k chunk kc, row group mg) at (kc * 16 + mg) * 128, row m % 8 at 16 bytes each
   {
     const __half* src = p.q + q_base + h * p.q_sh + (long long)qi * p.q_si;
@@ -99,55 +105,80 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   float m = -CUDART_INF_F, l = 0.f, o[D];
 #pragma unroll
   for (int d = 0; d < D; ++d) o[d] = 0.f;
-  uint32_t phase = 0;
+  uint32_t phase_s = 0, phase_pv = 0;
   bool ok = true;
 
-  // K and V tile at k0 -> buffer `buf`, asynchronously (16-byte copies straight into the operand layouts, zeros past
-  // key_end): 64 keys x 8 chunks of 8 values, 4 chunks per thread each.  The next tile travels while this one is used.
-  auto issue_tile = [&](int k0, int buf) {
-    const uint32_t kdst = smem_u32(ks + buf * L::kTile), vdst = smem_u32(vs + buf * L::kTile);
+  // K and V tile `t` (keys 64 t ..) -> ring slot t % 3, asynchronously (16-byte copies straight into the operand layouts,
+  // zeros past key_end): 64 keys x 8 chunks of 8 values, 4 chunks per thread each.  One commit group per call, also for a
+  // tile past the end (empty), so that the group count does not depend on the data.
+  const int tiles = (key_end + kAttnTcKeys - 1) / kAttnTcKeys;
+  auto issue_tile = [&](int t) {
+    if (t < tiles) {
+      const int k0 = t * kAttnTcKeys, slot = t % L::kRing;
+      const uint32_t kdst = smem_u32(ks + slot * L::kTile), vdst = smem_u32(vs + slot * L::kTile);
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int idx = tid + kAttnTcRows * it, r = idx >> 3, c = idx & 7, key = k0 + r;
-      const bool inside = key < key_end;
-      const size_t at = inside ? kv.offset(b, h, key) + c * 8 : 0;
-      // K as the B operand of S, K-major: (d chunk c, key group r / 8) at (c * 8 + r / 8) * 128, key r % 8 at 16 bytes each
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                   ::"r"(kdst + uint32_t((c * (kAttnTcKeys / 8) + (r >> 3)) * 128 + (r & 7) * 16)), "l"(kv.k + at), "r"(inside ? 16 : 0) : "memory");
-      // V as the B operand of PV, MN-major (d contiguous): (key group r / 8, d chunk c) at ((r / 8) * 8 + c) * 128, key r % 8
-      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                   ::"r"(vdst + uint32_t(((r >> 3) * (D / 8) + c) * 128 + (r & 7) * 16)), "l"(kv.v + at), "r"(inside ? 16 : 0) : "memory");
+      for (int it = 0; it < 4; ++it) {
+        const int idx = tid + kAttnTcRows * it, r = idx >> 3, c = idx & 7, key = k0 + r;
+        const bool inside = key < key_end;
+        const size_t at = inside ? kv.offset(b, h, key) + c * 8 : 0;
+        // K as the B operand of S, K-major: (d chunk c, key group r / 8) at (c * 8 + r / 8) * 128, key r % 8 at 16 bytes each
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                     ::"r"(kdst + uint32_t((c * (kAttnTcKeys / 8) + (r >> 3)) * 128 + (r & 7) * 16)), "l"(kv.k + at), "r"(inside ? 16 : 0) : "memory");
+        // V as the B operand of PV, MN-major (d contiguous): (key group r / 8, d chunk c) at ((r / 8) * 8 + c) * 128, key r % 8
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
+                     ::"r"(vdst + uint32_t(((r >> 3) * (D / 8) + c) * 128 + (r & 7) * 16)), "l"(kv.v + at), "r"(inside ? 16 : 0) : "memory");
+      }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  if (key_end > 0) issue_tile(0, 0);
-  int buf = 0;
-  for (int k0 = 0; k0 < key_end; k0 += kAttnTcKeys, buf ^= 1) {
-    // the buffer the next tile goes to was last read by the PV contraction of the previous step, which has completed
-    if (k0 + kAttnTcKeys < key_end) {
-      issue_tile(k0 + kAttnTcKeys, buf ^ 1);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
+  // S of tile t into accumulator t & 1 (one thread; the tile's K has landed and the accumulator has been read)
+  auto issue_s = [&](int t) {
+    tc_fence_after();
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      const uint64_t da = tc_desc(smem_u32(qs) + kk * 2 * (kAttnTcRows / 8) * 128, (kAttnTcRows / 8) * 128, 128);
+      const uint64_t db = tc_desc(smem_u32(ks + (t % L::kRing) * L::kTile) + kk * 2 * (kAttnTcKeys / 8) * 128, (kAttnTcKeys / 8) * 128, 128);
+      tc_mma_f16(tmem_base + uint32_t(64 * (t & 1)), da, db, idesc_s, kk > 0 ? 1u : 0u);
     }
+    tc_commit(&s_done);
+  };
+  // O = O * alpha + PV of the tile whose contraction was issued last (alpha is that tile's rescaling factor)
+  auto fold_pv = [&](float alpha) {
+    if (ok) ok = mbar_wait(&pv_done, phase_pv, kStatusMmaTimeout);
+    ok = __all_sync(0xffffffffu, ok);                         // tcgen05.ld is warp-collective
+    phase_pv ^= 1u;
+    tc_fence_after();
+    if (ok) {
+      float pv[D];
+      tmem_load64(lane_addr + 128u, pv);
+#pragma unroll
+      for (int d = 0; d < D; ++d) o[d] = o[d] * alpha + pv[d];
+    }
+  };
+
+  if (tiles > 0) {
+    issue_tile(0);
+    issue_tile(1);
+    asm volatile("cp.async.wait_group 1;" ::: "memory");       // tile 0
     fence_async_smem();
     __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
-        const uint64_t da = tc_desc(smem_u32(qs) + kk * 2 * (kAttnTcRows / 8) * 128, (kAttnTcRows / 8) * 128, 128);
-        const uint64_t db = tc_desc(smem_u32(ks + buf * L::kTile) + kk * 2 * (kAttnTcKeys / 8) * 128, (kAttnTcKeys / 8) * 128, 128);
-        tc_mma_f16(tmem_base, da, db, idesc_s, kk > 0 ? 1u : 0u);
-      }
-      tc_commit(&mma_done);
-    }
-    if (ok) ok = mbar_wait(&mma_done, phase, kStatusMmaTimeout);
-    ok = __all_sync(0xffffffffu, ok);                         // tcgen05.ld is warp-collective
-    phase ^= 1u;
+    if (tid == 0) issue_s(0);
+  }
+  float alpha_pending = 1.f;
+  for (int t = 0; t < tiles; ++t) {
+    const int k0 = t * kAttnTcKeys;
+    if (ok) ok = mbar_wait(&s_done, phase_s, kStatusMmaTimeout);
+    ok = __all_sync(0xffffffffu, ok);
+    phase_s ^= 1u;
     tc_fence_after();
     float s[kAttnTcKeys];
-    if (ok) tmem_load64(lane_addr, s);
+    if (ok) tmem_load64(lane_addr + uint32_t(64 * (t & 1)), s);
+    // ---- the next tile's S runs on the tensor cores while this tile's softmax runs on the CUDA cores
+    asm volatile("cp.async.wait_group 0;" ::: "memory");       // tile t + 1, requested one step ago
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();                                          // ... by every thread; and accumulator (t + 1) & 1 has been read (step t - 1)
+    if (tid == 0 && t + 1 < tiles) issue_s(t + 1);
     // ---- online softmax of this row
     float tile_max = -CUDART_INF_F;
 #pragma unroll
@@ -171,6 +202,10 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
     }
     l = l * alpha + tile_sum;
     m = next;
+    // ---- the previous tile's PV: it frees the P buffer, the PV accumulator and ring slot (t - 1) % 3 = (t + 2) % 3
+    if (t > 0) fold_pv(alpha_pending);
+    alpha_pending = alpha;
+    issue_tile(t + 2);
     // P as the A operand of PV, K-major: (key chunk kc, row group) at (kc * 16 + tid / 8) * 128, row tid % 8
 #pragma unroll
     for (int kc = 0; kc < kAttnTcKeys / 8; ++kc)
@@ -178,30 +213,20 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
           make_uint4(packed[4 * kc], packed[4 * kc + 1], packed[4 * kc + 2], packed[4 * kc + 3]);
     fence_async_smem();
     tc_fence_before();
-    __syncthreads();
+    __syncthreads();                                          // P is complete; every thread has read the PV accumulator
     if (tid == 0) {
       tc_fence_after();
 #pragma unroll
       for (int kk = 0; kk < kAttnTcKeys / 16; ++kk) {
         const uint64_t da = tc_desc(smem_u32(ps) + kk * 2 * (kAttnTcRows / 8) * 128, (kAttnTcRows / 8) * 128, 128);
-        const uint64_t db = tc_desc(smem_u32(vs + buf * L::kTile) + kk * 2 * (D / 8) * 128, (D / 8) * 128, 128);
-        tc_mma_f16(tmem_base + 64u, da, db, idesc_pv, kk > 0 ? 1u : 0u);
+        const uint64_t db = tc_desc(smem_u32(vs + (t % L::kRing) * L::kTile) + kk * 2 * (D / 8) * 128, (D / 8) * 128, 128);
+        tc_mma_f16(tmem_base + 128u, da, db, idesc_pv, kk > 0 ? 1u : 0u);
       }
-      tc_commit(&mma_done);
+      tc_commit(&pv_done);
     }
-    if (ok) ok = mbar_wait(&mma_done, phase, kStatusMmaTimeout);
-    ok = __all_sync(0xffffffffu, ok);
-    phase ^= 1u;
-    tc_fence_after();
-    float pv[D];
-    if (ok) {
-      tmem_load64(lane_addr + 64u, pv);
-#pragma unroll
-      for (int d = 0; d < D; ++d) o[d] = o[d] * alpha + pv[d];
-    }
-    tc_fence_before();
-    __syncthreads();                                          // the tiles and both accumulators are free again
   }
+  if (tiles > 0) fold_pv(alpha_pending);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");         // only empty groups can be left
   pdl_launch_dependents();
   // Padded layout (operator ABI): rows past the request's length are written as zeros.  Packed rows (row_start given): a
   // row past the request's length belongs to another request and is left alone.
@@ -221,7 +246,7 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
     }
   }
   __syncthreads();
-  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, 128); }
+  if (warp == 0) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
 }
 
 }  // namespace tib

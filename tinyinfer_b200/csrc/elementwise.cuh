@@ -55,16 +55,26 @@ __device__ __forceinline__ void row_stats(const T* x, int cols, float eps, float
   inv = rsqrtf(tree256(v) / cols + eps);
 }
 
-// One warp copies a row of `cols` halves into shared memory as fp32 (independent, coalesced loads).
+// One warp copies a row of `cols` halves into shared memory as fp32.  Up to four 16-byte loads per lane are issued
+// before the first is used; the fp32 values go out as two 16-byte shared stores (a lane's eight floats lie 32 bytes
+// from its neighbour's, so 4-byte stores would hit each bank eight times over).
 __device__ __forceinline__ void stage_row(const __half* x, float* dst, int cols) {
   const int lane = threadIdx.x & 31;
-  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (cols & 7) == 0) {
+  if ((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (cols & 7) == 0 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll 1
-    for (int c = lane * 8; c < cols; c += 256) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(x + c);
-      const __half* h = reinterpret_cast<const __half*>(&raw);
+    for (int c0 = lane * 8; c0 < cols; c0 += 1024) {
+      uint4 raw[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) dst[c + e] = h2f(h[e]);
+      for (int u = 0; u < 4; ++u)
+        if (c0 + 256 * u < cols) raw[u] = *reinterpret_cast<const uint4*>(x + c0 + 256 * u);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (c0 + 256 * u < cols) {
+          const __half* h = reinterpret_cast<const __half*>(&raw[u]);
+          float4* out = reinterpret_cast<float4*>(dst + c0 + 256 * u);
+          out[0] = make_float4(h2f(h[0]), h2f(h[1]), h2f(h[2]), h2f(h[3]));
+          out[1] = make_float4(h2f(h[4]), h2f(h[5]), h2f(h[6]), h2f(h[7]));
+        }
     }
   } else {
 #pragma unroll 1
@@ -83,7 +93,7 @@ layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, con
                  int rows, int cols, float eps, int early_trigger) {
   trace_event(kTrLayerNorm, 0);
   if (early_trigger) pdl_launch_dependents();
-  extern __shared__ float ln_rows[];
+  extern __shared__ __align__(16) float ln_rows[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, row = blockIdx.x * 4 + warp;
   const bool staged = cols <= kLnMaxCols;
   __half* gs = reinterpret_cast<__half*>(ln_rows + size_t(4) * cols);
@@ -107,10 +117,16 @@ layernorm_kernel(const __half* x, const int32_t* row_index, const __half* g, con
     if ((reinterpret_cast<uintptr_t>(yr) & 15) == 0 && (cols & 7) == 0) {
 #pragma unroll 1
       for (int c = lane * 8; c < cols; c += 256) {
+        // 16-byte shared loads: the row (two of them per lane), gamma and beta (cols is a multiple of 8, so all three are aligned)
+        const float4 lo = *reinterpret_cast<const float4*>(xs + c), hi = *reinterpret_cast<const float4*>(xs + c + 4);
+        const uint4 graw = *reinterpret_cast<const uint4*>(gs + c), braw = *reinterpret_cast<const uint4*>(bs + c);
+        const __half* gh = reinterpret_cast<const __half*>(&graw);
+        const __half* bh = reinterpret_cast<const __half*>(&braw);
+        const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
         uint4 packed;
         __half* h = reinterpret_cast<__half*>(&packed);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) h[e] = f2h((xs[c + e] - mean) * inv * h2f(gs[c + e]) + h2f(bs[c + e]));
+        for (int e = 0; e < 8; ++e) h[e] = f2h((v[e] - mean) * inv * h2f(gh[e]) + h2f(bh[e]));
         *reinterpret_cast<uint4*>(yr + c) = packed;
       }
     } else {

@@ -82,6 +82,7 @@ gemm_wide_kernel(const GemvArgs p) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(range_free + kWideBuffers);
   static_assert((2 * kWideStages + 2 * kWideBuffers) * 8 + 8 <= 256, "barrier block");
   __shared__ int s_failed;
+  __shared__ __align__(16) __half s_piece[2][2][8 * 128];       // a piece of a finished tile on its way out: [parity][half of the rows][row][channel]
   __shared__ long long s_row_base[3][kWideRows];               // K/V pool offset of each row of a tile (QKV projection); three tiles in rotation
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -205,27 +206,28 @@ gemm_wide_kernel(const GemvArgs p) {
     // The tile whose sums are complete and waiting to be finished (eight pieces of eight rows per thread).
     __half2 done[32];                                          // already rounded to fp16 after the bias: rows 2i, 2i + 1
     bool have_done = false;
-    int done_m0 = 0, done_col = 0;
+    int done_m0 = 0, done_n0 = 0, done_col = 0;
     const long long* done_base = nullptr;
     // Piece `piece` (rows 8 * piece .. + 7 of this thread's 64) of the finished tile: the rounding points of gemv_store
-    // (bias -> fp16 -> GELU -> fp16 -> + residual -> fp16, or K/V to their cache pages).  `res` holds the residual values.
-    auto residual_of = [&](int piece, __half (&res)[8]) {
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const int row = done_m0 + 64 * half_rows + piece * 8 + e;
-        res[e] = f2h(0.f);
-        if (have_done && p.residual && row < p.m && done_col < p.n && !(p.k_pool && done_col >= p.kv_hidden))
-          res[e] = p.residual[size_t(row) * p.ldo + done_col];
-      }
+    // (bias -> fp16 -> GELU -> fp16 -> + residual -> fp16, or K/V to their cache pages).  A thread owns one channel (its
+    // TMEM lane) but the output rows run along the channels, so the four warps that share a half of the rows pass the
+    // piece through shared memory ([8 rows][128 channels]) and every thread writes 16 bytes of one row: a warp stores two
+    // runs of 256 bytes instead of thirty-two 2-byte values.  All folder warps execute the same sequence of named
+    // barriers whatever happened to their waits.
+    const int tg = ((f & 3) << 5) | lane;                      // 0..127 within the half
+    const int out_row = tg >> 4, out_c8 = (tg & 15) * 8;       // this thread's 16 bytes of a piece
+    const bool wide_stores = (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
+                             (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0 && (p.kv_hidden & 7) == 0 &&
+                             (reinterpret_cast<uintptr_t>(p.k_pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.v_pool) & 15) == 0;
+    auto residual_of = [&](int piece) {
+      uint4 res = make_uint4(0u, 0u, 0u, 0u);
+      const int row = done_m0 + 64 * half_rows + piece * 8 + out_row, c0 = done_n0 + out_c8;
+      if (have_done && wide_stores && p.residual && row < p.m && c0 + 8 <= p.n && !(p.k_pool && c0 >= p.kv_hidden))
+        res = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldo + c0);
+      return res;
     };
-    auto finish_piece = [&](int piece, const __half (&res)[8]) {
-      if (!have_done || !ok || done_col >= p.n) return;
-      const bool to_cache = p.k_pool && done_col >= p.kv_hidden;
-      __half* pool = nullptr;
-      if (to_cache) {
-        const int cc = done_col - p.kv_hidden, which = cc >= p.kv_hidden, e = which ? cc - p.kv_hidden : cc;
-        pool = (which ? p.v_pool : p.k_pool) + (e >> 6) * 2048 + (e & 63);
-      }
+    auto finish_piece = [&](int piece, uint4 res) {
+      if (!have_done) return;                                   // uniform over all folder warps
       __half2 mine[4] = {};
 #pragma unroll
       for (int c = 0; c < 8; ++c)                               // unrolled: done[] is only ever indexed by constants
@@ -233,16 +235,43 @@ gemm_wide_kernel(const GemvArgs p) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) mine[e] = done[c * 4 + e];
         }
+      __half* stage = s_piece[piece & 1][half_rows];
+      const bool plain = !(p.k_pool && done_col >= p.kv_hidden);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        const int j = piece * 8 + e, row = done_m0 + 64 * half_rows + j;
-        if (row < p.m) {
-          __half h = (e & 1) ? __high2half(mine[e >> 1]) : __low2half(mine[e >> 1]);
-          if (to_cache) pool[done_base[64 * half_rows + j]] = h;
-          else {
-            if (p.gelu) h = f2h(gelu_tanh(h2f(h)));
-            if (p.residual) h = f2h(h2f(res[e]) + h2f(h));
-            static_cast<__half*>(p.out)[size_t(row) * p.ldo + done_col] = h;
+        __half h = (e & 1) ? __high2half(mine[e >> 1]) : __low2half(mine[e >> 1]);
+        if (p.gelu && plain) h = f2h(gelu_tanh(h2f(h)));
+        stage[e * 128 + 32 * quarter + lane] = h;
+      }
+      if (half_rows) asm volatile("bar.sync 6, 128;" ::: "memory");
+      else asm volatile("bar.sync 5, 128;" ::: "memory");
+      const int j = piece * 8 + out_row, row = done_m0 + 64 * half_rows + j, c0 = done_n0 + out_c8;
+      if (!ok || row >= p.m || c0 >= p.n) return;
+      if (wide_stores && c0 + 8 <= p.n) {
+        uint4 packed = *reinterpret_cast<const uint4*>(stage + out_row * 128 + out_c8);
+        __half* h = reinterpret_cast<__half*>(&packed);
+        if (p.k_pool && c0 >= p.kv_hidden) {
+          const int cc = c0 - p.kv_hidden, which = cc >= p.kv_hidden, e = which ? cc - p.kv_hidden : cc;
+          *reinterpret_cast<uint4*>((which ? p.v_pool : p.k_pool) + (e >> 6) * 2048 + (e & 63) + done_base[64 * half_rows + j]) = packed;
+        } else {
+          if (p.residual) {
+            const __half* r = reinterpret_cast<const __half*>(&res);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) h[e] = f2h(h2f(r[e]) + h2f(h[e]));
+          }
+          *reinterpret_cast<uint4*>(static_cast<__half*>(p.out) + size_t(row) * p.ldo + c0) = packed;
+        }
+      } else {
+#pragma unroll 1
+        for (int e = 0; e < 8 && c0 + e < p.n; ++e) {           // ragged edge or unaligned buffers: value by value
+          const int c = c0 + e;
+          if (p.k_pool && c >= p.kv_hidden) {
+            const int cc = c - p.kv_hidden, which = cc >= p.kv_hidden, x = which ? cc - p.kv_hidden : cc;
+            ((which ? p.v_pool : p.k_pool) + (x >> 6) * 2048 + (x & 63))[done_base[64 * half_rows + j]] = stage[out_row * 128 + out_c8 + e];
+          } else {
+            __half v = stage[out_row * 128 + out_c8 + e];
+            if (p.residual) v = f2h(h2f(p.residual[size_t(row) * p.ldo + c]) + h2f(v));
+            static_cast<__half*>(p.out)[size_t(row) * p.ldo + c] = v;
           }
         }
       }
@@ -262,8 +291,8 @@ gemm_wide_kernel(const GemvArgs p) {
       for (int j = 0; j < 64; ++j) sum[j] = 0.f;
       for (int r = 0; r < ranges; ++r, ++g) {
         const int buffer = g % kWideBuffers;
-        __half res[8];
-        if (r < 8) residual_of(r, res);                       // requested before the wait: in flight while the range completes
+        uint4 res = make_uint4(0u, 0u, 0u, 0u);
+        if (r < 8) res = residual_of(r);                      // requested before the wait: in flight while the range completes
         if (ok) ok = wait(&range_done[buffer], uint32_t(g / kWideBuffers) & 1u, kStatusMmaTimeout);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
@@ -281,20 +310,12 @@ gemm_wide_kernel(const GemvArgs p) {
         if (lane == 0 && ok) mbar_arrive(&range_free[buffer]);
         if (r < 8) finish_piece(r, res);                      // one piece of the previous tile between two folds
       }
-      for (int piece = ranges; piece < 8; ++piece) {          // fewer than eight ranges: the remaining pieces of the previous tile
-        __half res[8];
-        residual_of(piece, res);
-        finish_piece(piece, res);
-      }
+      for (int piece = ranges; piece < 8; ++piece) finish_piece(piece, residual_of(piece));   // fewer than eight ranges: the rest of the previous tile
 #pragma unroll
       for (int j = 0; j < 32; ++j) done[j] = __halves2half2(f2h(sum[2 * j] + bias), f2h(sum[2 * j + 1] + bias));
-      have_done = true; done_m0 = m0; done_col = col; done_base = row_base;
+      have_done = true; done_m0 = m0; done_n0 = n0; done_col = col; done_base = row_base;
     }
-    for (int piece = 0; piece < 8; ++piece) {                  // the last tile of this CTA
-      __half res[8];
-      residual_of(piece, res);
-      finish_piece(piece, res);
-    }
+    for (int piece = 0; piece < 8; ++piece) finish_piece(piece, residual_of(piece));   // the last tile of this CTA
   }
   tc_fence_before();
   __syncthreads();
