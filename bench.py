@@ -650,7 +650,7 @@ def main():
     parser.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     parser.add_argument("--no-server", action="store_true", help="skip the batching-server workload")
     parser.add_argument("--no-extras", action="store_true", help="skip config 0, config 3, the operator kernels and the sweep excerpt")
-    parser.add_argument("--plan", type=int, choices=[0, 1], default=None, help="decode plan: 1 persistent step (default where supported), 0 launch per operation")
+    parser.add_argument("--plan", type=int, choices=[0, 1], default=None, help="decode plan: 0 launch per operation replayed as a CUDA graph (default), 1 one persistent kernel per step")
     parser.add_argument("--quick", action="store_true", help="only the device-resident timed steps (for profilers)")
     parser.add_argument("--prefill", action="store_true", help="only the prefill pass of the workload's 32 prompts, --steps times (for profilers)")
     parser.add_argument("--sweep", action="store_true", help="operator sweep of the INT8-weight GEMV/GEMM instead of the decode benchmark")
