@@ -13,7 +13,8 @@
 // i starts (two S accumulators in TMEM, K/V tiles in a ring of three filled by cp.async one tile ahead), and PV of tile
 // i is folded into O only when tile i+1 needs the P buffer -- the additions happen in the same order as if every step
 // were waited for at once, so the pipelining does not change a bit of the result.
-// The probabilities enter the second contraction rounded to fp16 (the reference multiplies fp32 p by fp16 v); the
+// The exponentials are the hardware's ex2 (__expf: relative error of a few 2^-23, against the 2^-11 rounding of P that
+// follows).  The probabilities enter the second contraction rounded to fp16 (the reference multiplies fp32 p by fp16 v); the
 // difference is far inside the operator gate (atol = rtol = 0.02).  A row's result depends on its own keys only -- key
 // tiles start at key 0 whatever the query tile -- so it does not change with the batch or with the chunking of a prompt.
 // Head dimension 64 only; other shapes stay on the SIMT kernel.
@@ -189,13 +190,13 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
       tile_max = fmaxf(tile_max, s[j]);
     }
     const float next = fmaxf(m, tile_max);
-    const float alpha = next > -CUDART_INF_F ? expf(m - next) : 1.f;      // nothing seen yet: state stays empty
+    const float alpha = next > -CUDART_INF_F ? __expf(m - next) : 1.f;      // nothing seen yet: state stays empty
     float tile_sum = 0.f;
     uint32_t packed[kAttnTcKeys / 2];
 #pragma unroll
     for (int j = 0; j < kAttnTcKeys; j += 2) {
-      const float p0 = s[j] > -CUDART_INF_F ? expf(s[j] - next) : 0.f;
-      const float p1 = s[j + 1] > -CUDART_INF_F ? expf(s[j + 1] - next) : 0.f;
+      const float p0 = s[j] > -CUDART_INF_F ? __expf(s[j] - next) : 0.f;
+      const float p1 = s[j + 1] > -CUDART_INF_F ? __expf(s[j + 1] - next) : 0.f;
       tile_sum += p0 + p1;
       const __half2 h2 = __floats2half2_rn(p0, p1);
       packed[j / 2] = *reinterpret_cast<const uint32_t*>(&h2);
