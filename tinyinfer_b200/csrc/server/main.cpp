@@ -21,6 +21,7 @@
 #include <fcntl.h>
 #include <sys/epoll.h>
 #include <sys/eventfd.h>
+#include <sys/resource.h>
 #include <sys/socket.h>
 #include <unistd.h>
 
@@ -554,6 +555,12 @@ void Server::drain_completions() {
 }
 
 void Server::run() {
+  // every queued request holds a connection: take as many descriptors as the process may have
+  rlimit files{};
+  if (getrlimit(RLIMIT_NOFILE, &files) == 0 && files.rlim_cur < files.rlim_max) {
+    files.rlim_cur = files.rlim_max;
+    setrlimit(RLIMIT_NOFILE, &files);
+  }
   listener_ = socket(AF_INET, SOCK_STREAM | SOCK_NONBLOCK | SOCK_CLOEXEC, 0);
   if (listener_ < 0) throw std::runtime_error("socket");
   const int one = 1;
