@@ -350,6 +350,14 @@ def operator_sweep(shapes=((768, 2304), (768, 768), (768, 3072), (3072, 768), (7
 
 # DRAM bytes over algorithmic bytes of one launch of the persistent decode step, from the ncu capture summarised in
 # profiles/decode_step_kernel_batch32.md (dram__bytes_read.sum + dram__bytes_write.sum of one launch).
+# dram__bytes_read + dram__bytes_write per launch, as captured once with ncu on the same shapes: (bytes, summary file)
+KERNEL_TRAFFIC = {
+    "attention_decode": (27_125_400, "profiles/attn_decode_staged_kernel_batch32.md"),
+    "qkv 768x2304": (1_910_000, "profiles/gemm_tc_kernel_decode_batch32.md"),
+    "attn proj 768x768": (740_000, "profiles/gemm_tc_kernel_decode_batch32.md"),
+    "mlp fc 768x3072": (2_500_000, "profiles/gemm_tc_kernel_decode_batch32.md"),
+    "mlp proj 3072x768": (2_660_000, "profiles/gemm_tc_kernel_decode_batch32.md"),
+}
 STEP_TRAFFIC_SOURCE = "profiles/decode_step_kernel_batch32.md"
 STEP_TRAFFIC_RATIO = None
 
@@ -368,7 +376,7 @@ def config0_record(model, weights, peak):
     model.reset_all()
     return {"workload": "GPT-2 small INT8, batch 1, 32-token prompt, 63 greedy decode steps (cache 32..94 positions), seed 0",
             "us_per_step": seconds / 63 * 1e6, "tokens_per_s": 63 / seconds, "algorithmic_bytes_per_token": nbytes / 63,
-            "achieved_GBps": nbytes / seconds / 1e9, "frac": nbytes / seconds / 1e9 / peak, "gpu_launches_per_step": 1 if model.decode_plan() == 1 else 65}
+            "achieved_GBps": nbytes / seconds / 1e9, "frac": nbytes / seconds / 1e9 / peak, "gpu_launches_per_step": 1 if model.decode_plan() == 1 else 63}
 
 
 def config3_record(device):
@@ -548,7 +556,7 @@ def gpu_main(args, rank, world):
         # kernels of one decode step.  Persistent plan: one.  Launch-per-operation plan: embed, 12 x (QKV GEMM with LayerNorm
         # prologue and K/V placement, attention, projection GEMM, FC GEMM with LayerNorm prologue, projection GEMM), final
         # LayerNorm, vocabulary GEMM, argmax, advance.
-        launches_per_step = 1 if persistent else 1 + 12 * 5 + (0 if BATCH <= 8 else 1) + 3
+        launches_per_step = 1 if persistent else 1 + 12 * 5 + (0 if BATCH <= 8 else 1) + 2   # embed, 5 per layer, final LayerNorm, lm_head with argmax, publish
         step_gbs = total_bytes / (device_ms * 1e-3) / 1e9
 
         if args.quick:
@@ -586,7 +594,7 @@ def gpu_main(args, rank, world):
             try:
                 model.decode_plan(other)
                 ms_other, _ = timed_steps(min(K, 40), 3)
-                extras["other_decode_plan"] = {"plan": "persistent step kernel (1 launch per step)" if other == 1 else "launch per operation (65 launches per step)",
+                extras["other_decode_plan"] = {"plan": "persistent step kernel (1 launch per step)" if other == 1 else "launch per operation (64 launches per step)",
                                                "ms_per_step": ms_other / min(K, 40), "config0": config0_record(model, weights, peak)}
             except RuntimeError as error:                     # plan 1 is not available for every shape / device
                 extras["other_decode_plan"] = {"unavailable": str(error)}
@@ -629,8 +637,9 @@ def gpu_main(args, rank, world):
             line["kernels_note"] = "operator kernels of the launch-per-operation plan, each timed alone (CUDA graph over > L2 buffers)"
             if not persistent:
                 top = max(kernels.items(), key=lambda kv: kv[1]["seconds"] * kv[1]["launches_per_step"])
+                traffic, traffic_source = next((v for k, v in KERNEL_TRAFFIC.items() if k in top[0]), (None, None))
                 line["roofline"] = {"kernel": top[0], "bound": "hbm", "achieved": top[1]["gbs"], "peak": peak, "unit": "GB/s", "frac": top[1]["frac"],
-                                    "traffic": None, "algorithmic_bytes": top[1]["bytes"], "peak_source": peak_source,
+                                    "traffic": traffic, "traffic_source": traffic_source, "algorithmic_bytes": top[1]["bytes"], "peak_source": peak_source,
                                     "share_of_step": top[1]["seconds"] * top[1]["launches_per_step"] / (device_ms * 1e-3 / K)}
             line["operator_sweep_768x3072"] = [{k: (round(v, 3) if isinstance(v, float) else v) for k, v in row.items()}
                                                for row in operator_sweep(((768, 3072),), (1, 32, 128, 512), gelu_too=False)]
