@@ -422,8 +422,8 @@ def server_record(torch, dist, rank, world, manifest_path, model_kind, requests,
             probe.bind(("127.0.0.1", 0))
             port = probe.getsockname()[1]
         cmd = [str(binary()), "--model", model_kind, "--port", str(port), "--devices", ",".join(map(str, range(world))),
-               "--max-batch", "64", "--max-wait-us", "2000", "--max-new-tokens", "256", "--max-pending", "8192",
-               "--max-connections", "8192", "--per-connection", "32"]
+               "--max-batch", "64", "--max-wait-us", "2000", "--max-new-tokens", "256", "--max-pending", "20000",
+               "--max-connections", "19000", "--per-connection", "32"]
         if model_kind == "native":
             cmd += ["--manifest", str(manifest_path)]
         proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)

@@ -149,7 +149,7 @@ int tc_splits(int n, int k) {
   if (forced_splits > 0) splits = forced_splits;
   return splits;
 }
-constexpr int kWideMinRows = 129;       // fewer rows: one 32 / 64 / 128-row tile of the decode-shaped kernel (with its LayerNorm prologue)
+constexpr int kWideMinRows = 257;       // fewer rows: 32 / 64-row tiles of the decode-shaped kernel (measured: 63 decode rows + a prompt of n rows, and single prompts, are faster there up to about 260 rows)
 int tc_chunk(int k, int splits) {
   const int chunk = (k + splits - 1) / splits;
   return (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
