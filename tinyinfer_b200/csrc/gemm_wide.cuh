@@ -7,15 +7,16 @@
 //     of an fp16 artifact), stored once at load time in exactly the shared-memory layout tcgen05.mma wants
 //     ([slab of 128 channels][64-row stage][16 KB of MN-major core matrices]).  A stage is one contiguous 16 KB block:
 //     warp 0 fetches it with a single bulk copy, no thread ever touches a weight;
+//   * the rows of A arrive the same way: one TMA box of 128 rows x 64 columns per stage, written with the 128-byte
+//     swizzle that tcgen05.mma reads as a K-major operand (no thread copies a row either);
 //   * tiles of 128 channels x 128 rows, six operand stages in flight, CTAs persistent over the tiles of the problem, so
 //     the epilogue of one tile overlaps the main loop of the next;
 //   * the K ranges of gemm()'s K split still get separate TMEM accumulators (three, in rotation) and are added in range
 //     order -- by eight dedicated warps that keep the running sums in registers while the tensor cores work on the next
 //     range -- so a row's result carries the same bits as in the decode-shaped kernel, whatever the row count.
-// Warp roles (384 threads): 0 bulk-copy producer, 1 MMA issuer, 2-3 stage the rows of A (cp.async into K-major core
-// matrices), 4-11 fold the K ranges and finish the tile (bias, GELU, residual, K/V placement, store) -- the finishing of a
-// tile is cut into eight pieces that run between the folds of the next tile, so it never holds the tensor cores up.
-// Every wait is bounded.
+// Warp roles (320 threads): 0 producer (bulk copy of the weights, TMA of the rows), 1 MMA issuer, 2-9 fold the K ranges
+// and finish the tile (bias, GELU, residual, K/V placement, store) -- the finishing of a tile is cut into eight pieces
+// that run between the folds of the next tile, so it never holds the tensor cores up.  Every wait is bounded.
 #pragma once
 #include <cuda.h>
 
@@ -28,10 +29,9 @@ namespace tib {
 
 constexpr int kWideRows = 128;                     // rows of A per tile = MMA N
 constexpr int kWideStages = 6;                     // operand stages (weights 16 KB + rows 16 KB each): 192 KB in flight per SM
-constexpr int kWideStagers = 64;                   // warps 2..3
-constexpr int kWideFolders = 256;                  // warps 4..11
+constexpr int kWideFolders = 256;                  // warps 2..9
 constexpr int kWideBuffers = 3;                    // TMEM accumulators of one K range each: the MMAs run up to two ranges ahead of the folders
-constexpr int kWideThreads = 64 + kWideStagers + kWideFolders;
+constexpr int kWideThreads = 64 + kWideFolders;
 constexpr int kWideImageStage = 128 * kTcStageK * 2;        // bytes of one weight stage in the operand image
 
 struct WideSmem {
@@ -39,7 +39,7 @@ struct WideSmem {
   static constexpr int kOpBBytes = kWideRows * kTcStageK * 2;
   static constexpr int kOpBOff = kOpAOff + kWideStages * kWideImageStage;
   static constexpr int kBarOff = kOpBOff + kWideStages * kOpBBytes;
-  static constexpr int kBytes = kBarOff + 256 + 128;
+  static constexpr int kBytes = kBarOff + 256 + 1024;     // the swizzled operand stages sit on 1024-byte boundaries
 };
 
 // Byte offset of element (k, c) of a [K,N] matrix inside its operand image (stages_per_slab = ceil(K / 64)).
@@ -69,12 +69,19 @@ __global__ void wide_image_kernel(const int8_t* q, const __half* w16, long long 
   *reinterpret_cast<uint4*>(image + i * 16) = *reinterpret_cast<const uint4*>(h);
 }
 
-// grid = min(tiles, SMs) persistent CTAs, block = kWideThreads.  p.w = operand image; p.k_chunk = rows per K range.
+// Shared-memory descriptor of a K-major operand written by TMA with the 128-byte swizzle: rows of 128 bytes, groups of
+// eight rows 1024 bytes apart; a 16-element K step moves the start address by 32 bytes inside the swizzled row.
+__device__ __forceinline__ uint64_t tc_desc_sw128(uint32_t smem_addr) {
+  return uint64_t((smem_addr >> 4) & 0x3fffu) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+
+// grid = min(tiles, SMs) persistent CTAs, block = kWideThreads.  p.w = operand image; p.k_chunk = rows per K range;
+// a_map = [M, K] fp16 rows of A, box 64 x 128, 128-byte swizzle.
 __global__ void __launch_bounds__(kWideThreads, 1)
-gemm_wide_kernel(const GemvArgs p) {
+gemm_wide_kernel(const __grid_constant__ CUtensorMap a_map, const GemvArgs p) {
   using L = WideSmem;
   extern __shared__ uint8_t wide_smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(wide_smem_raw) + 127) & ~uintptr_t(127));
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(wide_smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* op_a = smem + L::kOpAOff;
   uint8_t* op_b = smem + L::kOpBOff;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
@@ -94,7 +101,7 @@ gemm_wide_kernel(const GemvArgs p) {
   pdl_launch_dependents();
   if (tid == 0) {
     s_failed = 0;
-    for (int s = 0; s < kWideStages; ++s) { mbar_init(&op_full[s], 1 + kWideStagers); mbar_init(&op_empty[s], 1); }   // producer + every stager thread
+    for (int s = 0; s < kWideStages; ++s) { mbar_init(&op_full[s], 2); mbar_init(&op_empty[s], 1); }   // weights and rows are announced separately
     for (int b = 0; b < kWideBuffers; ++b) { mbar_init(&range_done[b], 1); mbar_init(&range_free[b], kWideFolders / 32); }
     mbar_fence_init();
   }
@@ -116,20 +123,32 @@ gemm_wide_kernel(const GemvArgs p) {
   };
 
   if (warp == 0) {
-    // ------------------------------------------------------------ producer: one 16 KB bulk copy per stage (weights only)
-    if (lane == 0) {
+    // ------------------------------------------------------------ producer: per stage one 16 KB bulk copy (weights) and
+    // one TMA box (rows of A).  The weights of the first stages do not depend on the previous kernel and go out ahead of
+    // the dependency wait; the two halves of a stage are announced to its barrier separately (two arrivals).
+    if (lane == 0 && int(blockIdx.x) < tiles) {
       const uint8_t* image = static_cast<const uint8_t*>(p.w);
-      int it = 0;
+      const int my_tiles = (tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+      const int total = my_tiles * stages, lead = min(total, kWideStages);
+      auto weights = [&](int idx) {
+        const int slot = idx % kWideStages, tile = int(blockIdx.x) + (idx / stages) * int(gridDim.x), i = idx % stages;
+        mbar_expect_tx(&op_full[slot], kWideImageStage);
+        bulk_load(op_a + slot * kWideImageStage, image + (size_t(tile % slabs) * stages + i) * kWideImageStage, kWideImageStage, &op_full[slot]);
+      };
+      auto rows = [&](int idx) {
+        const int slot = idx % kWideStages, tile = int(blockIdx.x) + (idx / stages) * int(gridDim.x), i = idx % stages;
+        mbar_expect_tx(&op_full[slot], L::kOpBBytes);
+        tma_load_2d(op_b + slot * L::kOpBBytes, &a_map, i * kTcStageK, (tile / slabs) * kWideRows, &op_full[slot]);
+      };
+      for (int idx = 0; idx < lead; ++idx) weights(idx);
+      pdl_wait();                                              // A comes from the previous kernel
+      for (int idx = 0; idx < lead; ++idx) rows(idx);
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const int slab = tile % slabs;
-        for (int i = 0; i < stages && ok; ++i, ++it) {
-          const int slot = it % kWideStages;
-          ok = wait(&op_empty[slot], (uint32_t(it / kWideStages) & 1u) ^ 1u, kStatusPipeTimeout);
-          if (!ok) break;
-          mbar_expect_tx(&op_full[slot], kWideImageStage);
-          bulk_load(op_a + slot * kWideImageStage, image + (size_t(slab) * stages + i) * kWideImageStage, kWideImageStage, &op_full[slot]);
-        }
+      for (int idx = lead; idx < total && ok; ++idx) {
+        ok = wait(&op_empty[idx % kWideStages], (uint32_t(idx / kWideStages) & 1u) ^ 1u, kStatusPipeTimeout);
+        if (!ok) break;
+        weights(idx);
+        rows(idx);
       }
     }
   } else if (warp == 1) {
@@ -149,13 +168,12 @@ gemm_wide_kernel(const GemvArgs p) {
             const int slot = it % kWideStages;
             ok = wait(&op_full[slot], uint32_t(it / kWideStages) & 1u, kStatusPipeTimeout);
             if (!ok) break;
-            fence_async_smem();                                // the rows arrived through the generic proxy (cp.async)
             tc_fence_after();
             const uint32_t a_addr = smem_u32(op_a + slot * kWideImageStage), b_addr = smem_u32(op_b + slot * L::kOpBBytes);
 #pragma unroll
             for (int kk = 0; kk < kTcStageK / 16; ++kk) {
               const uint64_t da = tc_desc(a_addr + kk * 2 * 2048, 2048u, 128u);
-              const uint64_t db = tc_desc(b_addr + kk * 2 * (kWideRows / 8) * 128, (kWideRows / 8) * 128, 128);
+              const uint64_t db = tc_desc_sw128(b_addr + kk * 32);
               tc_mma_f16(tmem_base + uint32_t(buffer * kWideRows), da, db, idesc, (i > first || kk > 0) ? 1u : 0u);
             }
             tc_commit(&op_empty[slot]);
@@ -164,43 +182,12 @@ gemm_wide_kernel(const GemvArgs p) {
         }
       }
     }
-  } else if (warp < 2 + kWideStagers / 32) {
-    // ------------------------------------------------------------ rows of A -> K-major core matrices of the B operand
-    // Asynchronous 16-byte copies straight from global to shared memory (zero fill past the last row / past K), each
-    // thread's share of a stage signalled on the stage's barrier when its copies have landed: up to kWideStages stages of
-    // rows are in flight per CTA without passing through registers.
-    const int t = tid - 64;                                    // 0..63
-    constexpr int kPer = kWideRows * 8 / kWideStagers;         // 16-byte pieces per thread and stage
-    int it = 0;
-    bool ok = true;
-    pdl_wait();                                                // A comes from the previous kernel
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-      const int m0 = (tile / slabs) * kWideRows;
-      for (int i = 0; i < stages; ++i, ++it) {
-        const int slot = it % kWideStages, k0 = i * kTcStageK;
-        if (ok) ok = wait(&op_empty[slot], (uint32_t(it / kWideStages) & 1u) ^ 1u, kStatusMmaTimeout);
-        if (ok) {
-          const uint32_t dst = smem_u32(op_b + slot * L::kOpBBytes);
-#pragma unroll
-          for (int j = 0; j < kPer; ++j) {
-            const int id = t + kWideStagers * j, m8 = id & 7, kc = (id >> 3) & 7, mg = id >> 6;
-            const int row = m0 + mg * 8 + m8, kcol = k0 + kc * 8;
-            const bool inside = row < p.m && kcol < p.k;
-            const __half* src = inside ? p.a + size_t(row) * p.lda + kcol : p.a;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;"
-                         ::"r"(dst + uint32_t((kc * (kWideRows / 8) + mg) * 128 + m8 * 16)), "l"(src), "r"(inside ? 16 : 0) : "memory");
-          }
-          // arrives on the barrier once this thread's copies above are complete (counted in the barrier's expected arrivals)
-          asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&op_full[slot])) : "memory");
-        }
-      }
-    }
   } else {
     // ------------------------------------------------------------ fold the K ranges, finish the tile
-    const int f = warp - (2 + kWideStagers / 32);              // 0..7
+    const int f = warp - 2;                                    // 0..7
     const int quarter = warp & 3, half_rows = f >> 2;           // TMEM lanes 32 * quarter .., columns 64 * half_rows ..
     const uint32_t taddr = tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(64 * half_rows);
-    const int ft = tid - (64 + kWideStagers);                  // 0..255
+    const int ft = tid - 64;                                   // 0..255
     int g = 0, tile_no = 0;
     bool ok = true;
     // The tile whose sums are complete and waiting to be finished (eight pieces of eight rows per thread).

@@ -174,12 +174,16 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   // Many rows (prefill) of a matrix that has an operand image: the tile kernel built for that regime (gemm_wide.cuh), with
   // the K ranges of the split below, so a row's result is the one the decode-shaped kernel gives.
   if (c.w_image && c.m >= kWideMinRows && !c.out_fp32 && !c.ln_gamma && c.k % 8 == 0 && c.lda % 8 == 0 && reinterpret_cast<uintptr_t>(c.a) % 16 == 0) {
-    a.w = c.w_image;
-    a.k_chunk = tc_chunk(c.k, tc_splits(c.n, c.k));
-    const int tiles = ((c.n + 127) / 128) * ((c.m + kWideRows - 1) / kWideRows);
-    const cudaError_t ready = allow_smem(gemm_wide_kernel, WideSmem::kBytes);
-    if (ready != cudaSuccess) return ready;
-    return launch(gemm_wide_kernel, dim3(unsigned(std::min(tiles, sm_count()))), dim3(kWideThreads), WideSmem::kBytes, o, 1, a);
+    CUtensorMap rows; std::memset(&rows, 0, sizeof rows);
+    if (make_map_2d(&rows, c.a, false, uint64_t(c.m), uint64_t(c.k), uint64_t(c.lda), 64, uint32_t(kWideRows), true)) {
+      GemvArgs w = a;
+      w.w = c.w_image;
+      w.k_chunk = tc_chunk(c.k, tc_splits(c.n, c.k));
+      const int tiles = ((c.n + 127) / 128) * ((c.m + kWideRows - 1) / kWideRows);
+      const cudaError_t ready = allow_smem(gemm_wide_kernel, WideSmem::kBytes);
+      if (ready != cudaSuccess) return ready;
+      return launch(gemm_wide_kernel, dim3(unsigned(std::min(tiles, sm_count()))), dim3(kWideThreads), WideSmem::kBytes, o, 1, rows, w);
+    }
   }
   // Tensor-core path: int8 weights, 5 or more rows of A, operands addressable by TMA / 16-byte loads.
   static const int tc_min_rows = env_int("TINYINFER_B200_TC_MIN_ROWS", 5);      // measurement aid: where the SIMT kernel hands over
