@@ -14,9 +14,9 @@
 //   * the K ranges of gemm()'s K split still get separate TMEM accumulators (three, in rotation) and are added in range
 //     order -- by eight dedicated warps that keep the running sums in registers while the tensor cores work on the next
 //     range -- so a row's result carries the same bits as in the decode-shaped kernel, whatever the row count.
-// Warp roles (320 threads): 0 producer (bulk copy of the weights, TMA of the rows), 1 MMA issuer, 2-9 fold the K ranges
-// and finish the tile (bias, GELU, residual, K/V placement, store) -- the finishing of a tile is cut into eight pieces
-// that run between the folds of the next tile, so it never holds the tensor cores up.  Every wait is bounded.
+// Warp roles (576 threads): 0 producer (bulk copy of the weights, TMA of the rows), 1 MMA issuer, 2-17 fold the K ranges
+// and finish the tile (bias, GELU, residual, K/V placement, store) -- the finishing of a tile is cut into pieces of
+// eight rows that run between the folds of the next tile, so it never holds the tensor cores up.  Every wait is bounded.
 #pragma once
 #include <cuda.h>
 
@@ -29,7 +29,10 @@ namespace tib {
 
 constexpr int kWideRows = 128;                     // rows of A per tile = MMA N
 constexpr int kWideStages = 6;                     // operand stages (weights 16 KB + rows 16 KB each): 192 KB in flight per SM
-constexpr int kWideFolders = 256;                  // warps 2..9
+constexpr int kWideFolders = 512;                  // warps 2..17: four per TMEM lane quarter, each with a quarter of the tile's rows
+constexpr int kWideGroups = kWideFolders / 128;    // groups of four warps that share rows of the tile
+constexpr int kWideOwn = kWideRows / kWideGroups;  // rows of a tile one folder thread owns (for its channel)
+constexpr int kWidePieces = kWideOwn / 8;          // pieces of eight rows a finished tile leaves in
 constexpr int kWideBuffers = 3;                    // TMEM accumulators of one K range each: the MMAs run up to two ranges ahead of the folders
 constexpr int kWideThreads = 64 + kWideFolders;
 constexpr int kWideImageStage = 128 * kTcStageK * 2;        // bytes of one weight stage in the operand image
@@ -89,7 +92,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap a_map, const GemvArgs p) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(range_free + kWideBuffers);
   static_assert((2 * kWideStages + 2 * kWideBuffers) * 8 + 8 <= 256, "barrier block");
   __shared__ int s_failed;
-  __shared__ __align__(16) __half s_piece[2][2][8 * 128];       // a piece of a finished tile on its way out: [parity][half of the rows][row][channel]
+  __shared__ __align__(16) __half s_piece[2][kWideGroups][8 * 128];   // a piece of a finished tile on its way out: [parity][row group][row][channel]
   __shared__ long long s_row_base[3][kWideRows];               // K/V pool offset of each row of a tile (QKV projection); three tiles in rotation
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -184,31 +187,31 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap a_map, const GemvArgs p) {
     }
   } else {
     // ------------------------------------------------------------ fold the K ranges, finish the tile
-    const int f = warp - 2;                                    // 0..7
-    const int quarter = warp & 3, half_rows = f >> 2;           // TMEM lanes 32 * quarter .., columns 64 * half_rows ..
-    const uint32_t taddr = tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(64 * half_rows);
+    const int f = warp - 2;                                    // 0..15
+    const int quarter = warp & 3, group = f >> 2;               // TMEM lanes 32 * quarter .., columns kWideOwn * group ..
+    const uint32_t taddr = tmem_base + (uint32_t(32 * quarter) << 16) + uint32_t(kWideOwn * group);
     const int ft = tid - 64;                                   // 0..255
     int g = 0, tile_no = 0;
     bool ok = true;
     // The tile whose sums are complete and waiting to be finished (eight pieces of eight rows per thread).
-    __half2 done[32];                                          // already rounded to fp16 after the bias: rows 2i, 2i + 1
+    __half2 done[kWideOwn / 2];                                // already rounded to fp16 after the bias: rows 2i, 2i + 1
     bool have_done = false;
     int done_m0 = 0, done_n0 = 0, done_col = 0;
     const long long* done_base = nullptr;
-    // Piece `piece` (rows 8 * piece .. + 7 of this thread's 64) of the finished tile: the rounding points of gemv_store
+    // Piece `piece` (rows 8 * piece .. + 7 of this thread's kWideOwn) of the finished tile: the rounding points of gemv_store
     // (bias -> fp16 -> GELU -> fp16 -> + residual -> fp16, or K/V to their cache pages).  A thread owns one channel (its
-    // TMEM lane) but the output rows run along the channels, so the four warps that share a half of the rows pass the
+    // TMEM lane) but the output rows run along the channels, so the four warps that share a group of rows pass the
     // piece through shared memory ([8 rows][128 channels]) and every thread writes 16 bytes of one row: a warp stores two
     // runs of 256 bytes instead of thirty-two 2-byte values.  All folder warps execute the same sequence of named
     // barriers whatever happened to their waits.
-    const int tg = ((f & 3) << 5) | lane;                      // 0..127 within the half
+    const int tg = ((f & 3) << 5) | lane;                      // 0..127 within the group
     const int out_row = tg >> 4, out_c8 = (tg & 15) * 8;       // this thread's 16 bytes of a piece
     const bool wide_stores = (p.ldo & 7) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 &&
                              (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0 && (p.kv_hidden & 7) == 0 &&
                              (reinterpret_cast<uintptr_t>(p.k_pool) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.v_pool) & 15) == 0;
     auto residual_of = [&](int piece) {
       uint4 res = make_uint4(0u, 0u, 0u, 0u);
-      const int row = done_m0 + 64 * half_rows + piece * 8 + out_row, c0 = done_n0 + out_c8;
+      const int row = done_m0 + kWideOwn * group + piece * 8 + out_row, c0 = done_n0 + out_c8;
       if (have_done && wide_stores && p.residual && row < p.m && c0 + 8 <= p.n && !(p.k_pool && c0 >= p.kv_hidden))
         res = *reinterpret_cast<const uint4*>(p.residual + size_t(row) * p.ldo + c0);
       return res;
@@ -217,12 +220,12 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap a_map, const GemvArgs p) {
       if (!have_done) return;                                   // uniform over all folder warps
       __half2 mine[4] = {};
 #pragma unroll
-      for (int c = 0; c < 8; ++c)                               // unrolled: done[] is only ever indexed by constants
+      for (int c = 0; c < kWidePieces; ++c)                     // unrolled: done[] is only ever indexed by constants
         if (c == piece) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) mine[e] = done[c * 4 + e];
         }
-      __half* stage = s_piece[piece & 1][half_rows];
+      __half* stage = s_piece[piece & 1][group];
       const bool plain = !(p.k_pool && done_col >= p.kv_hidden);
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -230,16 +233,15 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap a_map, const GemvArgs p) {
         if (p.gelu && plain) h = f2h(gelu_tanh(h2f(h)));
         stage[e * 128 + 32 * quarter + lane] = h;
       }
-      if (half_rows) asm volatile("bar.sync 6, 128;" ::: "memory");
-      else asm volatile("bar.sync 5, 128;" ::: "memory");
-      const int j = piece * 8 + out_row, row = done_m0 + 64 * half_rows + j, c0 = done_n0 + out_c8;
+      asm volatile("bar.sync %0, 128;" ::"r"(5 + group) : "memory");
+      const int j = piece * 8 + out_row, row = done_m0 + kWideOwn * group + j, c0 = done_n0 + out_c8;
       if (!ok || row >= p.m || c0 >= p.n) return;
       if (wide_stores && c0 + 8 <= p.n) {
         uint4 packed = *reinterpret_cast<const uint4*>(stage + out_row * 128 + out_c8);
         __half* h = reinterpret_cast<__half*>(&packed);
         if (p.k_pool && c0 >= p.kv_hidden) {
           const int cc = c0 - p.kv_hidden, which = cc >= p.kv_hidden, e = which ? cc - p.kv_hidden : cc;
-          *reinterpret_cast<uint4*>((which ? p.v_pool : p.k_pool) + (e >> 6) * 2048 + (e & 63) + done_base[64 * half_rows + j]) = packed;
+          *reinterpret_cast<uint4*>((which ? p.v_pool : p.k_pool) + (e >> 6) * 2048 + (e & 63) + done_base[kWideOwn * group + j]) = packed;
         } else {
           if (p.residual) {
             const __half* r = reinterpret_cast<const __half*>(&res);
@@ -254,7 +256,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap a_map, const GemvArgs p) {
           const int c = c0 + e;
           if (p.k_pool && c >= p.kv_hidden) {
             const int cc = c - p.kv_hidden, which = cc >= p.kv_hidden, x = which ? cc - p.kv_hidden : cc;
-            ((which ? p.v_pool : p.k_pool) + (x >> 6) * 2048 + (x & 63))[done_base[64 * half_rows + j]] = stage[out_row * 128 + out_c8 + e];
+            ((which ? p.v_pool : p.k_pool) + (x >> 6) * 2048 + (x & 63))[done_base[kWideOwn * group + j]] = stage[out_row * 128 + out_c8 + e];
           } else {
             __half v = stage[out_row * 128 + out_c8 + e];
             if (p.residual) v = f2h(h2f(p.residual[size_t(row) * p.ldo + c]) + h2f(v));
@@ -269,17 +271,18 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap a_map, const GemvArgs p) {
       long long* row_base = s_row_base[tile_no % 3];
       if (p.k_pool) {
         for (int i = ft; i < kWideRows; i += kWideFolders) row_base[i] = m0 + i < p.m ? kv_row_base(p, m0 + i) : 0;
-        asm volatile("bar.sync 4, 256;" ::: "memory");
+        asm volatile("bar.sync 4, %0;" ::"n"(kWideFolders) : "memory");
       }
       const int col = n0 + 32 * quarter + lane;
       const float bias = p.bias && col < p.n ? h2f(p.bias[col]) : 0.f;
-      float sum[64];
+      static_assert(kWideOwn == 32, "one tcgen05.ld of 32 columns per range and folder warp");
+      float sum[kWideOwn];
 #pragma unroll
-      for (int j = 0; j < 64; ++j) sum[j] = 0.f;
+      for (int j = 0; j < kWideOwn; ++j) sum[j] = 0.f;
       for (int r = 0; r < ranges; ++r, ++g) {
         const int buffer = g % kWideBuffers;
         uint4 res = make_uint4(0u, 0u, 0u, 0u);
-        if (r < 8) res = residual_of(r);                      // requested before the wait: in flight while the range completes
+        if (r < kWidePieces) res = residual_of(r);            // requested before the wait: in flight while the range completes
         if (ok) ok = wait(&range_done[buffer], uint32_t(g / kWideBuffers) & 1u, kStatusMmaTimeout);
         ok = __all_sync(0xffffffffu, ok);
         tc_fence_after();
@@ -288,21 +291,18 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap a_map, const GemvArgs p) {
           tmem_load32(taddr + uint32_t(buffer * kWideRows), part);
 #pragma unroll
           for (int j = 0; j < 32; ++j) sum[j] += part[j];
-          tmem_load32(taddr + uint32_t(buffer * kWideRows) + 32u, part);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) sum[32 + j] += part[j];
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0 && ok) mbar_arrive(&range_free[buffer]);
-        if (r < 8) finish_piece(r, res);                      // one piece of the previous tile between two folds
+        if (r < kWidePieces) finish_piece(r, res);            // one piece of the previous tile between two folds
       }
-      for (int piece = ranges; piece < 8; ++piece) finish_piece(piece, residual_of(piece));   // fewer than eight ranges: the rest of the previous tile
+      for (int piece = ranges; piece < kWidePieces; ++piece) finish_piece(piece, residual_of(piece));   // fewer ranges than pieces: the rest of the previous tile
 #pragma unroll
-      for (int j = 0; j < 32; ++j) done[j] = __halves2half2(f2h(sum[2 * j] + bias), f2h(sum[2 * j + 1] + bias));
+      for (int j = 0; j < kWideOwn / 2; ++j) done[j] = __halves2half2(f2h(sum[2 * j] + bias), f2h(sum[2 * j + 1] + bias));
       have_done = true; done_m0 = m0; done_n0 = n0; done_col = col; done_base = row_base;
     }
-    for (int piece = 0; piece < 8; ++piece) finish_piece(piece, residual_of(piece));   // the last tile of this CTA
+    for (int piece = 0; piece < kWidePieces; ++piece) finish_piece(piece, residual_of(piece));   // the last tile of this CTA
   }
   tc_fence_before();
   __syncthreads();
