@@ -149,7 +149,7 @@ int tc_splits(int n, int k) {
   if (forced_splits > 0) splits = forced_splits;
   return splits;
 }
-constexpr int kWideMinRows = 257;       // fewer rows: 32 / 64-row tiles of the decode-shaped kernel (measured: 63 decode rows + a prompt of n rows, and single prompts, are faster there up to about 260 rows)
+constexpr int kWideMinRows = 129;       // fewer rows: 32 / 64-row tiles of the decode-shaped kernel with its LayerNorm prologue (measured from 129 rows up: 63 decode rows + a prompt of n rows, and single prompts, are faster on the many-row kernel)
 int tc_chunk(int k, int splits) {
   const int chunk = (k + splits - 1) / splits;
   return (chunk + kTcStageK - 1) / kTcStageK * kTcStageK;
@@ -173,7 +173,8 @@ cudaError_t gemm(const GemmCall& c, const LaunchOpts& o) {
   }
   // Many rows (prefill) of a matrix that has an operand image: the tile kernel built for that regime (gemm_wide.cuh), with
   // the K ranges of the split below, so a row's result is the one the decode-shaped kernel gives.
-  if (c.w_image && c.m >= kWideMinRows && !c.out_fp32 && !c.ln_gamma && c.k % 8 == 0 && c.lda % 8 == 0 && reinterpret_cast<uintptr_t>(c.a) % 16 == 0) {
+  static const int wide_min_rows = env_int("TINYINFER_B200_WIDE_MIN_ROWS", kWideMinRows);    // measurement aid
+  if (c.w_image && c.m >= wide_min_rows && !c.out_fp32 && !c.ln_gamma && c.k % 8 == 0 && c.lda % 8 == 0 && reinterpret_cast<uintptr_t>(c.a) % 16 == 0) {
     CUtensorMap rows; std::memset(&rows, 0, sizeof rows);
     if (make_map_2d(&rows, c.a, false, uint64_t(c.m), uint64_t(c.k), uint64_t(c.lda), 64, uint32_t(kWideRows), true)) {
       GemvArgs w = a;

@@ -501,7 +501,7 @@ struct ti_llm_model {
   // may start at once; measured: a few microseconds per step at small batches.  After a LayerNorm it did not pay.
   bool ln_trigger = false, gemm_trigger = true;
   tib::LaunchOpts ln_opts() const { tib::LaunchOpts o; o.stream = stream; o.pdl = use_pdl; o.early_trigger = ln_trigger; return o; }
-  bool wide_gemm = true;                         // passes of 257 rows and more run their GEMMs from the operand images
+  bool wide_gemm = true;                         // passes of 129 rows and more run their GEMMs from the operand images
   bool tc_attention = true;                      // requests with 64 or more rows in a pass: attention on the tensor cores
   bool mixed_attention = true;                   // mixed passes: single-token requests through the decode kernel
   bool attn_trigger = true;                      // the projection GEMM after attention prefetches its weights meanwhile
