@@ -5,10 +5,11 @@
 // q.k * rsqrt(64); fp32 online softmax; rows that see no key are exact zeros.  What changes is where the two
 // contractions run: one CTA owns 128 query rows of one (request, head) and walks the keys 64 at a time,
 //   S[128 x 64] = Q . K^T        tcgen05.mma kind::f16, both operands K-major in shared memory, accumulator in TMEM
-//   P = exp(S - max) (fp16)      one thread per query row: the row of S comes out of TMEM with tcgen05.ld, so the row
-//                                maximum and the row sum need no shuffles
+//   P = exp(S - max) (fp16)      two threads per query row (32 keys of the tile each): their halves of the row of S come
+//                                out of TMEM with tcgen05.ld; the tile maximum is exchanged through shared memory under a
+//                                barrier the pipeline needs anyway, the denominator is kept in two shares until the end
 //   PV[128 x 64] = P . V         tcgen05.mma with P K-major and V as it is stored (head dimension contiguous = MN-major)
-//   O = O * alpha + PV           in registers (64 fp32 per thread)
+//   O = O * alpha + PV           in registers (32 fp32 per thread)
 // The two contractions of neighbouring key tiles overlap the softmax: S of tile i+1 is issued before the softmax of tile
 // i starts (two S accumulators in TMEM, K/V tiles in a ring of three filled by cp.async one tile ahead), and PV of tile
 // i is folded into O only when tile i+1 needs the P buffer -- the additions happen in the same order as if every step
@@ -50,10 +51,12 @@ __device__ __forceinline__ void tmem_load64(uint32_t taddr, float (&v)[64]) {
   for (int i = 0; i < 32; ++i) { v[i] = lo[i]; v[32 + i] = hi[i]; }
 }
 
-// grid = (ceil(max query rows / 128), heads, batch), block = 128.  min_q: requests with fewer rows are skipped (another
+constexpr int kAttnTcThreads = 2 * kAttnTcRows;    // two threads per query row: warps 0-3 hold keys / dims 0..31, warps 4-7 hold 32..63
+
+// grid = (ceil(max query rows / 128), heads, batch), block = 256.  min_q: requests with fewer rows are skipped (another
 // kernel serves them); 0 = serve every request.
 template <typename KV>
-__global__ void __launch_bounds__(kAttnTcRows, 2)
+__global__ void __launch_bounds__(kAttnTcThreads, 2)
 attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   using L = AttnTcSmem;
   extern __shared__ __align__(128) uint8_t attn_tc_smem[];
@@ -63,8 +66,11 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   uint8_t* ps = attn_tc_smem + L::kPOff;
   __shared__ __align__(8) uint64_t s_done, pv_done;
   __shared__ uint32_t tmem_slot;
-  constexpr int D = 64;
+  __shared__ float s_half_max[2][2][kAttnTcRows];               // [tile parity][half][row]: a half's maximum of the tile, for its partner
+  __shared__ float s_half_sum[2][kAttnTcRows];                  // the halves' shares of the softmax denominator (end of the kernel)
+  constexpr int D = 64, H = 32;                                 // head size; keys of a tile and output dims per thread
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int row = tid & (kAttnTcRows - 1), half = tid >> 7;     // TMEM lane = row; a warp reads lanes 32 * (warp % 4) ..
   const int h = blockIdx.y, b = blockIdx.z, q0 = blockIdx.x * kAttnTcRows;
   pdl_wait();
   const int q_len_b = p.q_lengths[b];
@@ -74,7 +80,7 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   const long long off = p.offsets[b];
   const long long q_base = p.row_start ? p.row_start[b] * p.q_si : b * p.q_sb;
   const long long o_base = p.row_start ? p.row_start[b] * p.o_si : b * p.o_sb;
-  const int qi = q0 + tid;                                      // this thread's query row
+  const int qi = q0 + row;                                      // this thread's query row
   const bool active = qi < q_valid;
   const int last_query = min(q_valid, q0 + kAttnTcRows) - 1;
   long long bound = p.causal ? off + last_query + 1 : (long long)kv_valid;
@@ -88,29 +94,30 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   {
     const __half* src = p.q + q_base + h * p.q_sh + (long long)qi * p.q_si;
 #pragma unroll
-    for (int kc = 0; kc < D / 8; ++kc) {
+    for (int c = 0; c < D / 16; ++c) {
+      const int kc = half * (D / 16) + c;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (active) v = load8<true>(src + kc * 8);
-      *reinterpret_cast<uint4*>(qs + (kc * (kAttnTcRows / 8) + (tid >> 3)) * 128 + (tid & 7) * 16) = v;
+      *reinterpret_cast<uint4*>(qs + (kc * (kAttnTcRows / 8) + (row >> 3)) * 128 + (row & 7) * 16) = v;
     }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  const uint32_t lane_addr = tmem_base + (uint32_t(32 * warp) << 16);
+  const uint32_t lane_addr = tmem_base + (uint32_t(32 * (warp & 3)) << 16) + uint32_t(H * half);
   // instruction descriptors: fp32 accumulate, fp16 operands, M = 128, N = 64; S: both K-major; PV: B (= V) MN-major
   constexpr uint32_t idesc_s = (1u << 4) | (uint32_t(kAttnTcKeys >> 3) << 17) | (uint32_t(kAttnTcRows >> 4) << 24);
   constexpr uint32_t idesc_pv = idesc_s | (1u << 16);
 
-  float m = -CUDART_INF_F, l = 0.f, o[D];
+  float m = -CUDART_INF_F, l = 0.f, o[H];                       // l: this half's share of the denominator
 #pragma unroll
-  for (int d = 0; d < D; ++d) o[d] = 0.f;
+  for (int d = 0; d < H; ++d) o[d] = 0.f;
   uint32_t phase_s = 0, phase_pv = 0;
   bool ok = true;
 
   // K and V tile `t` (keys 64 t ..) -> ring slot t % 3, asynchronously (16-byte copies straight into the operand layouts,
-  // zeros past key_end): 64 keys x 8 chunks of 8 values, 4 chunks per thread each.  One commit group per call, also for a
+  // zeros past key_end): 64 keys x 8 chunks of 8 values, 2 chunks per thread each.  One commit group per call, also for a
   // tile past the end (empty), so that the group count does not depend on the data.
   const int tiles = (key_end + kAttnTcKeys - 1) / kAttnTcKeys;
   auto issue_tile = [&](int t) {
@@ -118,8 +125,8 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
       const int k0 = t * kAttnTcKeys, slot = t % L::kRing;
       const uint32_t kdst = smem_u32(ks + slot * L::kTile), vdst = smem_u32(vs + slot * L::kTile);
 #pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int idx = tid + kAttnTcRows * it, r = idx >> 3, c = idx & 7, key = k0 + r;
+      for (int it = 0; it < kAttnTcKeys * 8 / kAttnTcThreads; ++it) {
+        const int idx = tid + kAttnTcThreads * it, r = idx >> 3, c = idx & 7, key = k0 + r;
         const bool inside = key < key_end;
         const size_t at = inside ? kv.offset(b, h, key) + c * 8 : 0;
         // K as the B operand of S, K-major: (d chunk c, key group r / 8) at (c * 8 + r / 8) * 128, key r % 8 at 16 bytes each
@@ -150,10 +157,10 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
     phase_pv ^= 1u;
     tc_fence_after();
     if (ok) {
-      float pv[D];
-      tmem_load64(lane_addr + 128u, pv);
+      float pv[H];
+      tmem_load32(lane_addr + 128u, pv);
 #pragma unroll
-      for (int d = 0; d < D; ++d) o[d] = o[d] * alpha + pv[d];
+      for (int d = 0; d < H; ++d) o[d] = o[d] * alpha + pv[d];
     }
   };
 
@@ -167,34 +174,37 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   }
   float alpha_pending = 1.f;
   for (int t = 0; t < tiles; ++t) {
-    const int k0 = t * kAttnTcKeys;
+    const int k0 = t * kAttnTcKeys + H * half;                 // first key of this thread's half of the tile
     if (ok) ok = mbar_wait(&s_done, phase_s, kStatusMmaTimeout);
     ok = __all_sync(0xffffffffu, ok);
     phase_s ^= 1u;
     tc_fence_after();
-    float s[kAttnTcKeys];
-    if (ok) tmem_load64(lane_addr + uint32_t(64 * (t & 1)), s);
-    // ---- the next tile's S runs on the tensor cores while this tile's softmax runs on the CUDA cores
-    asm volatile("cp.async.wait_group 0;" ::: "memory");       // tile t + 1, requested one step ago
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();                                          // ... by every thread; and accumulator (t + 1) & 1 has been read (step t - 1)
-    if (tid == 0 && t + 1 < tiles) issue_s(t + 1);
-    // ---- online softmax of this row
+    float s[H];
+    if (ok) tmem_load32(lane_addr + uint32_t(64 * (t & 1)), s);
+    // ---- this half's maximum of the tile goes to the partner through shared memory; the barrier that publishes it is
+    // the one the next tile's S needs anyway
     float tile_max = -CUDART_INF_F;
 #pragma unroll
-    for (int j = 0; j < kAttnTcKeys; ++j) {
+    for (int j = 0; j < H; ++j) {
       const int key = k0 + j;
       const bool visible = ok && active && key < key_end && (long long)key <= my_last;
       s[j] = visible ? s[j] * rsqrtf(float(D)) : -CUDART_INF_F;
       tile_max = fmaxf(tile_max, s[j]);
     }
-    const float next = fmaxf(m, tile_max);
+    s_half_max[t & 1][half][row] = tile_max;
+    // ---- the next tile's S runs on the tensor cores while this tile's softmax runs on the CUDA cores
+    asm volatile("cp.async.wait_group 0;" ::: "memory");       // tile t + 1, requested one step ago
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();                                          // ... by every thread; accumulator (t + 1) & 1 has been read (step t - 1)
+    if (tid == 0 && t + 1 < tiles) issue_s(t + 1);
+    // ---- online softmax of this row (both halves compute the same maximum and rescaling factor)
+    const float next = fmaxf(m, fmaxf(tile_max, s_half_max[t & 1][half ^ 1][row]));
     const float alpha = next > -CUDART_INF_F ? __expf(m - next) : 1.f;      // nothing seen yet: state stays empty
     float tile_sum = 0.f;
-    uint32_t packed[kAttnTcKeys / 2];
+    uint32_t packed[H / 2];
 #pragma unroll
-    for (int j = 0; j < kAttnTcKeys; j += 2) {
+    for (int j = 0; j < H; j += 2) {
       const float p0 = s[j] > -CUDART_INF_F ? __expf(s[j] - next) : 0.f;
       const float p1 = s[j + 1] > -CUDART_INF_F ? __expf(s[j + 1] - next) : 0.f;
       tile_sum += p0 + p1;
@@ -207,11 +217,11 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
     if (t > 0) fold_pv(alpha_pending);
     alpha_pending = alpha;
     issue_tile(t + 2);
-    // P as the A operand of PV, K-major: (key chunk kc, row group) at (kc * 16 + tid / 8) * 128, row tid % 8
+    // P as the A operand of PV, K-major: (key chunk kc, row group) at (kc * 16 + row / 8) * 128, row % 8; this half's four chunks
 #pragma unroll
-    for (int kc = 0; kc < kAttnTcKeys / 8; ++kc)
-      *reinterpret_cast<uint4*>(ps + (kc * (kAttnTcRows / 8) + (tid >> 3)) * 128 + (tid & 7) * 16) =
-          make_uint4(packed[4 * kc], packed[4 * kc + 1], packed[4 * kc + 2], packed[4 * kc + 3]);
+    for (int c = 0; c < H / 8; ++c)
+      *reinterpret_cast<uint4*>(ps + ((half * (H / 8) + c) * (kAttnTcRows / 8) + (row >> 3)) * 128 + (row & 7) * 16) =
+          make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
     fence_async_smem();
     tc_fence_before();
     __syncthreads();                                          // P is complete; every thread has read the PV accumulator
@@ -229,12 +239,16 @@ attn_tc_kernel(const AttnArgs p, const KV kv, const int min_q) {
   if (tiles > 0) fold_pv(alpha_pending);
   asm volatile("cp.async.wait_group 0;" ::: "memory");         // only empty groups can be left
   pdl_launch_dependents();
+  // the denominator is the sum of the two halves' shares (both were rescaled by the same factors)
+  s_half_sum[half][row] = l;
+  __syncthreads();
+  l = s_half_sum[0][row] + s_half_sum[1][row];
   // Padded layout (operator ABI): rows past the request's length are written as zeros.  Packed rows (row_start given): a
   // row past the request's length belongs to another request and is left alone.
   if (ok && (p.row_start ? active : qi < p.q_len)) {
-    __half* dst = p.out + o_base + h * p.o_sh + (long long)qi * p.o_si;
+    __half* dst = p.out + o_base + h * p.o_sh + (long long)qi * p.o_si + H * half;
 #pragma unroll
-    for (int c = 0; c < D / 8; ++c) {
+    for (int c = 0; c < H / 8; ++c) {
       uint4 packed8;
       __half* hh = reinterpret_cast<__half*>(&packed8);
 #pragma unroll

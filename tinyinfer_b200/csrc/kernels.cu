@@ -383,7 +383,7 @@ cudaError_t attention_packed(const void* q, const void* k, const void* v, void* 
     const cudaError_t ready = allow_smem(attn_tc_kernel<KvPacked>, AttnTcSmem::kBytes);
     if (ready != cudaSuccess) return ready;
     const dim3 tc_grid((q_len + kAttnTcRows - 1) / kAttnTcRows, heads, batch);
-    return launch(attn_tc_kernel<KvPacked>, tc_grid, dim3(kAttnTcRows), AttnTcSmem::kBytes, o, 1, p, kv, 0);
+    return launch(attn_tc_kernel<KvPacked>, tc_grid, dim3(kAttnTcThreads), AttnTcSmem::kBytes, o, 1, p, kv, 0);
   }
   const dim3 grid((q_len + kAttnTileQ - 1) / kAttnTileQ, heads, batch);
   if (d == 64) return vec ? launch(attn_tile_kernel<64, KvPacked, true>, grid, dim3(256), 0, o, 1, p, kv)
@@ -416,7 +416,7 @@ cudaError_t attention_paged(const void* qkv, void* out, const int32_t* row_start
     const cudaError_t ready = allow_smem(attn_tc_kernel<KvPaged>, AttnTcSmem::kBytes);
     if (ready != cudaSuccess) return ready;
     const dim3 tc_grid((max_q + kAttnTcRows - 1) / kAttnTcRows, kv.heads, batch);
-    const cudaError_t st = launch(attn_tc_kernel<KvPaged>, tc_grid, dim3(kAttnTcRows), AttnTcSmem::kBytes, o, 1, p, paged(kv), kAttnTcMinRows);
+    const cudaError_t st = launch(attn_tc_kernel<KvPaged>, tc_grid, dim3(kAttnTcThreads), AttnTcSmem::kBytes, o, 1, p, paged(kv), kAttnTcMinRows);
     if (st != cudaSuccess || short_requests == 0) return st;
     p.skip_min_q = kAttnTcMinRows;
   }
