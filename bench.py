@@ -427,8 +427,13 @@ def server_record(torch, dist, rank, world, manifest_path, model_kind, requests,
         if model_kind == "native":
             cmd += ["--manifest", str(manifest_path)]
         proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
-        ready = proc.stdout.readline()
-        box[0] = port if ready and json.loads(ready).get("ready") else -1
+        import select
+        waited, _, _ = select.select([proc.stdout], [], [], 180.0)          # model load on every GPU; never block the run on it
+        ready = proc.stdout.readline() if waited else ""
+        try:
+            box[0] = port if ready and json.loads(ready).get("ready") else -1
+        except ValueError:
+            box[0] = -1
     if dist:
         dist.broadcast_object_list(box, src=0)
     port = box[0]
