@@ -404,10 +404,11 @@ def config3_record(device):
             "decode_plan": "persistent step" if plan == 1 else "launch per operation"}
 
 
-def server_record(torch, dist, rank, world, manifest_path, model_kind, requests, rate):
+def server_record(torch, dist, rank, world, manifest_path, model_kind, requests, rate, replicas_per_gpu=2, max_batch=32):
     """The batching-server workload (`requests` requests, Poisson arrivals, prompts log-uniform in [8, 900], outputs uniform in
-    [16, 256], seed 4) against ONE tinyinfer_server process that owns all `world` GPUs (one worker and one model replica
-    per GPU, requests routed to the worker with the fewest outstanding tokens).  Rank 0 starts the server; every rank
+    [16, 256], seed 4) against ONE tinyinfer_server process that owns all `world` GPUs (`replicas_per_gpu` workers and
+    model replicas per GPU with `max_batch` requests each -- by default two of 32, the configuration's 64 requests in
+    flight per GPU as two overlapping decode streams -- requests routed to the worker with the fewest outstanding tokens).  Rank 0 starts the server; every rank
     plays an equal share of the request stream through its own asyncio load generator; totals are summed, latency samples
     merged.  `rate` is far above what the GPUs sustain, so the requests queue at the server: a saturating load.
     model_kind "cpu" swaps the GPU model for the protocol stand-in (a token counter) and so measures the ceiling of the
@@ -421,8 +422,9 @@ def server_record(torch, dist, rank, world, manifest_path, model_kind, requests,
         with socket.socket() as probe:
             probe.bind(("127.0.0.1", 0))
             port = probe.getsockname()[1]
-        cmd = [str(binary()), "--model", model_kind, "--port", str(port), "--devices", ",".join(map(str, range(world))),
-               "--max-batch", "64", "--max-wait-us", "2000", "--max-new-tokens", "256", "--max-pending", "20000",
+        devices = ",".join(str(d) for d in range(world) for _ in range(replicas_per_gpu))
+        cmd = [str(binary()), "--model", model_kind, "--port", str(port), "--devices", devices,
+               "--max-batch", str(max_batch), "--max-wait-us", "2000", "--max-new-tokens", "256", "--max-pending", "20000",
                "--max-connections", "19000", "--per-connection", "32"]
         if model_kind == "native":
             cmd += ["--manifest", str(manifest_path)]
@@ -462,7 +464,8 @@ def server_record(torch, dist, rank, world, manifest_path, model_kind, requests,
                       "generated_tokens": tokens, "tokens_per_s": tokens / window if window > 0 else 0.0, "drain_window_s": window,
                       "mean_batch_size": sum(x["batch"] for x in shares) / max(1, completed),
                       "per_output_token_ms": loadgen.summarise(per_token), "ttft_ms": loadgen.summarise(ttft),
-                      "load_generators": world, "max_batch_per_gpu": 64}
+                      "load_generators": world, "replicas_per_gpu": replicas_per_gpu, "max_batch_per_replica": max_batch,
+                      "in_flight_per_gpu": replicas_per_gpu * max_batch}
     if dist:
         dist.barrier()
     if proc is not None:
@@ -613,6 +616,10 @@ def gpu_main(args, rank, world):
         offered = min(4096 * world, 16384)
         server["native"] = server_record(torch, dist, rank, world, manifest_path, "native", offered, 4000.0 * world)
         server["host_side_ceiling"] = server_record(torch, dist, rank, world, manifest_path, "cpu", offered, 4000.0 * world)
+        if world == 1:
+            # outside the configuration (more than 64 requests in flight per GPU): what one B200 sustains when four
+            # replicas of 64 overlap their decode steps
+            server["beyond"] = server_record(torch, dist, rank, world, manifest_path, "native", offered, 4000.0, replicas_per_gpu=4, max_batch=64)
 
     line = {"metric": "int8_gpt2_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": device_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations x int8 weights, f32 accumulate",
@@ -634,6 +641,8 @@ def gpu_main(args, rank, world):
         if server:
             line["server"] = server["native"]
             line["server_host_side_ceiling"] = server["host_side_ceiling"]
+            if "beyond" in server:
+                line["server_256_in_flight"] = server["beyond"]
         if world == 1 and not args.no_extras:
             cached_at_start = [len(p) + W for p in prompts]
             kernels = kernel_rooflines(cached_at_start, peak)

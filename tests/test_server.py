@@ -184,6 +184,20 @@ def test_several_workers_share_the_load_and_loadgen_runs():
     err = server.close()
 
 
+def test_a_device_listed_twice_carries_two_replicas():
+    """`--devices 0,0`: two workers (own model context each) on one device, both serving."""
+    with Server("--devices", "0,0", "--max-batch", 2, "--max-wait-us", 500, "--max-new-tokens", 64, "--max-pending", 512) as server:
+        assert server.ready["devices"] == [0, 0]
+        sock = server.connect()
+        items = loadgen.workload(4, 400.0, 12)
+        sock.sendall(b"".join(protocol.request(i, p, min(n, 64)) for _, i, p, n in items))
+        _, final = collect(sock, 12)
+        for _, i, p, n in items:
+            assert final[i]["status"] == 0 and final[i]["tokens"] == expected_tokens(p, min(n, 64))
+        sock.close()
+    server.close()
+
+
 @pytest.mark.parametrize("sanitizer", [[], ["-fsanitize=thread"]], ids=["plain", "tsan"])
 def test_mpsc_queue_with_real_threads(tmp_path, sanitizer):
     from tinyinfer_b200.build import SRC
