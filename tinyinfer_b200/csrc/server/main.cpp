@@ -441,7 +441,7 @@ void Worker::run() noexcept {
       for (size_t slot = 0; slot < slots; ++slot) {
         if (!active[slot]) continue;
         Active& a = *active[slot];
-        if (std::find(new_slots.begin(), new_slots.end(), int32_t(slot)) != new_slots.end()) continue;   // admitted this round
+        if (std::find(new_slots.begin(), new_slots.end(), int32_t(slot)) != new_slots.end()) continue;   // admitted in this pass
         if (a.job->cancel.load() || server_.stopping()) { replica_->reset(int(slot)); retire(slot, kCancelled); continue; }
         last_tokens.push_back({a.generated.back()});
         pass_slots.push_back(int32_t(slot));
