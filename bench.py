@@ -360,7 +360,7 @@ KERNEL_TRAFFIC = {
     "lm_head": (38_931_000, "profiles/gemm_tc_kernel_lm_head_batch32.md"),
 }
 STEP_TRAFFIC_SOURCE = "profiles/decode_step_kernel_batch32.md"
-STEP_TRAFFIC_RATIO = None
+STEP_TRAFFIC_RATIO = 1.06
 
 
 def config0_record(model, weights, peak):
