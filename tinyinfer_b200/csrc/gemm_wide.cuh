@@ -12,7 +12,7 @@
 //   * tiles of 128 channels x 128 rows, six operand stages in flight, CTAs persistent over the tiles of the problem, so
 //     the epilogue of one tile overlaps the main loop of the next;
 //   * the K ranges of gemm()'s K split still get separate TMEM accumulators (three, in rotation) and are added in range
-//     order -- by eight dedicated warps that keep the running sums in registers while the tensor cores work on the next
+//     order -- by sixteen dedicated warps that keep the running sums in registers while the tensor cores work on the next
 //     range -- so a row's result carries the same bits as in the decode-shaped kernel, whatever the row count.
 // Warp roles (576 threads): 0 producer (bulk copy of the weights, TMA of the rows), 1 MMA issuer, 2-17 fold the K ranges
 // and finish the tile (bias, GELU, residual, K/V placement, store) -- the finishing of a tile is cut into pieces of
