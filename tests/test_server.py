@@ -184,6 +184,21 @@ def test_several_workers_share_the_load_and_loadgen_runs():
     err = server.close()
 
 
+@pytest.mark.parametrize("group", [1, 3, 4])
+def test_grouped_admission_serves_every_request(group):
+    """`--admit-batch n`: a busy worker waits for n free slots (or for as many as there are requests waiting) before it
+    admits; whatever n, every request is served with the tokens the model function gives."""
+    with Server("--max-batch", 4, "--admit-batch", group, "--max-wait-us", 200, "--max-new-tokens", 64, "--max-pending", 512) as server:
+        sock = server.connect()
+        items = loadgen.workload(4, 400.0, 23)
+        sock.sendall(b"".join(protocol.request(i, p, min(n, 64)) for _, i, p, n in items))
+        _, final = collect(sock, 23)
+        for _, i, p, n in items:
+            assert final[i]["status"] == 0 and final[i]["tokens"] == expected_tokens(p, min(n, 64))
+        sock.close()
+    server.close()
+
+
 def test_a_device_listed_twice_carries_two_replicas():
     """`--devices 0,0`: two workers (own model context each) on one device, both serving."""
     with Server("--devices", "0,0", "--max-batch", 2, "--max-wait-us", 500, "--max-new-tokens", 64, "--max-pending", 512) as server:
