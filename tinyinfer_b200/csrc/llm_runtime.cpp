@@ -67,6 +67,7 @@ struct ti_llm_model {
   tib::ModelShape shape;
   bool int8 = false, poisoned = false;
   cudaStream_t stream = nullptr;
+  cudaStream_t copy_stream = nullptr;                 // results of steps launched ahead travel here, beside the next step
   ti_llm_trace trace{};
   std::vector<void*> owned;                      // cudaMalloc'ed
   std::vector<void*> pinned;                     // cudaMallocHost'ed
@@ -100,8 +101,11 @@ struct ti_llm_model {
     cudaGetDevice(&before);
     cudaSetDevice(opt.device);
     if (stream) cudaStreamSynchronize(stream);
+    if (copy_stream) cudaStreamSynchronize(copy_stream);
     for (const StepGraph& g : graphs) cudaGraphExecDestroy(g.exec);
     for (cudaEvent_t e : spec_done) if (e) cudaEventDestroy(e);
+    for (cudaEvent_t e : step_end) if (e) cudaEventDestroy(e);
+    if (copy_stream) cudaStreamDestroy(copy_stream);
     for (void* p : owned) cudaFree(p);
     for (void* p : pinned) cudaFreeHost(p);
     if (stream) cudaStreamDestroy(stream);
@@ -217,7 +221,12 @@ struct ti_llm_model {
     d_next = dev<int32_t>(size_t(opt.max_batch)); h_next = host<int32_t>(size_t(opt.max_batch));
     d_seg = dev<int32_t>(size_t(5) * opt.max_batch); h_seg = host<int32_t>(size_t(5) * opt.max_batch);
     d_step = dev<int32_t>(1);
-    for (int i = 0; i < 2; ++i) { h_spec[i] = host<int32_t>(size_t(opt.max_batch) + 1); ck(cudaEventCreateWithFlags(&spec_done[i], cudaEventDisableTiming)); }
+    for (int i = 0; i < 2; ++i) {
+      h_spec[i] = host<int32_t>(size_t(opt.max_batch) + 1);
+      ck(cudaEventCreateWithFlags(&spec_done[i], cudaEventDisableTiming));
+      ck(cudaEventCreateWithFlags(&step_end[i], cudaEventDisableTiming));
+    }
+    ck(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
     if (const char* v = std::getenv("TINYINFER_B200_SPECULATE")) { spec_after = std::atoi(v); speculate = spec_after > 0; }
     d_argmax = dev<uint8_t>(size_t(12) * opt.max_batch + 8);
     ck(cudaMemsetAsync(d_argmax, 0, size_t(12) * opt.max_batch + 8, stream));
@@ -493,7 +502,7 @@ struct ti_llm_model {
   bool speculate = true;
   int spec_after = 8, host_step = 0;                  // host_step mirrors the device step counter
   int32_t* h_spec[2] = {nullptr, nullptr};            // pinned: ids of a step launched ahead, then the device status word
-  cudaEvent_t spec_done[2] = {nullptr, nullptr};
+  cudaEvent_t spec_done[2] = {nullptr, nullptr}, step_end[2] = {nullptr, nullptr};
   int32_t *d_seg = nullptr, *h_seg = nullptr, *d_step = nullptr, *d_log = nullptr, *h_log = nullptr;
   bool use_graph = true, use_pdl = true;
   // Early release of the next launch (see LaunchOpts::early_trigger).  After a GEMM comes a kernel whose reads ahead
@@ -627,9 +636,12 @@ struct ti_llm_model {
         const int buffer = (spec.oldest + spec.inflight) & 1;
         if (persistent_step(batch)) launch_persistent(batch, false);
         else ck(cudaGraphLaunch(step_graph(batch, chunks), stream));
-        ck(cudaMemcpyAsync(h_spec[buffer], d_log + size_t(host_step) * batch, size_t(batch) * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
-        ck(cudaMemcpyAsync(h_spec[buffer] + opt.max_batch, d_status_addr, sizeof(unsigned int), cudaMemcpyDeviceToHost, stream));
-        ck(cudaEventRecord(spec_done[buffer], stream));
+        // the step's ids and the status word go home on the side stream: the next step does not queue behind the copies
+        ck(cudaEventRecord(step_end[buffer], stream));
+        ck(cudaStreamWaitEvent(copy_stream, step_end[buffer], 0));
+        ck(cudaMemcpyAsync(h_spec[buffer], d_log + size_t(host_step) * batch, size_t(batch) * sizeof(int32_t), cudaMemcpyDeviceToHost, copy_stream));
+        ck(cudaMemcpyAsync(h_spec[buffer] + opt.max_batch, d_status_addr, sizeof(unsigned int), cudaMemcpyDeviceToHost, copy_stream));
+        ck(cudaEventRecord(spec_done[buffer], copy_stream));
         ++host_step; ++spec.inflight;
         return true;
       };
